@@ -1,0 +1,175 @@
+/*
+ * swage_b200 -- C ABI of the B200 segmented-reduction / vector-add library.
+ *
+ * This is the boundary a Swage maintainer binds instead of the reference's
+ * "compile to PTX, load with the CUDA Driver, cuLaunchKernel" path:
+ *   include/swage-c/Codegen.h:21-31            (swageCompile*ToPTX)
+ *   python/SwageExtensionNanobind.cpp:27-99    (_compile_ptx, _compile_segmented_reduction_ptx)
+ *   python/swage/_runtime.py:399-531           (_CudaDriver: load / launch / launch_segmented)
+ * Kernels are prebuilt for sm_100a; nothing is compiled at run time.
+ *
+ * Conventions
+ *   - plain pointers and sizes only; `stream` is a cudaStream_t / CUstream
+ *     passed as void* (the integer PyTorch exposes as stream.cuda_stream);
+ *   - every device pointer must belong to the CUDA device that is current on
+ *     the calling thread; launches are asynchronous and never synchronise,
+ *     copy, cast, switch device or fall back to the CPU;
+ *   - every function returns a swg_status (0 = ok); on failure a thread-local
+ *     message is available from swg_last_error();
+ *   - the library keeps no caller pointer after a call returns; the only
+ *     object it owns is swg_plan (until swg_plan_destroy).
+ */
+#ifndef SWAGE_B200_H
+#define SWAGE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SWG_ABI_VERSION 1
+
+typedef enum swg_status {
+  SWG_OK = 0,
+  SWG_ERR_INVALID_ARGUMENT = 1, /* bad kind / schedule / NULL pointer / negative count */
+  SWG_ERR_INVALID_OFFSETS = 2,  /* offsets break the CSR contract */
+  SWG_ERR_CUDA = 3,             /* a CUDA runtime call failed; text names it */
+  SWG_ERR_PLAN_MISMATCH = 4,    /* plan built for other counts / device / operation */
+  SWG_ERR_UNSUPPORTED = 5,      /* schedule needs a plan, or size beyond a stated limit */
+  SWG_ERR_DEVICE_TIMEOUT = 6    /* a bounded device-side wait gave up (read by swg_plan_status) */
+} swg_status;
+
+/* Reduction kinds: the two the reference lowers
+ * (lib/Conversion/SegmentedReduction/SegmentedReduction.cpp:106-108 rejects the rest). */
+#define SWG_KIND_SUM 0 /* identity +0.0f, fp32 add */
+#define SWG_KIND_MAX 1 /* identity -inf, NaN-propagating maximum, -0 < +0 */
+
+/* Operation a plan is built for. */
+#define SWG_OP_REDUCE 0
+#define SWG_OP_SOFTMAX 1
+
+/* Schedules. AUTO lets the plan (or, without one, the mean segment length)
+ * decide.  WARP and CTA need no plan; SPLIT and PERSISTENT run the plan's
+ * tile tasks and therefore need one. */
+#define SWG_SCHED_AUTO 0
+#define SWG_SCHED_WARP 1       /* one warp per segment */
+#define SWG_SCHED_CTA 2        /* one CTA per segment: the reference's own mapping */
+#define SWG_SCHED_SPLIT 3      /* one tile task per CTA, long segments chunked, second-pass combine */
+#define SWG_SCHED_PERSISTENT 4 /* one CTA per SM slot, bulk-copy ring, tasks drawn from a ticket counter */
+
+/* Why swg_validate_offsets_i32 rejected an array (order = order of the checks
+ * in python/swage/_segmented_qualification.py:30-55). */
+#define SWG_OFFSETS_OK 0
+#define SWG_OFFSETS_EMPTY 1          /* no initial zero */
+#define SWG_OFFSETS_COUNT_RANGE 2    /* value or segment count outside [0, 2^31) */
+#define SWG_OFFSETS_OUTPUT_SMALL 3   /* fewer outputs than segments */
+#define SWG_OFFSETS_NONZERO_START 4  /* offsets[0] != 0 */
+#define SWG_OFFSETS_NEGATIVE 5       /* an offset < 0 */
+#define SWG_OFFSETS_DECREASING 6     /* offsets[i] < offsets[i-1] */
+#define SWG_OFFSETS_EXCEEDS_VALUES 7 /* offsets[last] > value_count */
+
+typedef struct swg_plan swg_plan;
+
+/* Text of the last failure on this thread ("" when none). */
+const char *swg_last_error(void);
+const char *swg_status_name(int status);
+int swg_abi_version(void);
+
+/* out[i] = x[i] + y[i] for 0 <= i < n.
+ * Replaces the generated kernel add_kernel(void*, void*, void*, int32)
+ * (lib/Conversion/FixedBlockToGPU/FixedBlockToGPU.cpp:177-226) and its launch
+ * (python/swage/_runtime.py:500-503, 511-531).  `block_hint` is the caller's
+ * logical BLOCK; it does not change any result bit and only has to be > 0.
+ * Pointers may be 4-byte aligned (offset views). n == 0 is a no-op. */
+int swg_vadd_f32(const float *x, const float *y, float *out, int32_t n,
+                 int32_t block_hint, void *stream);
+
+/* Host-side CSR validation, same rule set and order as
+ * python/swage/_segmented_qualification.py:30-55 (_validate_offsets):
+ * `count` = number of offsets (segments + 1).  Returns SWG_OK or
+ * SWG_ERR_INVALID_OFFSETS with *reason = SWG_OFFSETS_*, *index = first
+ * offending position (or -1). reason/index may be NULL. */
+int swg_validate_offsets_i32(const int32_t *host_offsets, int64_t count,
+                             int64_t value_count, int64_t output_count,
+                             int32_t *reason, int64_t *index);
+
+/* Host planner: segment-length histogram -> buckets -> tile tasks -> schedule.
+ * `host_offsets` has segment_count + 1 validated entries.  The plan owns
+ * device copies of the task list, of the offsets (16-byte aligned and padded,
+ * so they can be bulk-copied) and the scratch for split-segment partials, all
+ * on the current device.  It is the planned scheduling layer of the reference
+ * (DESIGN.md:143-151 there: warp, packed_warp, cta, split_cta, merge,
+ * persistent) made concrete.  A plan is valid only for launches whose device
+ * offsets hold the same numbers. */
+int swg_plan_create(const int32_t *host_offsets, int32_t segment_count,
+                    int32_t value_count, int op, swg_plan **plan);
+int swg_plan_destroy(swg_plan *plan);
+/* JSON text: counts, histogram, bucket shares, task counts, chosen schedule.
+ * Returns SWG_ERR_INVALID_ARGUMENT when `capacity` is too small. */
+int swg_plan_describe(const swg_plan *plan, char *json, size_t capacity);
+/* Synchronises the plan's device and reports a device-side wait that gave up
+ * in any launch since the last call (SWG_ERR_DEVICE_TIMEOUT), else SWG_OK. */
+int swg_plan_status(swg_plan *plan);
+
+/* The planner alone, on the host: no device is touched.  Writes up to
+ * `task_capacity` tasks as 4 x int32 each {first segment, segment count or
+ * partial slot (-1 = whole segment), first value, value count | kind << 28
+ * (kind 0 = packed whole segments, 1 = chunk of one long segment)}, the total
+ * number of tasks to *task_count, and the same JSON as swg_plan_describe.
+ * `tasks` and `json` may be NULL.  For inspection and for tests. */
+int swg_plan_host_tasks(const int32_t *host_offsets, int32_t segment_count,
+                        int op, int32_t *tasks, int64_t task_capacity,
+                        int64_t *task_count, char *json, size_t json_capacity);
+
+/* out[s] = reduce(values[offsets[s] .. offsets[s+1])) for 0 <= s < segment_count.
+ * Replaces the generated kernels segmented_sum / segmented_max(void* values,
+ * void* offsets, void* out, int32 value_count, int32 segment_count)
+ * (lib/Conversion/SegmentedReduction/SegmentedReduction.cpp:185-283) and their
+ * launch (python/swage/_segmented_qualification.py:154-169,
+ * python/swage/_runtime.py:505-509).  Empty segment -> identity.  Only the
+ * first segment_count outputs are written.  `plan` may be NULL (then only
+ * AUTO / WARP / CTA are accepted).  `block_hint` is the reference's
+ * block_size (threads per CTA for the CTA schedule; ignored elsewhere; 0 =
+ * library default).  Results are bit-reproducible from run to run for a given
+ * schedule and plan (no floating-point atomics). */
+int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
+                      float *out, int32_t value_count, int32_t segment_count,
+                      const swg_plan *plan, int schedule, int32_t block_hint,
+                      void *stream);
+
+/* out[i] = exp(values[i] - m_s) / d_s over each segment s, with m_s the
+ * segment maximum and d_s the sum of exp(values - m_s); empty segments write
+ * nothing; positions outside every segment are not touched.  `out` must not
+ * alias `values`.  The reference defines this only as a semantic form
+ * (test/Dialect/Swage/softmax.mlir:13-31; roadmap M5) and has no lowering. */
+int swg_segsoftmax_f32(const float *values, const int32_t *offsets, float *out,
+                       int32_t value_count, int32_t segment_count,
+                       const swg_plan *plan, int schedule, void *stream);
+
+/* Cut segment_count segments into `shards` contiguous ranges balanced by
+ * element count: shard g owns segments [seg_begin[g], seg_begin[g+1]).
+ * seg_begin has shards + 1 entries.  No reference counterpart (the reference
+ * is single-GPU: python/swage/_runtime.py:146-151); it is the sharding rule of
+ * the multi-GPU path. */
+int swg_shard_offsets(const int32_t *host_offsets, int32_t segment_count,
+                      int32_t shards, int32_t *seg_begin);
+
+/* Per-launch device timing of the dominant kernel of every call made between
+ * start and stop (the tile kernel of a planned reduce, not its combine pass;
+ * the only kernel otherwise).  The library records a pair of CUDA events
+ * around that kernel on the launch stream.  swg_profile_stop synchronises
+ * those events, writes up to `capacity` durations in milliseconds and the
+ * number of launches seen.  At most `capacity` launches given to start are
+ * recorded; later ones run untimed.  No reference counterpart: the reference
+ * has no timing facility (its debugging switches are the SWAGE_DUMP_*
+ * variables, python/swage/_runtime.py:381-396). */
+int swg_profile_start(int32_t capacity);
+int swg_profile_stop(float *milliseconds, int32_t capacity, int32_t *count);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SWAGE_B200_H */

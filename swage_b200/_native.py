@@ -1,0 +1,221 @@
+"""ctypes binding of ``libswage_b200.so`` (the C ABI in ``include/swage_b200.h``).
+
+This takes the place of the reference's ``_CudaDriver`` ctypes wrapper
+(``python/swage/_runtime.py:399-531``) and of its nanobind codegen module
+(``python/SwageExtensionNanobind.cpp:27-99``): instead of compiling PTX and
+calling ``cuLaunchKernel``, the Python layer calls prebuilt sm_100a kernels
+through plain C functions.
+
+There is no CPU fallback.  If the shared library is missing the loader raises
+``RuntimeError`` -- it does not try to build it, and nothing else in the
+package computes results on the host.
+"""
+
+import ctypes
+import pathlib
+import threading
+
+LIBRARY_PATH = pathlib.Path(__file__).resolve().parent / "libswage_b200.so"
+
+# mirrors of the header's constants
+KIND_SUM, KIND_MAX = 0, 1
+OP_REDUCE, OP_SOFTMAX = 0, 1
+SCHED_AUTO, SCHED_WARP, SCHED_CTA, SCHED_SPLIT, SCHED_PERSISTENT = range(5)
+SCHEDULES = {
+    "auto": SCHED_AUTO,
+    "warp": SCHED_WARP,
+    "cta": SCHED_CTA,
+    "split": SCHED_SPLIT,
+    "persistent": SCHED_PERSISTENT,
+}
+OFFSETS_REASONS = (
+    "ok", "empty", "count_range", "output_small", "nonzero_start",
+    "negative", "decreasing", "exceeds_values",
+)
+
+EXPORTS = (
+    "swg_last_error", "swg_status_name", "swg_abi_version", "swg_vadd_f32",
+    "swg_validate_offsets_i32", "swg_plan_create", "swg_plan_destroy",
+    "swg_plan_describe", "swg_plan_status", "swg_plan_host_tasks",
+    "swg_segreduce_f32",
+    "swg_segsoftmax_f32", "swg_shard_offsets", "swg_profile_start",
+    "swg_profile_stop",
+)
+
+_lock = threading.Lock()
+_library = None
+
+
+def _declare(lib):
+    c_int, c_i32, c_i64 = ctypes.c_int, ctypes.c_int32, ctypes.c_int64
+    ptr = ctypes.c_void_p
+    lib.swg_last_error.restype = ctypes.c_char_p
+    lib.swg_last_error.argtypes = []
+    lib.swg_status_name.restype = ctypes.c_char_p
+    lib.swg_status_name.argtypes = [c_int]
+    lib.swg_abi_version.restype = c_int
+    lib.swg_abi_version.argtypes = []
+    lib.swg_vadd_f32.restype = c_int
+    lib.swg_vadd_f32.argtypes = [ptr, ptr, ptr, c_i32, c_i32, ptr]
+    lib.swg_validate_offsets_i32.restype = c_int
+    lib.swg_validate_offsets_i32.argtypes = [
+        ptr, c_i64, c_i64, c_i64,
+        ctypes.POINTER(c_i32), ctypes.POINTER(c_i64)]
+    lib.swg_plan_create.restype = c_int
+    lib.swg_plan_create.argtypes = [
+        ptr, c_i32, c_i32, c_int, ctypes.POINTER(ptr)]
+    lib.swg_plan_destroy.restype = c_int
+    lib.swg_plan_destroy.argtypes = [ptr]
+    lib.swg_plan_describe.restype = c_int
+    lib.swg_plan_describe.argtypes = [ptr, ctypes.c_char_p, ctypes.c_size_t]
+    lib.swg_plan_status.restype = c_int
+    lib.swg_plan_status.argtypes = [ptr]
+    lib.swg_plan_host_tasks.restype = c_int
+    lib.swg_plan_host_tasks.argtypes = [
+        ptr, c_i32, c_int, ptr, c_i64, ctypes.POINTER(c_i64),
+        ctypes.c_char_p, ctypes.c_size_t]
+    lib.swg_segreduce_f32.restype = c_int
+    lib.swg_segreduce_f32.argtypes = [
+        c_int, ptr, ptr, ptr, c_i32, c_i32, ptr, c_int, c_i32, ptr]
+    lib.swg_segsoftmax_f32.restype = c_int
+    lib.swg_segsoftmax_f32.argtypes = [
+        ptr, ptr, ptr, c_i32, c_i32, ptr, c_int, ptr]
+    lib.swg_shard_offsets.restype = c_int
+    lib.swg_shard_offsets.argtypes = [ptr, c_i32, c_i32, ptr]
+    lib.swg_profile_start.restype = c_int
+    lib.swg_profile_start.argtypes = [c_i32]
+    lib.swg_profile_stop.restype = c_int
+    lib.swg_profile_stop.argtypes = [ptr, c_i32, ctypes.POINTER(c_i32)]
+
+
+def library():
+    """Load the shared library once; fail loudly when it is absent."""
+    global _library
+    with _lock:
+        if _library is None:
+            if not LIBRARY_PATH.exists():
+                raise RuntimeError(
+                    f"{LIBRARY_PATH} is missing: build it with "
+                    "'python -m swage_b200._build'. There is no CPU fallback."
+                )
+            lib = ctypes.CDLL(str(LIBRARY_PATH))
+            _declare(lib)
+            _library = lib
+        return _library
+
+
+def check(status, function_name):
+    """Raise in the reference's driver-error style (``_runtime.py:452-469``)."""
+    if status == 0:
+        return
+    lib = library()
+    name = lib.swg_status_name(status).decode()
+    text = (lib.swg_last_error() or b"").decode() or "unknown"
+    raise RuntimeError(f"{function_name} failed: {name} ({status}): {text}")
+
+
+def vadd(x_ptr, y_ptr, out_ptr, n, block, stream):
+    check(library().swg_vadd_f32(x_ptr, y_ptr, out_ptr, n, block, stream),
+          "swg_vadd_f32")
+
+
+def segreduce(kind, values_ptr, offsets_ptr, out_ptr, value_count,
+              segment_count, plan_handle, schedule, block, stream):
+    check(
+        library().swg_segreduce_f32(
+            kind, values_ptr, offsets_ptr, out_ptr, value_count,
+            segment_count, plan_handle, schedule, block, stream),
+        "swg_segreduce_f32",
+    )
+
+
+def segsoftmax(values_ptr, offsets_ptr, out_ptr, value_count, segment_count,
+               plan_handle, schedule, stream):
+    check(
+        library().swg_segsoftmax_f32(
+            values_ptr, offsets_ptr, out_ptr, value_count, segment_count,
+            plan_handle, schedule, stream),
+        "swg_segsoftmax_f32",
+    )
+
+
+def validate_offsets(host_ptr, count, value_count, output_count):
+    """Return ``(reason_name, index)``; ``("ok", -1)`` when the array is fine."""
+    reason = ctypes.c_int32(0)
+    index = ctypes.c_int64(-1)
+    library().swg_validate_offsets_i32(
+        host_ptr, count, value_count, output_count,
+        ctypes.byref(reason), ctypes.byref(index))
+    return OFFSETS_REASONS[reason.value], index.value
+
+
+def plan_create(host_ptr, segment_count, value_count, op):
+    handle = ctypes.c_void_p()
+    check(
+        library().swg_plan_create(
+            host_ptr, segment_count, value_count, op, ctypes.byref(handle)),
+        "swg_plan_create",
+    )
+    return handle
+
+
+def plan_destroy(handle):
+    library().swg_plan_destroy(handle)
+
+
+def plan_describe(handle):
+    buffer = ctypes.create_string_buffer(8192)
+    check(library().swg_plan_describe(handle, buffer, len(buffer)),
+          "swg_plan_describe")
+    return buffer.value.decode()
+
+
+def plan_host_tasks(host_ptr, segment_count, op=OP_REDUCE):
+    """Run the planner on the host only; return ``(tasks, description)``.
+
+    ``tasks`` is a list of ``(segment, count_or_slot, value_begin,
+    value_count, kind)`` tuples.
+    """
+    import json
+
+    lib = library()
+    total = ctypes.c_int64(0)
+    text = ctypes.create_string_buffer(8192)
+    check(lib.swg_plan_host_tasks(host_ptr, segment_count, op, None, 0,
+                                  ctypes.byref(total), text, len(text)),
+          "swg_plan_host_tasks")
+    words = (ctypes.c_int32 * (4 * max(total.value, 1)))()
+    check(lib.swg_plan_host_tasks(host_ptr, segment_count, op, words,
+                                  total.value, ctypes.byref(total), None, 0),
+          "swg_plan_host_tasks")
+    tasks = []
+    for t in range(total.value):
+        seg, count, vbegin, packed = words[4 * t:4 * t + 4]
+        packed &= 0xFFFFFFFF
+        tasks.append((seg, count, vbegin, packed & ((1 << 28) - 1),
+                      packed >> 28))
+    return tasks, json.loads(text.value.decode())
+
+
+def plan_status(handle):
+    check(library().swg_plan_status(handle), "swg_plan_status")
+
+
+def shard_offsets(host_ptr, segment_count, shards):
+    cuts = (ctypes.c_int32 * (shards + 1))()
+    check(library().swg_shard_offsets(host_ptr, segment_count, shards, cuts),
+          "swg_shard_offsets")
+    return list(cuts)
+
+
+def profile_start(capacity):
+    check(library().swg_profile_start(capacity), "swg_profile_start")
+
+
+def profile_stop(capacity):
+    """Durations (ms) of the dominant kernel of each call since the start."""
+    buffer = (ctypes.c_float * max(capacity, 1))()
+    count = ctypes.c_int32(0)
+    check(library().swg_profile_stop(buffer, capacity, ctypes.byref(count)),
+          "swg_profile_stop")
+    return [buffer[i] for i in range(min(count.value, capacity))]

@@ -1,0 +1,398 @@
+"""Segmented sum / max / softmax runner (drop-in for the reference's internal
+``python/swage/_segmented_qualification.py``).
+
+Same names, argument meaning and error behaviour for the launch half of that
+module: ``_validate_counts`` (:20-27), ``_validate_offsets`` (:30-55),
+``_validate_tensors`` (:58-93) and ``launch_gpu`` (:120-172).  The reference's
+``cpu_oracle`` (:288-329) is a test checker there and is one here too: it
+lives with the test infrastructure, not in this package, and nothing here
+computes a result on the host.
+
+Differences that do not change results:
+
+* offsets are validated by one native pass over the host copy instead of a
+  Python loop over a list (the reference's ``:43-50``);
+* no per-call compilation or module load (the reference's ``:144-155``);
+* ``block_size`` is still validated the same way but is only a hint: the
+  physical schedule (warp / CTA / split / persistent tile tasks) is chosen by
+  a plan built from the segment-length histogram;
+* plans are cached per offsets content (exact comparison of the host copy),
+  so repeated launches over the same CSR structure skip the planner.
+"""
+
+import collections
+import json
+import threading
+
+from . import _runtime
+
+_I32_LIMIT = 1 << 31
+_KINDS = {"sum": 0, "max": 1}
+# Below this many values + segments a launch is latency-bound whatever the
+# mapping, and the plan-free schedules are used.
+_PLAN_THRESHOLD = 1 << 16
+_PLAN_CACHE_ENTRIES = 4
+
+
+def _validate_counts(value_count, segment_count):
+    """Both counts travel as signed i32 through the kernel ABI."""
+    for label, count in (("value count", value_count),
+                         ("segment count", segment_count)):
+        if type(count) is not int or count < 0 or count >= _I32_LIMIT:
+            raise ValueError(f"{label} must be a nonnegative i32")
+
+
+def _validate_offsets(offsets, value_count, output_count):
+    """Validate a host list of offsets; return the segment count.
+
+    List form of the check, kept for callers that hold Python ints (the
+    reference's tests call it this way).  Tensors go through
+    ``_validate_host_offsets`` which applies the same rules natively.
+    """
+    if not offsets:
+        raise ValueError("offsets must contain at least the initial zero")
+    segment_count = len(offsets) - 1
+    _validate_counts(value_count, segment_count)
+    if type(output_count) is not int or output_count < segment_count:
+        raise ValueError(
+            f"output has {output_count} elements for {segment_count} segments"
+        )
+    if offsets[0] != 0:
+        raise ValueError("offsets must start at zero")
+    floor = 0
+    for offset in offsets:
+        if type(offset) is not int or offset < -_I32_LIMIT or (
+            offset >= _I32_LIMIT
+        ):
+            raise ValueError("offsets must contain signed i32 values")
+        if offset < 0:
+            raise ValueError("offsets must not be negative")
+        if offset < floor:
+            raise ValueError("offsets must be nondecreasing")
+        floor = offset
+    if offsets[-1] > value_count:
+        raise ValueError(
+            f"final offset {offsets[-1]} exceeds value count {value_count}"
+        )
+    return segment_count
+
+
+def _validate_host_offsets(host_offsets, value_count, output_count):
+    """Native one-pass form of ``_validate_offsets`` for a CPU int32 tensor."""
+    from . import _native
+
+    count = host_offsets.numel()
+    if count == 0:
+        raise ValueError("offsets must contain at least the initial zero")
+    segment_count = count - 1
+    _validate_counts(value_count, segment_count)
+    reason, _ = _native.validate_offsets(
+        host_offsets.data_ptr(), count, value_count, output_count
+    )
+    if reason == "ok":
+        return segment_count
+    if reason == "output_small":
+        raise ValueError(
+            f"output has {output_count} elements for {segment_count} segments"
+        )
+    if reason == "nonzero_start":
+        raise ValueError("offsets must start at zero")
+    if reason == "negative":
+        raise ValueError("offsets must not be negative")
+    if reason == "decreasing":
+        raise ValueError("offsets must be nondecreasing")
+    if reason == "exceeds_values":
+        raise ValueError(
+            f"final offset {int(host_offsets[-1])} exceeds value count "
+            f"{value_count}"
+        )
+    if reason == "empty":
+        raise ValueError("offsets must contain at least the initial zero")
+    raise ValueError("value count must be a nonnegative i32")
+
+
+def _validate_tensors(values, offsets, output, *, require_cuda=True,
+                      elementwise_output=False, _host_offsets=None):
+    """Check dtype / rank / layout / offsets / device; return both counts.
+
+    Same order and messages as the reference (:58-93).  With
+    ``elementwise_output`` the output holds one element per value (softmax)
+    instead of one per segment.
+    """
+    torch = _runtime._import_torch()
+    named = (("values", values), ("offsets", offsets), ("output", output))
+    for name, tensor in named:
+        if not isinstance(tensor, torch.Tensor):
+            raise TypeError(f"{name} must be a torch.Tensor")
+    for name, tensor in (named[0], named[2]):
+        if tensor.dtype != torch.float32:
+            raise TypeError(f"{name} must have dtype torch.float32")
+    if offsets.dtype != torch.int32:
+        raise TypeError("offsets must have dtype torch.int32")
+    for name, tensor in named:
+        if tensor.dim() != 1:
+            raise TypeError(f"{name} must have rank one")
+        if not tensor.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+
+    value_count = values.numel()
+    host = _host_offsets
+    if host is None:
+        host = offsets.detach().cpu()
+    output_count = output.numel()
+    if elementwise_output:
+        segment_count = _validate_host_offsets(
+            host, value_count, max(host.numel() - 1, 0)
+        )
+        if output_count < value_count:
+            raise ValueError(
+                f"output has {output_count} elements for {value_count} values"
+            )
+    else:
+        segment_count = _validate_host_offsets(host, value_count, output_count)
+    if require_cuda:
+        if not torch.cuda.is_available():
+            raise RuntimeError("CUDA is unavailable in PyTorch")
+        device = torch.cuda.current_device()
+        for name, tensor in named:
+            if tensor.device.type != "cuda":
+                raise TypeError(f"{name} must be a CUDA tensor")
+            if tensor.device.index != device:
+                raise ValueError(f"{name} must be on the current CUDA device")
+    _last_host_offsets.value = host
+    return value_count, segment_count
+
+
+# the host copy made by the most recent validation on this thread, so that
+# launch_gpu can hand it to the planner without a second device-to-host copy
+_last_host_offsets = threading.local()
+
+
+class SegmentPlan:
+    """A host-built schedule for one CSR offsets array on one device.
+
+    Built by the native planner from the segment-length histogram: segments
+    are bucketed by length, short ones are packed into tile tasks, long ones
+    are cut into chunks whose partials a second pass merges, and a schedule is
+    chosen.  The plan owns device copies of its task list, of the offsets and
+    of the partial scratch.  It stays valid for as long as the offsets hold
+    the same numbers; launches that share a plan must not overlap on the GPU
+    (they share the partial scratch and the ticket counter).
+    """
+
+    def __init__(self, host_offsets, value_count, op="reduce"):
+        from . import _native
+
+        torch = _runtime._import_torch()
+        if (
+            not isinstance(host_offsets, torch.Tensor)
+            or host_offsets.device.type != "cpu"
+            or host_offsets.dtype != torch.int32
+            or host_offsets.dim() != 1
+            or not host_offsets.is_contiguous()
+            or host_offsets.numel() < 1
+        ):
+            raise TypeError(
+                "plan needs a contiguous rank-one CPU int32 offsets tensor"
+            )
+        self._native = _native
+        self.segment_count = host_offsets.numel() - 1
+        self.value_count = int(value_count)
+        self.op = op
+        self.device = torch.cuda.current_device()
+        code = _native.OP_SOFTMAX if op == "softmax" else _native.OP_REDUCE
+        self._handle = _native.plan_create(
+            host_offsets.data_ptr(), self.segment_count, self.value_count, code
+        )
+
+    @property
+    def handle(self):
+        if self._handle is None:
+            raise RuntimeError("plan has been closed")
+        return self._handle
+
+    def describe(self):
+        """Histogram, bucket shares, task counts and the chosen schedule."""
+        return json.loads(self._native.plan_describe(self.handle))
+
+    def check(self):
+        """Synchronise and raise if a bounded device-side wait gave up."""
+        self._native.plan_status(self.handle)
+
+    def close(self):
+        if self._handle is not None:
+            self._native.plan_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def plan_segments(offsets, value_count=None, op="reduce"):
+    """Validate ``offsets`` (CPU or CUDA int32) and build a ``SegmentPlan``."""
+    torch = _runtime._import_torch()
+    if not isinstance(offsets, torch.Tensor):
+        raise TypeError("offsets must be a torch.Tensor")
+    if offsets.dtype != torch.int32:
+        raise TypeError("offsets must have dtype torch.int32")
+    if offsets.dim() != 1:
+        raise TypeError("offsets must have rank one")
+    host = offsets.detach().cpu().contiguous()
+    if value_count is None:
+        value_count = int(host[-1]) if host.numel() else 0
+    _validate_host_offsets(host, int(value_count), max(host.numel() - 1, 0))
+    return SegmentPlan(host, value_count, op)
+
+
+_plan_cache = collections.OrderedDict()
+_plan_cache_lock = threading.Lock()
+
+
+def _cached_plan(host_offsets, value_count, op, device):
+    """Plan for exactly these offsets; equality is checked on the full array."""
+    torch = _runtime._import_torch()
+    key = (device, op, host_offsets.numel(), value_count)
+    with _plan_cache_lock:
+        bucket = _plan_cache.get(key)
+        if bucket is not None:
+            for kept, plan in bucket:
+                if torch.equal(kept, host_offsets):
+                    _plan_cache.move_to_end(key)
+                    return plan
+        plan = SegmentPlan(host_offsets, value_count, op)
+        _plan_cache.setdefault(key, []).append((host_offsets.clone(), plan))
+        _plan_cache.move_to_end(key)
+        while sum(len(b) for b in _plan_cache.values()) > _PLAN_CACHE_ENTRIES:
+            oldest = next(iter(_plan_cache))
+            entries = _plan_cache[oldest]
+            entries.pop(0)[1].close()
+            if not entries:
+                del _plan_cache[oldest]
+        return plan
+
+
+def clear_plan_cache():
+    """Drop every cached plan (frees their device memory)."""
+    with _plan_cache_lock:
+        for entries in _plan_cache.values():
+            for _, plan in entries:
+                plan.close()
+        _plan_cache.clear()
+
+
+def _schedule_code(schedule):
+    from . import _native
+
+    if schedule not in _native.SCHEDULES:
+        raise ValueError(
+            "schedule must be one of " + ", ".join(sorted(_native.SCHEDULES))
+        )
+    return _native.SCHEDULES[schedule]
+
+
+def _check_block(block_size, torch):
+    if type(block_size) is not int or block_size <= 0:
+        raise ValueError("block size must be a positive integer")
+    limit = torch.cuda.get_device_properties(
+        torch.cuda.current_device()
+    ).max_threads_per_block
+    if block_size > limit:
+        raise ValueError(
+            f"block size {block_size} exceeds device limit {limit}"
+        )
+
+
+def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
+               schedule="auto", _validated=None):
+    """Queue one segmented ``sum`` or ``max`` on the current PyTorch stream.
+
+    ``output[s] = reduce(values[offsets[s]:offsets[s + 1]])`` for every
+    segment; an empty segment gives the identity (``+0.0`` / ``-inf``); only
+    the first ``segment_count`` outputs are written.  Reference: ``launch_gpu``
+    (``_segmented_qualification.py:120-172``).
+
+    ``plan`` (a ``SegmentPlan`` for these offsets) skips validation's planner
+    step; ``schedule`` forces ``warp``, ``cta``, ``split`` or ``persistent``.
+    """
+    torch = _runtime._import_torch()
+    if _validated is None:
+        value_count, segment_count = _validate_tensors(values, offsets, output)
+    else:
+        value_count, segment_count = _validated
+    _check_block(block_size, torch)
+    if kind not in _KINDS:
+        raise ValueError("reduction kind must be 'sum' or 'max'")
+    code = _schedule_code(schedule)
+    if segment_count == 0:
+        return None
+
+    from . import _native
+
+    if plan is None and (
+        code in (_native.SCHED_SPLIT, _native.SCHED_PERSISTENT)
+        or (code == _native.SCHED_AUTO
+            and value_count + segment_count >= _PLAN_THRESHOLD)
+    ):
+        host = getattr(_last_host_offsets, "value", None)
+        if host is None or host.numel() != segment_count + 1:
+            host = offsets.detach().cpu()
+        plan = _cached_plan(
+            host, value_count, "reduce", torch.cuda.current_device()
+        )
+    _last_host_offsets.value = None
+    stream = torch.cuda.current_stream()
+    _native.segreduce(
+        _KINDS[kind], values.data_ptr(), offsets.data_ptr(), output.data_ptr(),
+        value_count, segment_count,
+        plan.handle if plan is not None else None,
+        code, block_size, stream.cuda_stream,
+    )
+    for tensor in (values, offsets, output):
+        tensor.record_stream(stream)
+    return None
+
+
+def launch_softmax_gpu(values, offsets, output, *, plan=None, schedule="auto",
+                       _validated=None):
+    """Queue one segmented softmax on the current PyTorch stream.
+
+    ``output[i] = exp(values[i] - m) / d`` over each segment (``m`` its
+    maximum, ``d`` the sum of ``exp(values - m)``); empty segments write
+    nothing.  ``output`` has one element per value and must not alias
+    ``values``.  The reference only defines the semantic form
+    (``test/Dialect/Swage/softmax.mlir:13-31``).
+    """
+    torch = _runtime._import_torch()
+    if _validated is None:
+        value_count, segment_count = _validate_tensors(
+            values, offsets, output, elementwise_output=True
+        )
+    else:
+        value_count, segment_count = _validated
+    code = _schedule_code(schedule)
+    if values.data_ptr() == output.data_ptr() and value_count > 0:
+        raise ValueError("output must not alias values")
+    if segment_count == 0 or value_count == 0:
+        return None
+
+    from . import _native
+
+    _last_host_offsets.value = None
+    stream = torch.cuda.current_stream()
+    _native.segsoftmax(
+        values.data_ptr(), offsets.data_ptr(), output.data_ptr(), value_count,
+        segment_count, plan.handle if plan is not None else None, code,
+        stream.cuda_stream,
+    )
+    for tensor in (values, offsets, output):
+        tensor.record_stream(stream)
+    return None
+
+
+__all__ = [
+    "SegmentPlan", "clear_plan_cache", "launch_gpu", "launch_softmax_gpu",
+    "plan_segments",
+]

@@ -1,0 +1,463 @@
+// extern "C" entry points declared in include/swage_b200.h.
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "swg_launch.h"
+
+struct swg_plan {
+  swg::HostPlan host;
+  swg::DevicePlan dev;
+  std::string description;
+};
+
+namespace {
+
+struct DeviceInfo {
+  bool ready = false;
+  bool configured = false;  // kernel attributes are per device
+  int sm_count = 0;
+};
+
+std::mutex g_lock;
+DeviceInfo g_devices[64];
+
+// Per-launch timing (swg_profile_start / swg_profile_stop).
+struct Profile {
+  bool active = false;
+  std::vector<swg::Probe> probes;
+  size_t used = 0;
+};
+Profile g_profile;
+
+const swg::Probe *next_probe() {
+  std::lock_guard<std::mutex> guard(g_lock);
+  if (!g_profile.active || g_profile.used >= g_profile.probes.size())
+    return nullptr;
+  return &g_profile.probes[g_profile.used++];
+}
+
+void drop_probes() {
+  for (swg::Probe &probe : g_profile.probes) {
+    cudaEventDestroy(probe.start);
+    cudaEventDestroy(probe.stop);
+  }
+  g_profile.probes.clear();
+  g_profile.used = 0;
+  g_profile.active = false;
+}
+
+int cuda_failure(const char *what, cudaError_t error) {
+  swg::set_error("%s failed: %s (%d): %s", what, cudaGetErrorName(error),
+                 (int)error, cudaGetErrorString(error));
+  return SWG_ERR_CUDA;
+}
+
+// Current device + its SM count; configures kernel attributes once.
+int current_device(int *device, int *sm_count) {
+  cudaError_t e = cudaGetDevice(device);
+  if (e != cudaSuccess) return cuda_failure("cudaGetDevice", e);
+  if (*device < 0 || *device >= 64) {
+    swg::set_error("device index %d out of range", *device);
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> guard(g_lock);
+  DeviceInfo &info = g_devices[*device];
+  if (!info.ready) {
+    e = cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount,
+                               *device);
+    if (e != cudaSuccess) return cuda_failure("cudaDeviceGetAttribute", e);
+    info.ready = true;
+  }
+  if (!info.configured) {
+    e = swg::configure_segreduce_kernels();
+    if (e != cudaSuccess) return cuda_failure("cudaFuncSetAttribute", e);
+    info.configured = true;
+  }
+  *sm_count = info.sm_count;
+  return SWG_OK;
+}
+
+template <class T>
+int upload(T **dst, const T *src, size_t count, size_t padded_count,
+           const char *what) {
+  *dst = nullptr;
+  if (padded_count == 0) return SWG_OK;
+  cudaError_t e = cudaMalloc((void **)dst, padded_count * sizeof(T));
+  if (e != cudaSuccess) return cuda_failure(what, e);
+  if (padded_count > count) {
+    e = cudaMemset(*dst + count, 0, (padded_count - count) * sizeof(T));
+    if (e != cudaSuccess) return cuda_failure("cudaMemset", e);
+  }
+  if (count) {
+    e = cudaMemcpy(*dst, src, count * sizeof(T), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return cuda_failure("cudaMemcpy", e);
+  }
+  return SWG_OK;
+}
+
+void release(swg::DevicePlan &dev) {
+  cudaFree(dev.tasks);
+  cudaFree(dev.offsets);
+  cudaFree(dev.splits);
+  cudaFree(dev.partials);
+  cudaFree(dev.control);
+  dev = swg::DevicePlan();
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *swg_last_error(void) { return swg::last_error_text(); }
+
+const char *swg_status_name(int status) {
+  switch (status) {
+    case SWG_OK: return "SWG_OK";
+    case SWG_ERR_INVALID_ARGUMENT: return "SWG_ERR_INVALID_ARGUMENT";
+    case SWG_ERR_INVALID_OFFSETS: return "SWG_ERR_INVALID_OFFSETS";
+    case SWG_ERR_CUDA: return "SWG_ERR_CUDA";
+    case SWG_ERR_PLAN_MISMATCH: return "SWG_ERR_PLAN_MISMATCH";
+    case SWG_ERR_UNSUPPORTED: return "SWG_ERR_UNSUPPORTED";
+    case SWG_ERR_DEVICE_TIMEOUT: return "SWG_ERR_DEVICE_TIMEOUT";
+    default: return "SWG_ERR_UNKNOWN";
+  }
+}
+
+int swg_abi_version(void) { return SWG_ABI_VERSION; }
+
+int swg_vadd_f32(const float *x, const float *y, float *out, int32_t n,
+                 int32_t block_hint, void *stream) {
+  swg::clear_error();
+  if (n < 0 || block_hint <= 0) {
+    swg::set_error("swg_vadd_f32: n must be >= 0 and block_hint > 0");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  if (n == 0) return SWG_OK;
+  if (!x || !y || !out) {
+    swg::set_error("swg_vadd_f32: null pointer");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  cudaError_t e = swg::launch_vadd(x, y, out, n, (cudaStream_t)stream,
+                                   next_probe());
+  if (e != cudaSuccess) return cuda_failure("vector add launch", e);
+  return SWG_OK;
+}
+
+int swg_validate_offsets_i32(const int32_t *host_offsets, int64_t count,
+                             int64_t value_count, int64_t output_count,
+                             int32_t *reason, int64_t *index) {
+  swg::clear_error();
+  return swg::validate_offsets(host_offsets, count, value_count, output_count,
+                               reason, index);
+}
+
+int swg_plan_create(const int32_t *host_offsets, int32_t segment_count,
+                    int32_t value_count, int op, swg_plan **plan_out) {
+  swg::clear_error();
+  if (!plan_out) {
+    swg::set_error("swg_plan_create: plan is null");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  *plan_out = nullptr;
+  if (!host_offsets || segment_count < 0 || value_count < 0 ||
+      (op != SWG_OP_REDUCE && op != SWG_OP_SOFTMAX)) {
+    swg::set_error("swg_plan_create: bad arguments");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  int status = swg::validate_offsets(host_offsets, (int64_t)segment_count + 1,
+                                     value_count, segment_count, nullptr,
+                                     nullptr);
+  if (status != SWG_OK) return status;
+  int device = 0, sm_count = 0;
+  status = current_device(&device, &sm_count);
+  if (status != SWG_OK) return status;
+
+  swg_plan *plan = new (std::nothrow) swg_plan();
+  if (!plan) {
+    swg::set_error("swg_plan_create: out of host memory");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  swg::build_host_plan(host_offsets, segment_count, op, &plan->host);
+  plan->description = swg::describe_host_plan(plan->host);
+  swg::DevicePlan &dev = plan->dev;
+  dev.device = device;
+  dev.sm_count = sm_count;
+  dev.task_count = (int32_t)plan->host.tasks.size();
+  dev.split_count = (int32_t)plan->host.splits.size();
+  dev.partial_slots = plan->host.partial_slots;
+  const size_t noffsets = (size_t)segment_count + 1;
+  const size_t padded = ((noffsets + 3) / 4) * 4 + 4;
+  status = upload(&dev.tasks, plan->host.tasks.data(), plan->host.tasks.size(),
+                  plan->host.tasks.size(), "cudaMalloc(tasks)");
+  if (status == SWG_OK)
+    status = upload(&dev.offsets, host_offsets, noffsets, padded,
+                    "cudaMalloc(offsets)");
+  if (status == SWG_OK)
+    status = upload(&dev.splits, plan->host.splits.data(),
+                    plan->host.splits.size(), plan->host.splits.size(),
+                    "cudaMalloc(splits)");
+  if (status == SWG_OK)
+    status = upload<float>(&dev.partials, nullptr, 0,
+                           (size_t)dev.partial_slots, "cudaMalloc(partials)");
+  if (status == SWG_OK)
+    status = upload<uint32_t>(&dev.control, nullptr, 0, 4,
+                              "cudaMalloc(control)");
+  if (status != SWG_OK) {
+    release(dev);
+    delete plan;
+    return status;
+  }
+  // host vectors are no longer needed once uploaded
+  std::vector<swg::Task>().swap(plan->host.tasks);
+  std::vector<swg::SplitSegment>().swap(plan->host.splits);
+  *plan_out = plan;
+  return SWG_OK;
+}
+
+int swg_plan_host_tasks(const int32_t *host_offsets, int32_t segment_count,
+                        int op, int32_t *tasks, int64_t task_capacity,
+                        int64_t *task_count, char *json, size_t json_capacity) {
+  swg::clear_error();
+  if (!host_offsets || segment_count < 0 ||
+      (op != SWG_OP_REDUCE && op != SWG_OP_SOFTMAX)) {
+    swg::set_error("swg_plan_host_tasks: bad arguments");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  int status = swg::validate_offsets(
+      host_offsets, (int64_t)segment_count + 1,
+      host_offsets[segment_count] < 0 ? 0 : host_offsets[segment_count],
+      segment_count, nullptr, nullptr);
+  if (status != SWG_OK) return status;
+  swg::HostPlan plan;
+  swg::build_host_plan(host_offsets, segment_count, op, &plan);
+  if (task_count) *task_count = (int64_t)plan.tasks.size();
+  if (tasks) {
+    const int64_t n = std::min<int64_t>(task_capacity, plan.tasks.size());
+    static_assert(sizeof(swg::Task) == 16, "task is four 32-bit words");
+    memcpy(tasks, plan.tasks.data(), (size_t)n * sizeof(swg::Task));
+  }
+  if (json) {
+    const std::string text = swg::describe_host_plan(plan);
+    if (json_capacity <= text.size()) {
+      swg::set_error("swg_plan_host_tasks: need %zu bytes", text.size() + 1);
+      return SWG_ERR_INVALID_ARGUMENT;
+    }
+    memcpy(json, text.c_str(), text.size() + 1);
+  }
+  return SWG_OK;
+}
+
+int swg_plan_destroy(swg_plan *plan) {
+  swg::clear_error();
+  if (!plan) return SWG_OK;
+  int previous = -1;
+  const int owner = plan->dev.device;
+  cudaGetDevice(&previous);
+  if (owner >= 0 && previous != owner) cudaSetDevice(owner);
+  release(plan->dev);
+  if (previous >= 0 && previous != owner) cudaSetDevice(previous);
+  delete plan;
+  return SWG_OK;
+}
+
+int swg_plan_describe(const swg_plan *plan, char *json, size_t capacity) {
+  swg::clear_error();
+  if (!plan || !json || capacity <= plan->description.size()) {
+    swg::set_error("swg_plan_describe: need %zu bytes",
+                   plan ? plan->description.size() + 1 : (size_t)0);
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  memcpy(json, plan->description.c_str(), plan->description.size() + 1);
+  return SWG_OK;
+}
+
+int swg_plan_status(swg_plan *plan) {
+  swg::clear_error();
+  if (!plan) {
+    swg::set_error("swg_plan_status: plan is null");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return cuda_failure("cudaDeviceSynchronize", e);
+  uint32_t control[4] = {0, 0, 0, 0};
+  e = cudaMemcpy(control, plan->dev.control, sizeof(control),
+                 cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return cuda_failure("cudaMemcpy", e);
+  if (control[2] != 0) {
+    cudaMemset(plan->dev.control, 0, sizeof(control));
+    swg::set_error("a bounded device-side wait gave up during a launch");
+    return SWG_ERR_DEVICE_TIMEOUT;
+  }
+  return SWG_OK;
+}
+
+int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
+                      float *out, int32_t value_count, int32_t segment_count,
+                      const swg_plan *plan, int schedule, int32_t block_hint,
+                      void *stream) {
+  swg::clear_error();
+  if (kind != SWG_KIND_SUM && kind != SWG_KIND_MAX) {
+    swg::set_error("reduction kind must be SWG_KIND_SUM or SWG_KIND_MAX");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  if (value_count < 0 || segment_count < 0 || block_hint < 0 ||
+      schedule < SWG_SCHED_AUTO || schedule > SWG_SCHED_PERSISTENT) {
+    swg::set_error("swg_segreduce_f32: bad count, block or schedule");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  if (segment_count == 0) return SWG_OK;
+  if (!offsets || !out || (!values && value_count > 0)) {
+    swg::set_error("swg_segreduce_f32: null pointer");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  int device = 0, sm_count = 0;
+  int status = current_device(&device, &sm_count);
+  if (status != SWG_OK) return status;
+  if (plan) {
+    if (plan->host.segment_count != segment_count ||
+        plan->host.value_count > value_count || plan->dev.device != device) {
+      swg::set_error(
+          "plan was built for %d segments / %d values on device %d, launch "
+          "has %d segments / %d values on device %d",
+          plan->host.segment_count, plan->host.value_count, plan->dev.device,
+          segment_count, value_count, device);
+      return SWG_ERR_PLAN_MISMATCH;
+    }
+    if (schedule == SWG_SCHED_AUTO) schedule = plan->host.schedule;
+  } else {
+    if (schedule == SWG_SCHED_SPLIT || schedule == SWG_SCHED_PERSISTENT) {
+      swg::set_error("the split and persistent schedules need a plan");
+      return SWG_ERR_UNSUPPORTED;
+    }
+    if (schedule == SWG_SCHED_AUTO)
+      schedule = (int64_t)value_count >= (int64_t)segment_count * 2048
+                     ? SWG_SCHED_CTA
+                     : SWG_SCHED_WARP;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t e = cudaSuccess;
+  const swg::Probe *probe = next_probe();
+  switch (schedule) {
+    case SWG_SCHED_WARP:
+      e = swg::launch_segreduce_warp(kind, values, offsets, out, segment_count,
+                                     sm_count, s, probe);
+      break;
+    case SWG_SCHED_CTA:
+      e = swg::launch_segreduce_cta(kind, values, offsets, out, segment_count,
+                                    block_hint, sm_count, s, probe);
+      break;
+    case SWG_SCHED_SPLIT:
+      e = swg::launch_segreduce_split(kind, values, out, value_count,
+                                      plan->dev, s, probe);
+      break;
+    default:
+      e = swg::launch_segreduce_persistent(kind, values, out, value_count,
+                                           plan->dev, s, probe);
+      break;
+  }
+  if (e != cudaSuccess) return cuda_failure("segmented reduce launch", e);
+  return SWG_OK;
+}
+
+int swg_segsoftmax_f32(const float *values, const int32_t *offsets, float *out,
+                       int32_t value_count, int32_t segment_count,
+                       const swg_plan *plan, int schedule, void *stream) {
+  swg::clear_error();
+  if (value_count < 0 || segment_count < 0 || schedule < SWG_SCHED_AUTO ||
+      schedule > SWG_SCHED_PERSISTENT) {
+    swg::set_error("swg_segsoftmax_f32: bad count or schedule");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  if (segment_count == 0 || value_count == 0) return SWG_OK;
+  if (!offsets || !out || !values) {
+    swg::set_error("swg_segsoftmax_f32: null pointer");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  if (values == out) {
+    swg::set_error("swg_segsoftmax_f32: out must not alias values");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  int device = 0, sm_count = 0;
+  int status = current_device(&device, &sm_count);
+  if (status != SWG_OK) return status;
+  (void)plan;
+  if (schedule == SWG_SCHED_AUTO)
+    schedule = (int64_t)value_count >= (int64_t)segment_count * 1024
+                   ? SWG_SCHED_CTA
+                   : SWG_SCHED_WARP;
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t e;
+  const swg::Probe *probe = next_probe();
+  if (schedule == SWG_SCHED_WARP)
+    e = swg::launch_segsoftmax_warp(values, offsets, out, segment_count,
+                                    sm_count, s, probe);
+  else
+    e = swg::launch_segsoftmax_cta(values, offsets, out, segment_count,
+                                   sm_count, s, probe);
+  if (e != cudaSuccess) return cuda_failure("segmented softmax launch", e);
+  return SWG_OK;
+}
+
+int swg_shard_offsets(const int32_t *host_offsets, int32_t segment_count,
+                      int32_t shards, int32_t *seg_begin) {
+  swg::clear_error();
+  return swg::shard_offsets(host_offsets, segment_count, shards, seg_begin);
+}
+
+int swg_profile_start(int32_t capacity) {
+  swg::clear_error();
+  if (capacity < 1 || capacity > (1 << 20)) {
+    swg::set_error("swg_profile_start: capacity must be in [1, 2^20]");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> guard(g_lock);
+  drop_probes();
+  g_profile.probes.reserve((size_t)capacity);
+  for (int32_t i = 0; i < capacity; ++i) {
+    swg::Probe probe;
+    cudaError_t e = cudaEventCreate(&probe.start);
+    if (e == cudaSuccess) {
+      e = cudaEventCreate(&probe.stop);
+      if (e != cudaSuccess) cudaEventDestroy(probe.start);
+    }
+    if (e != cudaSuccess) {
+      drop_probes();
+      return cuda_failure("cudaEventCreate", e);
+    }
+    g_profile.probes.push_back(probe);
+  }
+  g_profile.active = true;
+  return SWG_OK;
+}
+
+int swg_profile_stop(float *milliseconds, int32_t capacity, int32_t *count) {
+  swg::clear_error();
+  std::lock_guard<std::mutex> guard(g_lock);
+  if (!g_profile.active) {
+    swg::set_error("swg_profile_stop: profiling was not started");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  const size_t used = g_profile.used;
+  int status = SWG_OK;
+  for (size_t i = 0; i < used; ++i) {
+    cudaError_t e = cudaEventSynchronize(g_profile.probes[i].stop);
+    float ms = 0.0f;
+    if (e == cudaSuccess)
+      e = cudaEventElapsedTime(&ms, g_profile.probes[i].start,
+                               g_profile.probes[i].stop);
+    if (e != cudaSuccess) {
+      status = cuda_failure("cudaEventElapsedTime", e);
+      break;
+    }
+    if (milliseconds && (int32_t)i < capacity) milliseconds[i] = ms;
+  }
+  if (count) *count = (int32_t)used;
+  drop_probes();
+  return status;
+}
+
+}  // extern "C"

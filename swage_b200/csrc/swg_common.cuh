@@ -1,0 +1,193 @@
+// Shared device helpers for the sm_100a kernels: reduction operators with the
+// reference's semantics, warp/CTA reductions with a fixed combine order, and
+// thin wrappers over the PTX this library relies on (NaN-propagating max,
+// mbarrier, bulk async copy).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "swage_b200.h"
+
+namespace swg {
+
+constexpr int kWarp = 32;
+constexpr unsigned kFullMask = 0xffffffffu;
+
+// ---------------------------------------------------------------------------
+// Operators.  Sum: fp32 add from +0.0f.  Max: arith.maximumf of the reference
+// (SegmentedReduction.cpp:173-175, 256-258): NaN if either side is NaN and
+// -0.0 ordered below +0.0; identity -inf.  max.NaN.f32 has exactly these rules.
+// ---------------------------------------------------------------------------
+struct SumOp {
+  static __device__ __forceinline__ float identity() { return 0.0f; }
+  static __device__ __forceinline__ float apply(float a, float b) {
+    return __fadd_rn(a, b);  // never contracted into an fma
+  }
+};
+
+struct MaxOp {
+  static __device__ __forceinline__ float identity() {
+    return -CUDART_INF_F;
+  }
+  static __device__ __forceinline__ float apply(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+  }
+};
+
+template <class Op>
+__device__ __forceinline__ float fold4(float acc, float4 q) {
+  return Op::apply(Op::apply(acc, Op::apply(q.x, q.y)), Op::apply(q.z, q.w));
+}
+
+// Butterfly over the 32 lanes; every lane ends with the same value and the
+// combine order is fixed, so results do not depend on timing.
+template <class Op>
+__device__ __forceinline__ float warp_reduce(float v) {
+#pragma unroll
+  for (int delta = 16; delta > 0; delta >>= 1)
+    v = Op::apply(v, __shfl_xor_sync(kFullMask, v, delta));
+  return v;
+}
+
+// Reduce over a sub-group of `width` adjacent lanes (width a power of two).
+template <class Op>
+__device__ __forceinline__ float group_reduce(float v, int width) {
+  for (int delta = width >> 1; delta > 0; delta >>= 1)
+    v = Op::apply(v, __shfl_xor_sync(kFullMask, v, delta));
+  return v;
+}
+
+// CTA-wide reduce through `scratch` (>= 32 floats of shared memory).  All
+// threads of the CTA must call it; the value is returned to every thread.
+template <class Op>
+__device__ __forceinline__ float cta_reduce(float v, float *scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_reduce<Op>(v);
+  __syncthreads();  // scratch may still be read from a previous call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = lane < nwarps ? scratch[lane] : Op::identity();
+  return warp_reduce<Op>(r);
+}
+
+// ---------------------------------------------------------------------------
+// Global loads.  Values are read exactly once, so they bypass L1 and are
+// marked evict-first in L2.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float4 ld_stream4(const float4 *p) {
+  return __ldcs(p);
+}
+__device__ __forceinline__ float ld_stream(const float *p) { return __ldcs(p); }
+
+// Elements before the first 16-byte boundary at or after p (0..3).
+__device__ __forceinline__ int head_elems(const float *p) {
+  return (int)(((16u - (unsigned)((uintptr_t)p & 15u)) & 15u) >> 2);
+}
+
+// One thread's share of reduce(v[begin, end)) when `nthreads` threads with
+// ranks 0..nthreads-1 stride over the range: scalar head up to the first
+// 16-byte boundary, float4 body (four independent accumulators), scalar tail.
+template <class Op>
+__device__ __forceinline__ float strided_partial(const float *__restrict__ v,
+                                                 int64_t begin, int64_t end,
+                                                 int rank, int nthreads) {
+  float acc = Op::identity();
+  const float *p = v + begin;
+  int64_t len = end - begin;
+  if (len <= 0) return acc;
+  int head = head_elems(p);
+  if (head > len) head = (int)len;
+  if (rank < head) acc = Op::apply(acc, ld_stream(p + rank));
+  const float4 *body = reinterpret_cast<const float4 *>(p + head);
+  int64_t nvec = (len - head) >> 2;
+  float a1 = Op::identity(), a2 = Op::identity(), a3 = Op::identity();
+  int64_t i = rank;
+  for (; i + 3 * (int64_t)nthreads < nvec; i += 4 * (int64_t)nthreads) {
+    float4 q0 = ld_stream4(body + i);
+    float4 q1 = ld_stream4(body + i + nthreads);
+    float4 q2 = ld_stream4(body + i + 2 * (int64_t)nthreads);
+    float4 q3 = ld_stream4(body + i + 3 * (int64_t)nthreads);
+    acc = fold4<Op>(acc, q0);
+    a1 = fold4<Op>(a1, q1);
+    a2 = fold4<Op>(a2, q2);
+    a3 = fold4<Op>(a3, q3);
+  }
+  for (; i < nvec; i += nthreads) acc = fold4<Op>(acc, ld_stream4(body + i));
+  acc = Op::apply(Op::apply(acc, a1), Op::apply(a2, a3));
+  int64_t tail = head + (nvec << 2);
+  int rem = (int)(len - tail);
+  if (rank < rem) acc = Op::apply(acc, ld_stream(p + tail + rank));
+  return acc;
+}
+
+// ---------------------------------------------------------------------------
+// mbarrier + bulk async copy (TMA, untiled form).  Every wait is bounded: after
+// kSpinLimit failed probes the caller gets `false` and is expected to raise the
+// error flag and leave.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kSpinLimit = 1u << 22;  // probes; each probe may suspend
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(count)
+               : "memory");
+}
+
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar,
+                                                      uint32_t bytes) {
+  asm volatile(
+      "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "r"(bytes)
+      : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Bounded wait; false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+// global -> shared bulk copy, completion counted in bytes on `bar`.  Both
+// addresses 16-byte aligned, `bytes` a multiple of 16.  No multicast.
+__device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem,
+                                         uint32_t bytes, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
+      "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+}  // namespace swg

@@ -1,0 +1,73 @@
+// Internal launch interface between the C ABI (swg_api.cu) and the kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "swg_plan.h"
+
+namespace swg {
+
+// Device-resident part of a plan; every pointer is owned by the plan.
+struct DevicePlan {
+  int device = -1;
+  int sm_count = 0;
+  Task *tasks = nullptr;
+  int32_t task_count = 0;
+  int32_t *offsets = nullptr;      // aligned, padded copy of the CSR offsets
+  SplitSegment *splits = nullptr;
+  int32_t split_count = 0;
+  float *partials = nullptr;       // one float per partial slot
+  int32_t partial_slots = 0;
+  uint32_t *control = nullptr;     // [0] ticket, [1] finished CTAs, [2] error
+};
+
+// Optional pair of events recorded around the dominant kernel of a call.
+struct Probe {
+  cudaEvent_t start;
+  cudaEvent_t stop;
+};
+
+inline void probe_begin(const Probe *probe, cudaStream_t stream) {
+  if (probe) cudaEventRecord(probe->start, stream);
+}
+inline void probe_end(const Probe *probe, cudaStream_t stream) {
+  if (probe) cudaEventRecord(probe->stop, stream);
+}
+
+cudaError_t launch_vadd(const float *x, const float *y, float *out, int32_t n,
+                        cudaStream_t stream, const Probe *probe);
+
+cudaError_t launch_segreduce_warp(int kind, const float *values,
+                                  const int32_t *offsets, float *out,
+                                  int32_t segment_count, int sm_count,
+                                  cudaStream_t stream, const Probe *probe);
+cudaError_t launch_segreduce_cta(int kind, const float *values,
+                                 const int32_t *offsets, float *out,
+                                 int32_t segment_count, int32_t block,
+                                 int sm_count, cudaStream_t stream,
+                                 const Probe *probe);
+// One tile task per CTA + combine pass.
+cudaError_t launch_segreduce_split(int kind, const float *values, float *out,
+                                   int32_t value_count, const DevicePlan &plan,
+                                   cudaStream_t stream, const Probe *probe);
+// Persistent CTAs, bulk-copy ring, ticket counter + combine pass.
+cudaError_t launch_segreduce_persistent(int kind, const float *values,
+                                        float *out, int32_t value_count,
+                                        const DevicePlan &plan,
+                                        cudaStream_t stream,
+                                        const Probe *probe);
+cudaError_t configure_segreduce_kernels();
+
+cudaError_t launch_segsoftmax_cta(const float *values, const int32_t *offsets,
+                                  float *out, int32_t segment_count,
+                                  int sm_count, cudaStream_t stream,
+                                  const Probe *probe);
+cudaError_t launch_segsoftmax_warp(const float *values, const int32_t *offsets,
+                                   float *out, int32_t segment_count,
+                                   int sm_count, cudaStream_t stream,
+                                   const Probe *probe);
+
+const char *last_error_text();
+
+}  // namespace swg

@@ -1,0 +1,245 @@
+// Host planner: offsets validation, segment-length histogram, packing of
+// segments into tile tasks, schedule choice and multi-GPU sharding.  Plain
+// C++ (no CUDA) so it can be unit-tested without a device.
+//
+// Vocabulary follows the reference's docs/concepts/segments-tiles-tasks.md
+// (:32-51): a segment is the logical unit, a tile the fixed-size physical
+// unit, a task the schedulable bridge ("several short segments packed into
+// one tile", "one chunk of a long segment", "a reduction merge").
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "swg_plan.h"
+
+namespace swg {
+
+namespace {
+thread_local char g_error[512] = "";
+}
+
+void set_error(const char *format, ...) {
+  va_list args;
+  va_start(args, format);
+  vsnprintf(g_error, sizeof(g_error), format, args);
+  va_end(args);
+}
+
+void clear_error() { g_error[0] = '\0'; }
+
+const char *last_error_text() { return g_error; }
+
+// Same checks, same order as _validate_offsets
+// (python/swage/_segmented_qualification.py:30-55).  The reference walks a
+// Python list; this is one pass over the int32 array.
+int validate_offsets(const int32_t *offsets, int64_t count, int64_t value_count,
+                     int64_t output_count, int32_t *reason, int64_t *index) {
+  int32_t why = SWG_OFFSETS_OK;
+  int64_t where = -1;
+  const int64_t limit = int64_t(1) << 31;
+  if (offsets == nullptr || count < 1) {
+    why = SWG_OFFSETS_EMPTY;
+  } else if (value_count < 0 || value_count >= limit || count - 1 >= limit) {
+    why = SWG_OFFSETS_COUNT_RANGE;
+  } else if (output_count < count - 1) {
+    why = SWG_OFFSETS_OUTPUT_SMALL;
+  } else if (offsets[0] != 0) {
+    why = SWG_OFFSETS_NONZERO_START;
+    where = 0;
+  } else {
+    int32_t previous = 0;
+    for (int64_t i = 0; i < count; ++i) {
+      int32_t offset = offsets[i];
+      if (offset < 0) {
+        why = SWG_OFFSETS_NEGATIVE;
+        where = i;
+        break;
+      }
+      if (offset < previous) {
+        why = SWG_OFFSETS_DECREASING;
+        where = i;
+        break;
+      }
+      previous = offset;
+    }
+    if (why == SWG_OFFSETS_OK && offsets[count - 1] > value_count) {
+      why = SWG_OFFSETS_EXCEEDS_VALUES;
+      where = count - 1;
+    }
+  }
+  if (reason) *reason = why;
+  if (index) *index = where;
+  if (why == SWG_OFFSETS_OK) return SWG_OK;
+  set_error("offsets rejected: reason %d at index %lld", (int)why,
+            (long long)where);
+  return SWG_ERR_INVALID_OFFSETS;
+}
+
+static inline int length_bin(int64_t length) {
+  if (length <= 0) return 0;
+  int bin = 1;
+  while ((int64_t(1) << bin) <= length && bin < kHistogramBins - 1) ++bin;
+  return bin;  // 2^(bin-1) <= length < 2^bin
+}
+
+namespace {
+
+struct Packer {
+  HostPlan *plan;
+  int32_t seg_begin = 0, nseg = 0, vbegin = 0, vcount = 0;
+
+  void flush() {
+    if (nseg == 0) return;
+    Task task;
+    task.seg = seg_begin;
+    task.count = nseg;
+    task.vbegin = vbegin;
+    task.vcount_kind = (kTaskPack << 28) | (uint32_t)vcount;
+    plan->tasks.push_back(task);
+    plan->pack_tasks++;
+    nseg = 0;
+    vcount = 0;
+  }
+
+  void add(int32_t seg, int32_t start, int32_t length) {
+    if (nseg > 0 &&
+        (vcount + length > kTileValues || nseg >= kTileMaxSegments))
+      flush();
+    if (nseg == 0) {
+      seg_begin = seg;
+      vbegin = start;
+    }
+    nseg++;
+    vcount += length;
+  }
+};
+
+void plan_reduce(const int32_t *offsets, int32_t segment_count,
+                 HostPlan *plan) {
+  Packer packer{plan};
+  plan->tasks.reserve((size_t)(offsets[segment_count] / kTileValues) + 64);
+  for (int32_t seg = 0; seg < segment_count; ++seg) {
+    const int32_t start = offsets[seg];
+    const int32_t length = offsets[seg + 1] - start;
+    if (length <= kLongSegment) {
+      packer.add(seg, start, length);
+      continue;
+    }
+    packer.flush();
+    // Chunk boundaries sit on multiples of four elements so that, for a
+    // 16-byte aligned values pointer, every chunk but the first starts on a
+    // 16-byte boundary.
+    const int64_t end = (int64_t)start + length;
+    const int64_t origin = start & ~3;
+    const int64_t nchunks = (end - origin + kTileValues - 1) / kTileValues;
+    int32_t slot = -1;
+    if (nchunks > 1) {
+      SplitSegment split;
+      split.seg = seg;
+      split.slot_begin = plan->partial_slots;
+      split.slot_count = (int32_t)nchunks;
+      split.pad = 0;
+      plan->splits.push_back(split);
+      slot = plan->partial_slots;
+      plan->partial_slots += (int32_t)nchunks;
+    }
+    for (int64_t chunk = 0; chunk < nchunks; ++chunk) {
+      const int64_t lo = std::max<int64_t>(start, origin + chunk * kTileValues);
+      const int64_t hi =
+          std::min<int64_t>(end, origin + (chunk + 1) * kTileValues);
+      Task task;
+      task.seg = seg;
+      task.count = nchunks > 1 ? slot + (int32_t)chunk : -1;
+      task.vbegin = (int32_t)lo;
+      task.vcount_kind = (kTaskChunk << 28) | (uint32_t)(hi - lo);
+      plan->tasks.push_back(task);
+      plan->chunk_tasks++;
+    }
+  }
+  packer.flush();
+}
+
+}  // namespace
+
+void build_host_plan(const int32_t *offsets, int32_t segment_count, int op,
+                     HostPlan *plan) {
+  plan->segment_count = segment_count;
+  plan->value_count = offsets[segment_count];
+  plan->op = op;
+  for (int32_t seg = 0; seg < segment_count; ++seg) {
+    const int64_t length = (int64_t)offsets[seg + 1] - offsets[seg];
+    const int bin = length_bin(length);
+    plan->histogram[bin]++;
+    plan->elements_in_bin[bin] += length;
+    plan->max_length = std::max(plan->max_length, length);
+  }
+  plan->mean_length =
+      segment_count > 0 ? (double)plan->value_count / segment_count : 0.0;
+  plan_reduce(offsets, segment_count, plan);
+  // Tile tasks drawn by persistent CTAs are never worse than a static
+  // mapping once there is more than a handful of them; below that a launch
+  // is latency-bound whatever the mapping, and one CTA per task is enough.
+  plan->schedule =
+      plan->tasks.size() <= 148 ? SWG_SCHED_SPLIT : SWG_SCHED_PERSISTENT;
+}
+
+std::string describe_host_plan(const HostPlan &plan) {
+  std::string text = "{";
+  char buffer[256];
+  snprintf(buffer, sizeof(buffer),
+           "\"segments\": %d, \"values\": %d, \"op\": %d, \"schedule\": %d, "
+           "\"mean_length\": %.3f, \"max_length\": %lld, \"tasks\": %zu, "
+           "\"pack_tasks\": %lld, \"chunk_tasks\": %lld, "
+           "\"split_segments\": %zu, \"partial_slots\": %d, "
+           "\"tile_values\": %d, \"long_segment\": %d, ",
+           plan.segment_count, plan.value_count, plan.op, plan.schedule,
+           plan.mean_length, (long long)plan.max_length, plan.tasks.size(),
+           (long long)plan.pack_tasks, (long long)plan.chunk_tasks,
+           plan.splits.size(), plan.partial_slots, kTileValues, kLongSegment);
+  text += buffer;
+  text += "\"histogram\": [";
+  for (int bin = 0; bin < kHistogramBins; ++bin) {
+    snprintf(buffer, sizeof(buffer), "%s%lld", bin ? ", " : "",
+             (long long)plan.histogram[bin]);
+    text += buffer;
+  }
+  text += "], \"elements_in_bin\": [";
+  for (int bin = 0; bin < kHistogramBins; ++bin) {
+    snprintf(buffer, sizeof(buffer), "%s%lld", bin ? ", " : "",
+             (long long)plan.elements_in_bin[bin]);
+    text += buffer;
+  }
+  text += "]}";
+  return text;
+}
+
+// Element-balanced contiguous segment ranges: the cut before shard g is the
+// segment boundary closest to g * total / shards.
+int shard_offsets(const int32_t *offsets, int32_t segment_count, int32_t shards,
+                  int32_t *seg_begin) {
+  if (offsets == nullptr || seg_begin == nullptr || shards < 1 ||
+      segment_count < 0) {
+    set_error("shard_offsets: bad arguments");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  const int64_t total = offsets[segment_count];
+  seg_begin[0] = 0;
+  for (int32_t g = 1; g < shards; ++g) {
+    const int64_t ideal = total * g / shards;
+    // first boundary index b in [0, segment_count] with offsets[b] >= ideal
+    const int32_t *at =
+        std::lower_bound(offsets, offsets + segment_count + 1, (int32_t)ideal);
+    int32_t boundary = (int32_t)(at - offsets);
+    if (boundary > segment_count) boundary = segment_count;
+    if (boundary > 0 &&
+        ideal - offsets[boundary - 1] < (int64_t)offsets[boundary] - ideal)
+      boundary -= 1;
+    if (boundary < seg_begin[g - 1]) boundary = seg_begin[g - 1];
+    seg_begin[g] = boundary;
+  }
+  seg_begin[shards] = segment_count;
+  return SWG_OK;
+}
+
+}  // namespace swg

@@ -1,0 +1,133 @@
+"""Segmented softmax on the GPU against the fp64 oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import workloads
+from gpu_util import launch_softmax_gpu, offsets_from_lengths
+
+pytestmark = pytest.mark.gpu
+
+SCHEDULES = ["auto", "warp", "cta"]
+
+
+def check_softmax(values, offsets, schedule, poison=True):
+    """|err| <= 1e-5 * sqrt(len) * max|x| per element against fp64, and a
+    much tighter relative bound where the probability is not tiny."""
+    values = np.asarray(values, dtype=np.float32)
+    offsets = np.asarray(offsets, dtype=np.int32)
+    device_values = torch.as_tensor(values).cuda()
+    output = torch.full((values.size,), float("nan"), device="cuda")
+    launch_softmax_gpu(device_values, torch.as_tensor(offsets).cuda(), output,
+                       schedule=schedule)
+    torch.cuda.synchronize()
+    result = output.cpu().numpy().astype(np.float64)
+    exact = oracle.segsoftmax_f64(values, offsets)
+    inside = ~np.isnan(exact)
+    assert np.isnan(result[~inside]).all(), "wrote outside every segment"
+    lengths = np.diff(offsets)
+    per_segment = 1e-5 * np.sqrt(lengths) * oracle.segabsmax_f64(values,
+                                                                 offsets)
+    bound = np.repeat(per_segment, lengths)
+    covered = slice(0, int(offsets[-1]))
+    error = np.abs(result[covered] - exact[covered])
+    assert np.all(error <= bound + 1e-12)
+    assert np.all(error <= 4e-6 * exact[covered] + 1e-10)
+    return result
+
+
+@pytest.mark.parametrize("schedule", SCHEDULES)
+def test_small_cases(schedule):
+    rng = np.random.default_rng(4)
+    for lengths in ([1], [0], [0, 2, 0, 0, 3], [33, 33, 33, 33],
+                    [1, 257, 2, 3837], [4097], [129, 0, 128, 127, 1]):
+        offsets = offsets_from_lengths(lengths)
+        values = (2 * rng.standard_normal(offsets[-1] + 2)).astype(np.float32)
+        result = check_softmax(values, offsets, schedule)
+        for a, b in zip(offsets[:-1], offsets[1:]):
+            if b > a:
+                assert abs(result[a:b].sum() - 1) < 1e-5
+
+
+@pytest.mark.parametrize("schedule", SCHEDULES)
+def test_large_magnitudes_do_not_overflow(schedule):
+    values = np.array([1000.0, 999.0, -1000.0, 88.0, 89.0, -5000.0, -5001.0],
+                      dtype=np.float32)
+    check_softmax(values, np.array([0, 3, 5, 7], dtype=np.int32), schedule)
+
+
+@pytest.mark.parametrize("schedule", SCHEDULES)
+@pytest.mark.parametrize("shift", [0, 1, 3])
+def test_misaligned_pointers(schedule, shift):
+    rng = np.random.default_rng(8)
+    lengths = list(rng.integers(0, 400, size=100)) + [70000, 2, 5000]
+    offsets = offsets_from_lengths(lengths)
+    host = (2 * rng.standard_normal(offsets[-1] + 8)).astype(np.float32)
+    base = torch.as_tensor(host).cuda()
+    values = base[shift:shift + int(offsets[-1])]
+    out_base = torch.full((int(offsets[-1]) + 8,), float("nan"),
+                          device="cuda")
+    output = out_base[(shift * 2) % 4:(shift * 2) % 4 + int(offsets[-1])]
+    launch_softmax_gpu(values, torch.as_tensor(offsets).cuda(), output,
+                       schedule=schedule)
+    torch.cuda.synchronize()
+    exact = oracle.segsoftmax_f64(host[shift:shift + int(offsets[-1])],
+                                  offsets)
+    assert np.allclose(output.cpu().numpy(), exact, rtol=4e-6, atol=1e-10)
+
+
+def test_nan_and_empty_semantics():
+    values = torch.tensor([1.0, float("nan"), 3.0, 4.0, 5.0], device="cuda")
+    offsets = torch.tensor([0, 3, 3, 5], dtype=torch.int32, device="cuda")
+    output = torch.zeros(5, device="cuda")
+    launch_softmax_gpu(values, offsets, output)
+    torch.cuda.synchronize()
+    host = output.cpu().numpy()
+    assert np.isnan(host[:3]).all()
+    assert np.allclose(host[3:], [1 / (1 + np.e), np.e / (1 + np.e)],
+                       rtol=1e-6)
+
+
+def test_rejects_aliasing_and_short_output():
+    values = torch.randn(8, device="cuda")
+    offsets = torch.tensor([0, 8], dtype=torch.int32, device="cuda")
+    with pytest.raises(ValueError, match="must not alias"):
+        launch_softmax_gpu(values, offsets, values)
+    with pytest.raises(ValueError, match="output has 4 elements"):
+        launch_softmax_gpu(values, offsets, torch.empty(4, device="cuda"))
+
+
+@pytest.mark.parametrize("schedule", SCHEDULES)
+def test_config_softmax_reduced(schedule):
+    """The softmax configuration's length mix at 1/64 of its segment count."""
+    offsets = workloads.c4_offsets(segments=4096)
+    values = workloads.normal_values(int(offsets[-1]), "cuda",
+                                     workloads.SEEDS["c4"], scale=2.0)
+    check_softmax(values.cpu().numpy(), offsets, schedule)
+
+
+def test_full_size_softmax_properties():
+    """262144 segments, about 1.13e9 values: every segment sums to one, the
+    output is a valid probability everywhere, and a sample of segments
+    matches the fp64 oracle."""
+    offsets = workloads.c4_offsets()
+    count = int(offsets[-1])
+    values = workloads.normal_values(count, "cuda", workloads.SEEDS["c4"],
+                                     scale=2.0)
+    device_offsets = torch.as_tensor(offsets).cuda()
+    output = torch.empty(count, device="cuda")
+    launch_softmax_gpu(values, device_offsets, output)
+    torch.cuda.synchronize()
+    assert bool(((output >= 0) & (output <= 1)).all())
+    lengths = torch.as_tensor(np.diff(offsets).astype(np.int64)).cuda()
+    sums = torch.segment_reduce(output.double(), "sum", lengths=lengths)
+    assert float((sums - 1).abs().max()) < 1e-4
+    rng = np.random.default_rng(1)
+    for seg in rng.choice(len(offsets) - 1, size=64, replace=False):
+        a, b = int(offsets[seg]), int(offsets[seg + 1])
+        piece = values[a:b].cpu().numpy()
+        exact = oracle.segsoftmax_f64(piece, np.array([0, b - a], np.int32))
+        got = output[a:b].cpu().numpy()
+        assert np.allclose(got, exact, rtol=4e-6, atol=1e-10)
