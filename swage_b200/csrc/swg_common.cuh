@@ -127,10 +127,16 @@ __device__ __forceinline__ float strided_partial(const float *__restrict__ v,
 
 // ---------------------------------------------------------------------------
 // mbarrier + bulk async copy (TMA, untiled form).  Every wait is bounded: after
-// kSpinLimit failed probes the caller gets `false` and is expected to raise the
+// kWaitLimitNs without success the caller gets `false` and is expected to raise the
 // error flag and leave.
 // ---------------------------------------------------------------------------
-constexpr uint32_t kSpinLimit = 1u << 22;  // probes; each probe may suspend
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // two seconds
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -172,11 +178,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   return done != 0;
 }
 
-// Bounded wait; false = gave up.
+// Bounded wait; false = gave up after kWaitLimitNs.  The clock is only read
+// once the first few probes have failed, so the common case costs one probe.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+  for (int probe = 0; probe < 16; ++probe)
     if (mbar_try_wait(bar, parity)) return true;
-  return false;
+  const uint64_t deadline = global_timer_ns() + kWaitLimitNs;
+  for (;;) {
+    for (int probe = 0; probe < 32; ++probe)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() > deadline) return false;
+  }
 }
 
 // global -> shared bulk copy, completion counted in bytes on `bar`.  Both

@@ -186,7 +186,7 @@ void build_host_plan(const int32_t *offsets, int32_t segment_count, int op,
 
 std::string describe_host_plan(const HostPlan &plan) {
   std::string text = "{";
-  char buffer[256];
+  char buffer[1024];
   snprintf(buffer, sizeof(buffer),
            "\"segments\": %d, \"values\": %d, \"op\": %d, \"schedule\": %d, "
            "\"mean_length\": %.3f, \"max_length\": %lld, \"tasks\": %zu, "

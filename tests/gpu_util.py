@@ -31,8 +31,10 @@ def bits_equal_or_both_nan(actual, expected):
 def run_reduce(values, offsets, kind, schedule="auto", plan=None, extra=3,
                block_size=128):
     """Launch on the GPU; return the first S outputs and the untouched tail."""
-    device_values = torch.as_tensor(values).cuda()
-    device_offsets = torch.as_tensor(offsets).cuda()
+    device_values = torch.as_tensor(
+        np.asarray(values, dtype=np.float32)).cuda()
+    device_offsets = torch.as_tensor(
+        np.asarray(offsets, dtype=np.int32)).cuda()
     segments = len(offsets) - 1
     output = torch.full((segments + extra,), float("nan"), device="cuda")
     launch_gpu(device_values, device_offsets, output, kind, block_size,

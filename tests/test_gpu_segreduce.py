@@ -193,7 +193,10 @@ def test_plan_description_reports_histogram_and_schedule():
     plan = make_plan(offsets)
     info = plan.describe()
     assert info["segments"] == 1 << 16 and info["values"] == 1 << 22
-    assert info["split_segments"] >= 4 and info["max_length"] == 1 << 19
+    lengths = np.diff(offsets)
+    assert info["max_length"] == int(lengths.max())
+    assert info["split_segments"] == int((lengths > info["tile_values"]).sum())
+    assert sum(info["histogram"]) == 1 << 16
     assert info["schedule"] in (3, 4)
     plan.check()
     plan.close()
@@ -286,10 +289,22 @@ def full_size_check(offsets, values, kind):
         exact = oracle.segsum_f64(host_values, offsets, threads=threads)
         bound = oracle.sum_tolerance(host_values, offsets)
         assert np.all(np.abs(result - exact) <= bound)
-        # the sequential fp32 oracle meets the same bound (reported alongside)
+        # The reference's strictly sequential fp32 order is reported beside
+        # it, not held to the bound: over 2**23 elements its rounding error
+        # grows past 1e-5*sqrt(len)*max|x| while the GPU's tree order stays
+        # well inside.
         sequential = oracle.segreduce_f32(host_values, offsets, "sum",
                                           threads=threads)
-        assert np.all(np.abs(sequential - exact) <= bound)
+        nonempty = bound > 0
+        gpu_ratio = float(np.max(np.abs(result - exact)[nonempty]
+                                 / bound[nonempty]))
+        cpu_ratio = float(np.max(np.abs(sequential - exact)[nonempty]
+                                 / bound[nonempty]))
+        print(f"worst |err|/bound: gpu {gpu_ratio:.3g}, "
+              f"sequential fp32 oracle {cpu_ratio:.3g}")
+        assert gpu_ratio <= 1.0 and np.isfinite(cpu_ratio)
+        short = nonempty & (np.diff(offsets) <= 4096)
+        assert np.all(np.abs(sequential - exact)[short] <= bound[short])
         # linearity: scaling by two is exact in fp32, so sums double exactly
         doubled = torch.empty(segments, device="cuda")
         launch_gpu(values * 2, device_offsets, doubled, "sum", plan=plan)
