@@ -139,6 +139,31 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
                       const swg_plan *plan, int schedule, int32_t block_hint,
                       void *stream);
 
+/* Same result as swg_segreduce_f32 with a plan and SWG_SCHED_SPLIT, for
+ * callers that must not allocate device memory: code running inside a
+ * framework whose memory pool already owns the GPU's memory, a serving loop
+ * that cannot afford cudaMalloc's implicit synchronisation, or a client whose
+ * allocations are capped by its host process.  This entry point has no
+ * counterpart in the reference.
+ *
+ * The planner runs on the host from `host_offsets` (segment_count + 1 entries,
+ * validated here) and the task list, an aligned copy of the offsets and the
+ * partials of split segments are placed in a fixed array that is part of the
+ * library image on every GPU (about 1.8 MB, held until the process exits).
+ * No cudaMalloc, cudaFree or other allocating call is made.
+ * Limits: at most 262144 segments, 32768 tile tasks (about 2.6e8 values),
+ * 32768 partials and 8192 split segments; larger inputs are rejected with
+ * SWG_ERR_UNSUPPORTED and a message naming the limit.
+ * The first call on a device looks up the array's device address; make that
+ * first call outside any stream capture.  All calls share the array, which
+ * keeps the last call's contents (the parts that must start at zero are
+ * cleared on `stream` each time), so two calls that can overlap on the GPU --
+ * different streams, or different host threads -- race: serialise them. */
+int swg_segreduce_f32_noalloc(int kind, const float *values,
+                              const int32_t *host_offsets, float *out,
+                              int32_t value_count, int32_t segment_count,
+                              void *stream);
+
 /* out[i] = exp(values[i] - m_s) / d_s over each segment s, with m_s the
  * segment maximum and d_s the sum of exp(values - m_s); empty segments write
  * nothing; positions outside every segment are not touched.  `out` must not

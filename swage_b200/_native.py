@@ -39,7 +39,7 @@ EXPORTS = (
     "swg_plan_describe", "swg_plan_status", "swg_plan_host_tasks",
     "swg_segreduce_f32",
     "swg_segsoftmax_f32", "swg_shard_offsets", "swg_profile_start",
-    "swg_profile_stop",
+    "swg_profile_stop", "swg_segreduce_f32_noalloc",
 )
 
 _lock = threading.Lock()
@@ -82,6 +82,9 @@ def _declare(lib):
         ptr, ptr, ptr, c_i32, c_i32, ptr, c_int, ptr]
     lib.swg_shard_offsets.restype = c_int
     lib.swg_shard_offsets.argtypes = [ptr, c_i32, c_i32, ptr]
+    lib.swg_segreduce_f32_noalloc.restype = c_int
+    lib.swg_segreduce_f32_noalloc.argtypes = [
+        c_int, ptr, ptr, ptr, c_i32, c_i32, ptr]
     lib.swg_profile_start.restype = c_int
     lib.swg_profile_start.argtypes = [c_i32]
     lib.swg_profile_stop.restype = c_int
@@ -126,6 +129,24 @@ def segreduce(kind, values_ptr, offsets_ptr, out_ptr, value_count,
             kind, values_ptr, offsets_ptr, out_ptr, value_count,
             segment_count, plan_handle, schedule, block, stream),
         "swg_segreduce_f32",
+    )
+
+
+def segreduce_noalloc(kind, values_ptr, host_offsets_ptr, out_ptr, value_count,
+                      segment_count, stream):
+    """Split-schedule reduce that allocates no device memory.
+
+    For callers that cannot call cudaMalloc (their framework's pool owns the
+    memory, or an allocation's implicit synchronisation is not acceptable).
+    The offsets pointer is a HOST pointer; the plan is built per call and its
+    data lives in a fixed array inside the library.  Calls must not overlap on
+    the GPU; inputs beyond the array's limits raise ``RuntimeError``.
+    """
+    check(
+        library().swg_segreduce_f32_noalloc(
+            kind, values_ptr, host_offsets_ptr, out_ptr, value_count,
+            segment_count, stream),
+        "swg_segreduce_f32_noalloc",
     )
 
 

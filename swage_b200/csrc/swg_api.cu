@@ -363,6 +363,58 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
   return SWG_OK;
 }
 
+int swg_segreduce_f32_noalloc(int kind, const float *values,
+                              const int32_t *host_offsets, float *out,
+                              int32_t value_count, int32_t segment_count,
+                              void *stream) {
+  swg::clear_error();
+  if (kind != SWG_KIND_SUM && kind != SWG_KIND_MAX) {
+    swg::set_error("reduction kind must be SWG_KIND_SUM or SWG_KIND_MAX");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  if (value_count < 0 || segment_count < 0 || !host_offsets) {
+    swg::set_error("swg_segreduce_f32_noalloc: bad count or null offsets");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  if (segment_count > swg::kStaticMaxSegments) {
+    swg::set_error(
+        "swg_segreduce_f32_noalloc: %d segments exceed the fixed scratch "
+        "(at most %d); use swg_plan_create + swg_segreduce_f32",
+        segment_count, swg::kStaticMaxSegments);
+    return SWG_ERR_UNSUPPORTED;
+  }
+  int status = swg::validate_offsets(host_offsets, (int64_t)segment_count + 1,
+                                     value_count, segment_count, nullptr,
+                                     nullptr);
+  if (status != SWG_OK) return status;
+  if (segment_count == 0) return SWG_OK;
+  if (!out || (!values && value_count > 0)) {
+    swg::set_error("swg_segreduce_f32_noalloc: null pointer");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  swg::HostPlan plan;
+  swg::build_host_plan(host_offsets, segment_count, SWG_OP_REDUCE, &plan);
+  if ((int64_t)plan.tasks.size() > swg::kStaticMaxTasks ||
+      plan.partial_slots > swg::kStaticMaxSlots ||
+      (int64_t)plan.splits.size() > swg::kStaticMaxSplits) {
+    swg::set_error(
+        "swg_segreduce_f32_noalloc: input needs %zu tile tasks / %d partials "
+        "/ %zu split segments, the fixed scratch holds %d / %d / %d; use "
+        "swg_plan_create + swg_segreduce_f32",
+        plan.tasks.size(), plan.partial_slots, plan.splits.size(),
+        swg::kStaticMaxTasks, swg::kStaticMaxSlots, swg::kStaticMaxSplits);
+    return SWG_ERR_UNSUPPORTED;
+  }
+  int device = 0, sm_count = 0;
+  status = current_device(&device, &sm_count);
+  if (status != SWG_OK) return status;
+  cudaError_t e = swg::launch_segreduce_static(
+      kind, values, out, value_count, host_offsets, segment_count, plan,
+      device, sm_count, (cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_failure("allocation-free reduce", e);
+  return SWG_OK;
+}
+
 int swg_segsoftmax_f32(const float *values, const int32_t *offsets, float *out,
                        int32_t value_count, int32_t segment_count,
                        const swg_plan *plan, int schedule, void *stream) {

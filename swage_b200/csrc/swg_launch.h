@@ -59,6 +59,19 @@ cudaError_t launch_segreduce_persistent(int kind, const float *values,
                                         const Probe *probe);
 cudaError_t configure_segreduce_kernels();
 
+// Allocation-free variant: the split schedule run out of a fixed-size
+// file-scope device array.  Limits of that array:
+constexpr int kStaticMaxSegments = 1 << 18;
+constexpr int kStaticMaxTasks = 1 << 15;
+constexpr int kStaticMaxSlots = 1 << 15;
+constexpr int kStaticMaxSplits = 1 << 13;
+cudaError_t launch_segreduce_static(int kind, const float *values, float *out,
+                                    int32_t value_count,
+                                    const int32_t *host_offsets,
+                                    int32_t segment_count,
+                                    const HostPlan &plan, int device,
+                                    int sm_count, cudaStream_t stream);
+
 cudaError_t launch_segsoftmax_cta(const float *values, const int32_t *offsets,
                                   float *out, int32_t segment_count,
                                   int sm_count, cudaStream_t stream,

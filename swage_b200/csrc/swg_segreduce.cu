@@ -17,6 +17,8 @@
 // All of them are HBM-bound: 4 bytes per value + 4 per offset + 4 per output.
 // No floating-point atomics anywhere: every result is produced by a fixed
 // combine tree, so launches are bit-reproducible.
+#include <mutex>
+
 #include "swg_common.cuh"
 #include "swg_launch.h"
 
@@ -543,6 +545,110 @@ cudaError_t launch_segreduce_persistent(int kind, const float *values,
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   return launch_combine(kind, plan, out, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the split schedule.
+//
+// Everything the split schedule normally keeps in plan-owned cudaMalloc memory
+// (task list, aligned offsets copy, split-segment list, partials, control
+// words) lives instead in one file-scope device array of fixed size, so the
+// call path contains no cudaMalloc / cudaFree.  Every GPU that loads this
+// library holds the array (about 1.8 MB) until the process exits.
+//
+// The array's name is only a host-side handle: the address kernels can use is
+// obtained once per device with cudaGetSymbolAddress, with that device
+// current, the first time the entry point runs there.
+// ---------------------------------------------------------------------------
+constexpr size_t round256(size_t bytes) { return (bytes + 255) / 256 * 256; }
+constexpr size_t kStaticOffsetBytes =
+    round256(((size_t)kStaticMaxSegments + 8) * 4);
+constexpr size_t kStaticTaskBytes = (size_t)kStaticMaxTasks * sizeof(Task);
+constexpr size_t kStaticSplitBytes =
+    (size_t)kStaticMaxSplits * sizeof(SplitSegment);
+constexpr size_t kStaticPartialBytes = (size_t)kStaticMaxSlots * 4;
+constexpr size_t kStaticControlBytes = 256;
+constexpr size_t kStaticOffsetAt = 0;
+constexpr size_t kStaticTaskAt = kStaticOffsetAt + kStaticOffsetBytes;
+constexpr size_t kStaticSplitAt = kStaticTaskAt + kStaticTaskBytes;
+constexpr size_t kStaticPartialAt = kStaticSplitAt + kStaticSplitBytes;
+constexpr size_t kStaticControlAt = kStaticPartialAt + kStaticPartialBytes;
+constexpr size_t kStaticBytes = kStaticControlAt + kStaticControlBytes;
+static_assert(kStaticTaskAt % 256 == 0 && kStaticSplitAt % 256 == 0 &&
+                  kStaticPartialAt % 256 == 0 && kStaticControlAt % 256 == 0,
+              "regions of the static scratch keep 256-byte alignment");
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+namespace {
+std::mutex g_static_lock;
+unsigned char *g_static_address[64] = {nullptr};
+}  // namespace
+
+// Device address of the static scratch on the current device (set up on the
+// first call per device).
+static cudaError_t static_scratch_address(int device, unsigned char **address) {
+  std::lock_guard<std::mutex> guard(g_static_lock);
+  if (g_static_address[device] == nullptr) {
+    void *found = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&found, g_static_scratch);
+    if (e != cudaSuccess) return e;
+    g_static_address[device] = static_cast<unsigned char *>(found);
+  }
+  *address = g_static_address[device];
+  return cudaSuccess;
+}
+
+cudaError_t launch_segreduce_static(int kind, const float *values, float *out,
+                                    int32_t value_count,
+                                    const int32_t *host_offsets,
+                                    int32_t segment_count,
+                                    const HostPlan &plan, int device,
+                                    int sm_count, cudaStream_t stream) {
+  unsigned char *base = nullptr;
+  cudaError_t e = static_scratch_address(device, &base);
+  if (e != cudaSuccess) return e;
+  int32_t *d_off = reinterpret_cast<int32_t *>(base + kStaticOffsetAt);
+  Task *d_tasks = reinterpret_cast<Task *>(base + kStaticTaskAt);
+  SplitSegment *d_splits =
+      reinterpret_cast<SplitSegment *>(base + kStaticSplitAt);
+  float *d_partials = reinterpret_cast<float *>(base + kStaticPartialAt);
+  uint32_t *d_control = reinterpret_cast<uint32_t *>(base + kStaticControlAt);
+
+  const size_t noffsets = (size_t)segment_count + 1;
+  const size_t padded = ((noffsets + 3) / 4) * 4 + 4;
+  // The array keeps the previous call's contents: the padding after the
+  // offsets and the control words are the parts that must start at zero.
+  e = cudaMemsetAsync(d_off + noffsets, 0, (padded - noffsets) * 4, stream);
+  if (e != cudaSuccess) return e;
+  e = cudaMemsetAsync(d_control, 0, kStaticControlBytes, stream);
+  if (e != cudaSuccess) return e;
+  e = cudaMemcpyAsync(d_off, host_offsets, noffsets * 4,
+                      cudaMemcpyHostToDevice, stream);
+  if (e != cudaSuccess) return e;
+  e = cudaMemcpyAsync(d_tasks, plan.tasks.data(),
+                      plan.tasks.size() * sizeof(Task), cudaMemcpyHostToDevice,
+                      stream);
+  if (e != cudaSuccess) return e;
+  if (!plan.splits.empty()) {
+    e = cudaMemcpyAsync(d_splits, plan.splits.data(),
+                        plan.splits.size() * sizeof(SplitSegment),
+                        cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return e;
+  }
+  DevicePlan dev;
+  dev.device = device;
+  dev.sm_count = sm_count;
+  dev.tasks = d_tasks;
+  dev.task_count = (int32_t)plan.tasks.size();
+  dev.offsets = d_off;
+  dev.splits = d_splits;
+  dev.split_count = (int32_t)plan.splits.size();
+  dev.partials = d_partials;
+  dev.partial_slots = plan.partial_slots;
+  dev.control = d_control;
+  return launch_segreduce_split(kind, values, out, value_count, dev, stream,
+                                nullptr);
 }
 
 }  // namespace swg
