@@ -38,7 +38,9 @@ typedef enum swg_status {
   SWG_ERR_CUDA = 3,             /* a CUDA runtime call failed; text names it */
   SWG_ERR_PLAN_MISMATCH = 4,    /* plan built for other counts / device / operation */
   SWG_ERR_UNSUPPORTED = 5,      /* schedule needs a plan, or size beyond a stated limit */
-  SWG_ERR_DEVICE_TIMEOUT = 6    /* a bounded device-side wait gave up (read by swg_plan_status) */
+  SWG_ERR_DEVICE_TIMEOUT = 6,   /* a bounded device-side wait gave up (read by swg_plan_status) */
+  SWG_ERR_DEVICE_CHECK = 7      /* a kernel found a task or segment outside the launch's arrays:
+                                   the plan does not belong to these offsets (swg_plan_status) */
 } swg_status;
 
 /* Reduction kinds: the two the reference lowers
@@ -109,8 +111,11 @@ int swg_plan_destroy(swg_plan *plan);
 /* JSON text: counts, histogram, bucket shares, task counts, chosen schedule.
  * Returns SWG_ERR_INVALID_ARGUMENT when `capacity` is too small. */
 int swg_plan_describe(const swg_plan *plan, char *json, size_t capacity);
-/* Synchronises the plan's device and reports a device-side wait that gave up
- * in any launch since the last call (SWG_ERR_DEVICE_TIMEOUT), else SWG_OK. */
+/* Synchronises the plan's device and reports what the kernels flagged in any
+ * launch since the last call: a bounded wait that gave up
+ * (SWG_ERR_DEVICE_TIMEOUT) or a task / segment that does not fit the launch's
+ * arrays and was skipped instead of dereferenced (SWG_ERR_DEVICE_CHECK);
+ * else SWG_OK. */
 int swg_plan_status(swg_plan *plan);
 
 /* The planner alone, on the host: no device is touched.  Writes up to
@@ -151,7 +156,7 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
  * partials of split segments are placed in a fixed array that is part of the
  * library image on every GPU (about 1.8 MB, held until the process exits).
  * No cudaMalloc, cudaFree or other allocating call is made.
- * Limits: at most 262144 segments, 32768 tile tasks (about 2.6e8 values),
+ * Limits: at most 262144 segments, 32768 tile tasks (about 6.7e7 values),
  * 32768 partials and 8192 split segments; larger inputs are rejected with
  * SWG_ERR_UNSUPPORTED and a message naming the limit.
  * The first call on a device looks up the array's device address; make that

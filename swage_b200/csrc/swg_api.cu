@@ -123,6 +123,7 @@ const char *swg_status_name(int status) {
     case SWG_ERR_PLAN_MISMATCH: return "SWG_ERR_PLAN_MISMATCH";
     case SWG_ERR_UNSUPPORTED: return "SWG_ERR_UNSUPPORTED";
     case SWG_ERR_DEVICE_TIMEOUT: return "SWG_ERR_DEVICE_TIMEOUT";
+    case SWG_ERR_DEVICE_CHECK: return "SWG_ERR_DEVICE_CHECK";
     default: return "SWG_ERR_UNKNOWN";
   }
 }
@@ -187,6 +188,7 @@ int swg_plan_create(const int32_t *host_offsets, int32_t segment_count,
   dev.device = device;
   dev.sm_count = sm_count;
   dev.task_count = (int32_t)plan->host.tasks.size();
+  dev.segment_count = segment_count;
   dev.split_count = (int32_t)plan->host.splits.size();
   dev.partial_slots = plan->host.partial_slots;
   const size_t noffsets = (size_t)segment_count + 1;
@@ -289,8 +291,13 @@ int swg_plan_status(swg_plan *plan) {
   if (e != cudaSuccess) return cuda_failure("cudaMemcpy", e);
   if (control[2] != 0) {
     cudaMemset(plan->dev.control, 0, sizeof(control));
-    swg::set_error("a bounded device-side wait gave up during a launch");
-    return SWG_ERR_DEVICE_TIMEOUT;
+    const char *what = control[2] == 1 ? "a bounded device-side wait gave up"
+                       : control[2] == 2
+                           ? "a task of the plan does not fit the launch's "
+                             "arrays"
+                           : "the device offsets do not match the plan";
+    swg::set_error("%s (code %u, detail %u)", what, control[2], control[3]);
+    return control[2] == 1 ? SWG_ERR_DEVICE_TIMEOUT : SWG_ERR_DEVICE_CHECK;
   }
   return SWG_OK;
 }

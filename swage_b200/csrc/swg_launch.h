@@ -14,12 +14,13 @@ struct DevicePlan {
   int sm_count = 0;
   Task *tasks = nullptr;
   int32_t task_count = 0;
+  int32_t segment_count = 0;
   int32_t *offsets = nullptr;      // aligned, padded copy of the CSR offsets
   SplitSegment *splits = nullptr;
   int32_t split_count = 0;
   float *partials = nullptr;       // one float per partial slot
   int32_t partial_slots = 0;
-  uint32_t *control = nullptr;     // [0] ticket, [1] finished CTAs, [2] error
+  uint32_t *control = nullptr;     // [0] ticket, [1] finished, [2] error, [3] detail
 };
 
 // Optional pair of events recorded around the dominant kernel of a call.

@@ -12,9 +12,9 @@
 namespace swg {
 
 // Geometry shared by the planner and the tile kernels.
-constexpr int kTileValues = 8192;      // values per tile task (32 KiB of fp32)
-constexpr int kTileMaxSegments = 2048; // segments per packed tile task
-constexpr int kLongSegment = 2048;     // longer segments are reduced CTA-wide
+constexpr int kTileValues = 2048;      // values per tile task (8 KiB of fp32)
+constexpr int kTileMaxSegments = 512;  // segments per packed tile task
+constexpr int kLongSegment = 1024;     // longer segments become chunk tasks
 constexpr int kHistogramBins = 33;     // bin b: len == 0 | 2^(b-1) <= len < 2^b
 
 // One schedulable unit.  16 bytes so a task is one 128-bit load.

@@ -177,11 +177,16 @@ void build_host_plan(const int32_t *offsets, int32_t segment_count, int op,
   plan->mean_length =
       segment_count > 0 ? (double)plan->value_count / segment_count : 0.0;
   plan_reduce(offsets, segment_count, plan);
-  // Tile tasks drawn by persistent CTAs are never worse than a static
-  // mapping once there is more than a handful of them; below that a launch
-  // is latency-bound whatever the mapping, and one CTA per task is enough.
-  plan->schedule =
-      plan->tasks.size() <= 148 ? SWG_SCHED_SPLIT : SWG_SCHED_PERSISTENT;
+  // Schedule choice from the histogram (measured on B200):
+  //  - every segment of moderate length and none long: one warp per segment
+  //    streams straight from global memory and needs no staging;
+  //  - anything skewed, or dominated by short segments: tile tasks, one per
+  //    warp (split), which balance long segments and pack short ones.
+  // The persistent schedule runs the same tasks and is selectable, but the
+  // hardware CTA scheduler keeps more tiles in flight than its private rings.
+  const bool moderate =
+      plan->max_length <= 4096 && plan->mean_length >= 256.0;
+  plan->schedule = moderate ? SWG_SCHED_WARP : SWG_SCHED_SPLIT;
 }
 
 std::string describe_host_plan(const HostPlan &plan) {
@@ -192,11 +197,13 @@ std::string describe_host_plan(const HostPlan &plan) {
            "\"mean_length\": %.3f, \"max_length\": %lld, \"tasks\": %zu, "
            "\"pack_tasks\": %lld, \"chunk_tasks\": %lld, "
            "\"split_segments\": %zu, \"partial_slots\": %d, "
-           "\"tile_values\": %d, \"long_segment\": %d, ",
+           "\"tile_values\": %d, \"tile_max_segments\": %d, "
+           "\"long_segment\": %d, ",
            plan.segment_count, plan.value_count, plan.op, plan.schedule,
            plan.mean_length, (long long)plan.max_length, plan.tasks.size(),
            (long long)plan.pack_tasks, (long long)plan.chunk_tasks,
-           plan.splits.size(), plan.partial_slots, kTileValues, kLongSegment);
+           plan.splits.size(), plan.partial_slots, kTileValues, kTileMaxSegments,
+           kLongSegment);
   text += buffer;
   text += "\"histogram\": [";
   for (int bin = 0; bin < kHistogramBins; ++bin) {

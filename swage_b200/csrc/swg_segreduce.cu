@@ -7,12 +7,13 @@
 //
 //   warp        one warp per segment, 128-bit loads straight from global
 //   cta         one CTA per segment (the reference's own mapping, vectorised)
-//   split       the plan's tile tasks, one per CTA; segments longer than a
-//               tile are chunked into partials and merged by a second pass
-//   persistent  the same tile tasks, drawn from a ticket counter by one
-//               resident CTA per SM; a producer warp stages tiles into a
-//               shared-memory ring with bulk async copies (TMA) while eight
-//               consumer warps reduce the previous ones
+//   split       the plan's tile tasks, one per warp, eight per CTA; segments
+//               longer than a tile are chunked into partials and merged by a
+//               second pass
+//   persistent  the same tile tasks, drawn from a ticket counter by the
+//               warps of one resident CTA per SM; every warp keeps three
+//               tiles in flight in its own shared-memory ring, filled with
+//               bulk async copies (TMA), and reduces them as they land
 //
 // All of them are HBM-bound: 4 bytes per value + 4 per offset + 4 per output.
 // No floating-point atomics anywhere: every result is produced by a fixed
@@ -68,25 +69,36 @@ __global__ void segreduce_cta_kernel(const float *__restrict__ values,
 
 // ---------------------------------------------------------------------------
 // Tile tasks (split and persistent schedules)
+//
+// A task is small enough (kTileValues values, kTileMaxSegments segments) for
+// ONE WARP to own it from the bulk copy to the output store, so no CTA-wide
+// barrier appears anywhere: every warp runs its own copy -> wait -> reduce
+// pipeline on its own shared-memory stages and its own mbarriers, and the SM
+// overlaps the phases of its resident warps.
 // ---------------------------------------------------------------------------
-constexpr int kConsumerThreads = 256;
-constexpr int kConsumerWarps = kConsumerThreads / 32;
-constexpr int kShortSegment = 32;  // reduced by a single thread inside a tile
-constexpr int kLongListCap = 256;  // > kTileValues / (kShortSegment + 1)
+constexpr int kLaneSegment = 16;    // reduced by a single lane inside a tile
+constexpr int kGroupSegment = 256;  // up to here by a group of eight lanes
 constexpr int kTileFloats = kTileValues + 8;
 constexpr int kTileOffsets = kTileMaxSegments + 8;
 constexpr int kStageTileBytes = kTileFloats * 4;
 constexpr int kStageOffsetBytes = kTileOffsets * 4;
 constexpr int kStageBytes =
-    ((kStageTileBytes + kStageOffsetBytes + 16 + 127) / 128) * 128;
+    ((kStageTileBytes + kStageOffsetBytes + 127) / 128) * 128;
 constexpr uint32_t kTaskStop = 15u;  // sentinel kind: no more tasks
-constexpr int kRingStages = 4;
-constexpr int kTicketBatch = 4;
+
+constexpr int kSplitWarps = 4;       // split: tasks per CTA, one stage each
 
 struct Stage {
   float *tile;
   int32_t *soff;
-  Task *desc;
+};
+
+// Per-warp lists of the segments (of the current 32) that more than one lane
+// works on, and their results.
+struct WarpScratch {
+  int begin[32];
+  int end[32];
+  float result[32];
 };
 
 __device__ __forceinline__ Stage stage_at(unsigned char *base, int index) {
@@ -94,33 +106,77 @@ __device__ __forceinline__ Stage stage_at(unsigned char *base, int index) {
   Stage s;
   s.tile = reinterpret_cast<float *>(p);
   s.soff = reinterpret_cast<int32_t *>(p + kStageTileBytes);
-  s.desc = reinterpret_cast<Task *>(p + kStageTileBytes + kStageOffsetBytes);
   return s;
 }
 
-struct Scratch {
-  float red[32];
-  int long_list[kLongListCap];
-  int long_count;
-};
-
-__device__ __forceinline__ void consumer_sync() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+__device__ __forceinline__ Task stop_task() {
+  Task t;
+  t.seg = 0;
+  t.count = 0;
+  t.vbegin = 0;
+  t.vcount_kind = kTaskStop << 28;
+  return t;
 }
 
-// Warp-collective: stage one task.  `mis` is the phase of the values pointer
-// inside a 16-byte line, in elements.  The bulk copy takes every 16-byte line
-// that intersects the task's value range and lies wholly inside the values
-// array (neighbouring elements that ride along are never read); the at most
-// three elements at either end of the array that no such line covers are
-// fetched with plain loads.  Element i lands at tile[i - origin] with
-// origin = vbegin - ((vbegin + mis) & 3).
+__device__ __forceinline__ bool is_stop(const Task &t) {
+  return (t.vcount_kind >> 28) == kTaskStop;
+}
+
+// Broadcast lane `src`'s task to the whole warp.
+__device__ __forceinline__ Task shuffle_task(const Task &mine, int src) {
+  Task t;
+  t.seg = __shfl_sync(kFullMask, mine.seg, src);
+  t.count = __shfl_sync(kFullMask, mine.count, src);
+  t.vbegin = __shfl_sync(kFullMask, mine.vbegin, src);
+  t.vcount_kind = __shfl_sync(kFullMask, mine.vcount_kind, src);
+  return t;
+}
+
+// What a task may touch; every task is checked against it before use, so a
+// plan that does not belong to the launch's arrays (or a corrupted one) is
+// reported through the error word instead of being dereferenced.
+struct Limits {
+  int32_t value_count;
+  int32_t segment_count;
+  int32_t partial_slots;
+};
+
+// Error codes left in control[2] (first one wins; control[3] = detail).
+constexpr uint32_t kErrTimeout = 1u, kErrBadTask = 2u, kErrBadSegment = 3u;
+
+__device__ __forceinline__ void report(uint32_t *control, uint32_t code,
+                                       uint32_t detail) {
+  if (atomicCAS(control + 2, 0u, code) == 0u) atomicExch(control + 3, detail);
+}
+
+__device__ __forceinline__ bool task_ok(const Task &t, const Limits &limits) {
+  const uint32_t kind = t.vcount_kind >> 28;
+  const int64_t vcount = (int64_t)(t.vcount_kind & kTaskCountMask);
+  if (t.seg < 0 || t.seg >= limits.segment_count) return false;
+  if (t.vbegin < 0 || vcount > kTileValues ||
+      (int64_t)t.vbegin + vcount > limits.value_count)
+    return false;
+  if (kind == kTaskPack)
+    return t.count >= 1 && t.count <= kTileMaxSegments &&
+           (int64_t)t.seg + t.count <= limits.segment_count;
+  if (kind == kTaskChunk)
+    return t.count >= -1 && t.count < limits.partial_slots;
+  return false;
+}
+
+// Stage one task; runs entirely in the calling thread, so several lanes of a
+// producer warp can stage several tasks at once.  `mis` is the phase of the
+// values pointer inside a 16-byte line, in elements.  The bulk copy takes
+// every 16-byte line that intersects the task's value range and lies wholly
+// inside the values array (neighbouring elements that ride along are never
+// read); the at most three elements at either end of the array that no such
+// line covers are fetched with plain loads.  Element i lands at
+// tile[i - origin] with origin = vbegin - ((vbegin + mis) & 3).
 __device__ __forceinline__ void issue_task(const Task &task,
                                            const float *__restrict__ values,
                                            int mis, int32_t value_count,
                                            const int32_t *__restrict__ d_off,
-                                           Stage stage, uint64_t *full,
-                                           int lane) {
+                                           Stage stage, uint64_t *full) {
   const uint32_t kind = task.vcount_kind >> 28;
   const int64_t vb = task.vbegin;
   const int64_t ve = vb + (int64_t)(task.vcount_kind & kTaskCountMask);
@@ -130,14 +186,14 @@ __device__ __forceinline__ void issue_task(const Task &task,
   const int64_t last_line = (int64_t)value_count - ((value_count + mis) & 3);
   if (hi > last_line) hi = last_line;
   if (hi < lo) hi = lo;
-
-  int64_t idx = -1;
-  if (lane < 8) idx = vb + lane;
-  else if (lane < 16) idx = ve - 1 - (lane - 8);
-  if (idx >= vb && idx < ve && (idx < lo || idx >= hi))
-    stage.tile[idx - origin] = values[idx];
-
-  uint32_t bytes_v = (uint32_t)(hi - lo) * 4u;
+  if (lo > vb || hi < ve) {
+    // only the first and the last task of an array can get here
+    for (int64_t idx = vb; idx < ve && idx < lo; ++idx)
+      stage.tile[idx - origin] = values[idx];
+    for (int64_t idx = hi > vb ? hi : vb; idx < ve; ++idx)
+      if (idx >= hi || idx < lo) stage.tile[idx - origin] = values[idx];
+  }
+  const uint32_t bytes_v = (uint32_t)(hi - lo) * 4u;
   uint32_t bytes_o = 0;
   int32_t o_lo = 0;
   if (kind == kTaskPack) {
@@ -145,256 +201,293 @@ __device__ __forceinline__ void issue_task(const Task &task,
     const int32_t o_hi = (task.seg + task.count + 1 + 3) & ~3;
     bytes_o = (uint32_t)(o_hi - o_lo) * 4u;
   }
-  __syncwarp();
-  if (lane == 0) {
-    *stage.desc = task;
-    mbar_arrive_expect_tx(full, bytes_v + bytes_o);
-    if (bytes_v) bulk_g2s(stage.tile + (lo - origin), values + lo, bytes_v, full);
-    if (bytes_o) bulk_g2s(stage.soff, d_off + o_lo, bytes_o, full);
-  }
+  mbar_arrive_expect_tx(full, bytes_v + bytes_o);
+  if (bytes_v) bulk_g2s(stage.tile + (lo - origin), values + lo, bytes_v, full);
+  if (bytes_o) bulk_g2s(stage.soff, d_off + o_lo, bytes_o, full);
 }
 
-// Reduce one staged task with the kConsumerThreads consumer threads.
+// Warp-collective: reduce one staged task.
 template <class Op>
-__device__ __forceinline__ void process_task(const Stage &stage, int mis,
+__device__ __forceinline__ void process_task(const Task &task,
+                                             const Stage &stage, int mis,
                                              float *__restrict__ out,
                                              float *__restrict__ partials,
-                                             Scratch *scratch, int tid) {
-  const Task task = *stage.desc;
+                                             WarpScratch *scratch,
+                                             const Limits &limits,
+                                             uint32_t *control, int lane) {
+  if (!task_ok(task, limits)) {
+    if (lane == 0) report(control, kErrBadTask, (uint32_t)task.seg);
+    return;
+  }
   const uint32_t kind = task.vcount_kind >> 28;
   const int vcount = (int)(task.vcount_kind & kTaskCountMask);
   const int shift = (int)(((int64_t)task.vbegin + mis) & 3);
   const float *tile = stage.tile;
-  const int lane = tid & 31, warp = tid >> 5;
 
   if (kind == kTaskChunk) {
-    // One piece of a long segment: every consumer thread strides over it.
-    const float *p = tile + shift;
+    // One piece of a long segment occupies tile[shift, shift + vcount):
+    // scalar ends, 128-bit body, four independent accumulators per lane.
+    const int lo = shift, hi = shift + vcount;
+    int blo = (lo + 3) & ~3, bhi = hi & ~3;
+    if (blo > bhi) blo = bhi = hi;  // too short for an aligned body
+    const int head_end = blo < hi ? blo : hi;
     float a0 = Op::identity(), a1 = Op::identity(), a2 = Op::identity(),
           a3 = Op::identity();
-    int i = tid;
-    for (; i + 3 * kConsumerThreads < vcount; i += 4 * kConsumerThreads) {
-      a0 = Op::apply(a0, p[i]);
-      a1 = Op::apply(a1, p[i + kConsumerThreads]);
-      a2 = Op::apply(a2, p[i + 2 * kConsumerThreads]);
-      a3 = Op::apply(a3, p[i + 3 * kConsumerThreads]);
+    if (lo + lane < head_end) a0 = Op::apply(a0, tile[lo + lane]);
+    const float4 *body = reinterpret_cast<const float4 *>(tile);
+    const int vlo = blo >> 2, vhi = bhi >> 2;
+    int v = vlo + lane;
+    for (; v + 96 < vhi; v += 128) {
+      const float4 q0 = body[v], q1 = body[v + 32], q2 = body[v + 64],
+                   q3 = body[v + 96];
+      a0 = fold4<Op>(a0, q0);
+      a1 = fold4<Op>(a1, q1);
+      a2 = fold4<Op>(a2, q2);
+      a3 = fold4<Op>(a3, q3);
     }
-    for (; i < vcount; i += kConsumerThreads) a0 = Op::apply(a0, p[i]);
-    float acc = Op::apply(Op::apply(a0, a1), Op::apply(a2, a3));
-    acc = warp_reduce<Op>(acc);
-    if (lane == 0) scratch->red[warp] = acc;
-    consumer_sync();
-    if (warp == 0) {
-      float r = lane < kConsumerWarps ? scratch->red[lane] : Op::identity();
-      r = warp_reduce<Op>(r);
-      if (lane == 0) {
-        if (task.count < 0) out[task.seg] = r;
-        else partials[task.count] = r;
-      }
+    for (; v < vhi; v += 32) a0 = fold4<Op>(a0, body[v]);
+    const int tail = bhi > head_end ? bhi : head_end;
+    if (tail + lane < hi) a1 = Op::apply(a1, tile[tail + lane]);
+    const float r =
+        warp_reduce<Op>(Op::apply(Op::apply(a0, a1), Op::apply(a2, a3)));
+    if (lane == 0) {
+      if (task.count < 0) out[task.seg] = r;
+      else partials[task.count] = r;
     }
-    consumer_sync();  // red[] and the tile are free again
     return;
   }
 
-  // Packed whole segments.  Tile-relative bounds of segment k are
-  // soff[ob + k] - origin and soff[ob + k + 1] - origin.
+  // Packed whole segments, 32 at a time: lane k owns segment base + k.
+  //   length <= kLaneSegment   summed by the owning lane alone
+  //   length <= kGroupSegment  listed, then reduced four at a time by the
+  //                            warp's four groups of eight lanes
+  //   longer                   listed, then reduced by the whole warp
+  // Listed results come back through the warp's scratch to their owning
+  // lanes, so the 32 results leave in one coalesced store.  Tile-relative
+  // bounds of segment k are soff[k] - origin and soff[k + 1] - origin.
   const int32_t *soff = stage.soff + (task.seg & 3);
   const int origin = task.vbegin - shift;
-  if (tid == 0) scratch->long_count = 0;
-  consumer_sync();
-  for (int k = tid; k < task.count; k += kConsumerThreads) {
-    const int a = soff[k] - origin, b = soff[k + 1] - origin;
-    if (b - a <= kShortSegment) {
-      float acc = Op::identity();
+  const unsigned below = (1u << lane) - 1u;
+  const int group = lane >> 3, sub = lane & 7;
+  const unsigned group_mask = 0xffu << (group * 8);
+  for (int base = 0; base < task.count; base += 32) {
+    const int k = base + lane;
+    const bool valid = k < task.count;
+    int a = valid ? soff[k] - origin : 0;
+    int b = valid ? soff[k + 1] - origin : 0;
+    if (valid && (a < shift || b < a || b > shift + vcount)) {
+      // offsets that do not match the plan: report, treat as empty
+      report(control, kErrBadSegment, (uint32_t)(task.seg + k));
+      a = b = shift;
+    }
+    const int length = b - a;
+    float acc = Op::identity();
+    const bool medium =
+        valid && length > kLaneSegment && length <= kGroupSegment;
+    const bool wide = valid && length > kGroupSegment;
+    if (valid && length <= kLaneSegment)
       for (int i = a; i < b; ++i) acc = Op::apply(acc, tile[i]);
-      out[task.seg + k] = acc;
-    } else {
-      const int slot = atomicAdd(&scratch->long_count, 1);
-      scratch->long_list[slot] = k;
+    const unsigned medium_mask = __ballot_sync(kFullMask, medium);
+    const unsigned wide_mask = __ballot_sync(kFullMask, wide);
+    if ((medium_mask | wide_mask) == 0) {
+      if (valid) out[task.seg + k] = acc;
+      continue;
     }
-  }
-  consumer_sync();
-  const int nlong = scratch->long_count;
-  for (int j = warp; j < nlong; j += kConsumerWarps) {
-    const int k = scratch->long_list[j];
-    const int a = soff[k] - origin, b = soff[k + 1] - origin;
-    float a0 = Op::identity(), a1 = Op::identity();
-    int i = a + lane;
-    for (; i + 32 < b; i += 64) {
-      a0 = Op::apply(a0, tile[i]);
-      a1 = Op::apply(a1, tile[i + 32]);
+    const int medium_count = __popc(medium_mask);
+    const int listed = medium_count + __popc(wide_mask);
+    int slot = -1;
+    if (medium) slot = __popc(medium_mask & below);
+    if (wide) slot = medium_count + __popc(wide_mask & below);
+    if (slot >= 0) {
+      scratch->begin[slot] = a;
+      scratch->end[slot] = b;
     }
-    if (i < b) a0 = Op::apply(a0, tile[i]);
-    const float r = warp_reduce<Op>(Op::apply(a0, a1));
-    if (lane == 0) out[task.seg + k] = r;
+    __syncwarp();
+    for (int e = group; e < medium_count; e += 4) {
+      const int ea = scratch->begin[e], eb = scratch->end[e];
+      float p0 = Op::identity(), p1 = Op::identity(), p2 = Op::identity(),
+            p3 = Op::identity();
+      int i = ea + sub;
+      for (; i + 24 < eb; i += 32) {
+        p0 = Op::apply(p0, tile[i]);
+        p1 = Op::apply(p1, tile[i + 8]);
+        p2 = Op::apply(p2, tile[i + 16]);
+        p3 = Op::apply(p3, tile[i + 24]);
+      }
+      for (; i < eb; i += 8) p0 = Op::apply(p0, tile[i]);
+      float r = Op::apply(Op::apply(p0, p1), Op::apply(p2, p3));
+      r = Op::apply(r, __shfl_xor_sync(group_mask, r, 4));
+      r = Op::apply(r, __shfl_xor_sync(group_mask, r, 2));
+      r = Op::apply(r, __shfl_xor_sync(group_mask, r, 1));
+      if (sub == 0) scratch->result[e] = r;
+    }
+    __syncwarp();
+    for (int e = medium_count; e < listed; ++e) {
+      const int ea = scratch->begin[e], eb = scratch->end[e];
+      float p0 = Op::identity(), p1 = Op::identity(), p2 = Op::identity(),
+            p3 = Op::identity();
+      int i = ea + lane;
+      for (; i + 96 < eb; i += 128) {
+        p0 = Op::apply(p0, tile[i]);
+        p1 = Op::apply(p1, tile[i + 32]);
+        p2 = Op::apply(p2, tile[i + 64]);
+        p3 = Op::apply(p3, tile[i + 96]);
+      }
+      for (; i < eb; i += 32) p0 = Op::apply(p0, tile[i]);
+      const float r =
+          warp_reduce<Op>(Op::apply(Op::apply(p0, p1), Op::apply(p2, p3)));
+      if (lane == 0) scratch->result[e] = r;
+    }
+    __syncwarp();
+    if (slot >= 0) acc = scratch->result[slot];
+    if (valid) out[task.seg + k] = acc;
+    __syncwarp();  // the lists are rewritten by the next 32 segments
   }
-  consumer_sync();  // long_list and the tile are free again
 }
 
-// split schedule: one task per CTA, single stage.
+// split schedule: CTA b, warp w reduces task b * kSplitWarps + w.
 template <class Op>
-__global__ void __launch_bounds__(kConsumerThreads)
+__global__ void __launch_bounds__(kSplitWarps * 32)
 segreduce_split_kernel(const float *__restrict__ values,
                        float *__restrict__ out, int32_t value_count,
-                       const Task *__restrict__ tasks,
+                       const Task *__restrict__ tasks, int32_t task_count,
                        const int32_t *__restrict__ d_off,
                        float *__restrict__ partials,
-                       uint32_t *__restrict__ control) {
+                       uint32_t *__restrict__ control, Limits limits) {
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ uint64_t full;
-  __shared__ Scratch scratch;
-  const int tid = threadIdx.x;
+  __shared__ uint64_t full[kSplitWarps];
+  __shared__ WarpScratch scratch[kSplitWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int mis = (int)(((uintptr_t)values >> 2) & 3);
-  Stage stage = stage_at(smem, 0);
-  if (tid == 0) {
-    mbar_init(&full, 1);
+  const int64_t index = (int64_t)blockIdx.x * kSplitWarps + warp;
+  if (index >= task_count) return;
+  if (lane == 0) {
+    mbar_init(&full[warp], 1);
     fence_mbar_init();
   }
-  __syncthreads();
-  if (tid < 32) {
-    const Task task = tasks[blockIdx.x];
-    issue_task(task, values, mis, value_count, d_off, stage, &full, tid);
-  }
-  if (!mbar_wait(&full, 0)) {
-    if (tid == 0) atomicExch(control + 2, 1u);
+  __syncwarp();
+  const Task task = tasks[index];
+  const Stage stage = stage_at(smem, warp);
+  if (!task_ok(task, limits)) {
+    if (lane == 0) report(control, kErrBadTask, (uint32_t)index);
     return;
   }
-  process_task<Op>(stage, mis, out, partials, &scratch, tid);
+  if (lane == 0)
+    issue_task(task, values, mis, value_count, d_off, stage, &full[warp]);
+  if (!mbar_wait(&full[warp], 0)) {
+    if (lane == 0) report(control, kErrTimeout, (uint32_t)index);
+    return;
+  }
+  process_task<Op>(task, stage, mis, out, partials, &scratch[warp], limits,
+                   control, lane);
 }
 
-// persistent schedule.
-//   warp kConsumerWarps (the last one) = producer: draws tickets in batches,
-//   loads the task descriptors one batch ahead, and keeps the ring full.
-//   warps 0..kConsumerWarps-1 = consumers.
-// control[0] = next ticket, control[1] = CTAs that stopped drawing,
-// control[2] = error flag.  The last CTA to stop resets [0] and [1] so the
-// next launch starts from zero without a memset.
-template <class Op>
-__global__ void __launch_bounds__(kConsumerThreads + 32, 1)
+// persistent schedule: one resident CTA per SM, every warp an independent
+// worker with its own ring of kStages shared-memory stages and its own
+// mbarriers; no warp ever waits on another.  A worker draws tickets kStages
+// at a time from control[0], two rounds ahead of their use, and loads the
+// task descriptors one round ahead, so neither the atomic nor the descriptor
+// load sits on its critical path; it refills a stage with the next task's
+// bulk async copy as soon as it has reduced the previous one.
+// control[1] counts workers that have stopped drawing; the last one resets
+// control[0] and control[1] so the next launch needs no memset.
+// control[2] is the error code, control[3] its detail.
+template <class Op, int kWarps, int kStages>
+__global__ void __launch_bounds__(kWarps * 32, 1)
 segreduce_persistent_kernel(const float *__restrict__ values,
                             float *__restrict__ out, int32_t value_count,
                             const Task *__restrict__ tasks, int32_t task_count,
                             const int32_t *__restrict__ d_off,
                             float *__restrict__ partials,
-                            uint32_t *__restrict__ control) {
+                            uint32_t *__restrict__ control, Limits limits) {
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ uint64_t full[kRingStages], empty[kRingStages];
-  __shared__ Scratch scratch;
-  const int tid = threadIdx.x;
+  __shared__ uint64_t full[kWarps * kStages];
+  __shared__ WarpScratch scratch[kWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int mis = (int)(((uintptr_t)values >> 2) & 3);
-  if (tid == 0) {
-    for (int s = 0; s < kRingStages; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
-    }
+  uint64_t *bars = full + warp * kStages;
+  unsigned char *ring = smem + (size_t)warp * kStages * kStageBytes;
+  if (lane == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
     fence_mbar_init();
   }
-  __syncthreads();
+  __syncwarp();
 
-  if (tid >= kConsumerThreads) {
-    // ---------------- producer warp ----------------
-    const int lane = tid - kConsumerThreads;
-    int stage = 0;
-    uint32_t phase = 0;
-    int armed = 0;  // stages armed and possibly not yet consumed
-    bool ok = true;
-    Task stop;
-    stop.seg = 0;
-    stop.count = 0;
-    stop.vbegin = 0;
-    stop.vcount_kind = kTaskStop << 28;
-
-    auto draw = [&]() -> uint32_t {
-      uint32_t t = 0;
-      if (lane == 0) t = atomicAdd(control, (uint32_t)kTicketBatch);
-      return __shfl_sync(kFullMask, t, 0);
-    };
-    auto fetch = [&](uint32_t base) -> Task {
-      Task t = stop;
-      const uint32_t mine = base + (uint32_t)lane;
-      if (lane < kTicketBatch && mine < (uint32_t)task_count)
-        t = tasks[mine];
-      return t;
-    };
-
-    uint32_t base_next = draw();
-    Task cur = fetch(base_next);
-    base_next = draw();
-    bool done = false;
-    while (!done && ok) {
-      const uint32_t base_after = draw();   // in flight during this batch
-      const Task nxt = fetch(base_next);    // descriptors one batch ahead
-      for (int j = 0; j < kTicketBatch; ++j) {
-        Task task;
-        task.seg = __shfl_sync(kFullMask, cur.seg, j);
-        task.count = __shfl_sync(kFullMask, cur.count, j);
-        task.vbegin = __shfl_sync(kFullMask, cur.vbegin, j);
-        task.vcount_kind = __shfl_sync(kFullMask, cur.vcount_kind, j);
-        if (!mbar_wait(&empty[stage], phase ^ 1u)) {
-          ok = false;
-          break;
-        }
-        Stage st = stage_at(smem, stage);
-        if ((task.vcount_kind >> 28) == kTaskStop) {
-          if (lane == 0) {
-            *st.desc = task;
-            mbar_arrive(&full[stage]);
-          }
-          done = true;
-          break;
-        }
-        issue_task(task, values, mis, value_count, d_off, st, &full[stage],
-                   lane);
-        if (armed < kRingStages) ++armed;
-        if (++stage == kRingStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
-      }
-      cur = nxt;
-      base_next = base_after;
-    }
-    if (!ok) {
-      // A wait gave up: flag it, then let the copies already in flight land
-      // (bounded) before this CTA's shared memory can be handed on.
-      if (lane == 0) atomicExch(control + 2, 1u);
-      int s = stage;
-      uint32_t ph = phase;
-      for (int k = 0; k < armed; ++k) {
-        if (--s < 0) {
-          s = kRingStages - 1;
-          ph ^= 1u;
-        }
-        mbar_wait(&full[s], ph);
-      }
-    }
+  // draw() leaves the ticket in lane 0 only; it is broadcast where it is
+  // used, a round later, so the atomic's latency is off the critical path.
+  auto draw = [&]() -> uint32_t {
+    uint32_t t = 0;
+    if (lane == 0) t = atomicAdd(control, (uint32_t)kStages);
+    return t;
+  };
+  auto fetch = [&](uint32_t lane0_base) -> Task {
+    const uint32_t base = __shfl_sync(kFullMask, lane0_base, 0);
+    Task t = stop_task();
+    const uint32_t mine = base + (uint32_t)lane;
+    if (lane < kStages && mine < (uint32_t)task_count) t = tasks[mine];
+    return t;
+  };
+  // Stage `t` into stage s; a task that fails its check is staged as an
+  // immediate arrival and reported by process_task.
+  auto stage_in = [&](const Task &t, int s) {
     if (lane == 0) {
-      __threadfence();
-      const uint32_t finished = atomicAdd(control + 1, 1u);
-      if (finished == gridDim.x - 1) {
-        atomicExch(control, 0u);
-        atomicExch(control + 1, 0u);
-      }
+      if (task_ok(t, limits))
+        issue_task(t, values, mis, value_count, d_off, stage_at(ring, s),
+                   &bars[s]);
+      else
+        mbar_arrive(&bars[s]);
     }
-    return;
-  }
+  };
 
-  // ---------------- consumer warps ----------------
-  int stage = 0;
-  uint32_t phase = 0;
-  for (;;) {
-    if (!mbar_wait(&full[stage], phase)) {
-      if (tid == 0) atomicExch(control + 2, 1u);
-      return;
+  // lane s holds the task now staged in stage s (cur) and the one that will
+  // replace it (nxt)
+  Task cur = fetch(draw());
+  Task nxt = fetch(draw());
+  uint32_t base_after = draw();
+#pragma unroll
+  for (int s = 0; s < kStages; ++s) {
+    const Task t = shuffle_task(cur, s);
+    if (!is_stop(t)) stage_in(t, s);
+  }
+  uint32_t parity = 0;
+  bool running = true, ok = true;
+  while (running) {
+    const Task after = fetch(base_after);  // descriptors two rounds ahead
+    base_after = draw();                   // tickets three rounds ahead
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) {
+      const Task t = shuffle_task(cur, s);
+      if (is_stop(t)) {
+        running = false;
+        break;
+      }
+      if (!mbar_wait(&bars[s], parity)) {
+        if (lane == 0) report(control, kErrTimeout, (uint32_t)t.seg);
+        ok = false;
+        running = false;
+        break;
+      }
+      process_task<Op>(t, stage_at(ring, s), mis, out, partials,
+                       &scratch[warp], limits, control, lane);
+      __syncwarp();  // every lane is done with the stage before it is refilled
+      const Task n = shuffle_task(nxt, s);
+      if (!is_stop(n)) stage_in(n, s);
     }
-    Stage st = stage_at(smem, stage);
-    if ((st.desc->vcount_kind >> 28) == kTaskStop) break;
-    process_task<Op>(st, mis, out, partials, &scratch, tid);
-    // process_task ends on a consumer barrier: every read of the stage is done
-    if (tid == 0) mbar_arrive(&empty[stage]);
-    if (++stage == kRingStages) {
-      stage = 0;
-      phase ^= 1u;
+    cur = nxt;
+    nxt = after;
+    parity ^= 1u;
+  }
+  if (!ok) {
+    // A wait gave up: let this warp's copies in flight land (bounded) before
+    // its shared memory can be handed on.
+    for (int s = 0; s < kStages; ++s) mbar_wait(&bars[s], parity);
+  }
+  if (lane == 0) {
+    __threadfence();
+    const uint32_t finished = atomicAdd(control + 1, 1u);
+    if (finished == gridDim.x * kWarps - 1) {
+      atomicExch(control, 0u);
+      atomicExch(control + 1, 0u);
     }
   }
 }
@@ -423,23 +516,55 @@ segreduce_combine_kernel(const SplitSegment *__restrict__ splits,
 // ---------------------------------------------------------------------------
 // launchers
 // ---------------------------------------------------------------------------
+constexpr int kSplitBytes = kSplitWarps * kStageBytes;
+
+template <class Op, int kWarps, int kStages>
+static cudaError_t persistent_launch(const float *values, float *out,
+                                     int32_t value_count,
+                                     const DevicePlan &plan,
+                                     cudaStream_t stream, bool configure) {
+  constexpr int kBytes = kWarps * kStages * kStageBytes;
+  static_assert(kBytes + 8 * kWarps * kStages +
+                        (int)sizeof(WarpScratch) * kWarps <= 227 * 1024,
+                "rings exceed shared memory");
+  if (configure)
+    return cudaFuncSetAttribute(
+        segreduce_persistent_kernel<Op, kWarps, kStages>,
+        cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
+  int grid = plan.sm_count;
+  const int needed = (plan.task_count + kWarps - 1) / kWarps;
+  if (grid > needed) grid = needed;
+  segreduce_persistent_kernel<Op, kWarps, kStages>
+      <<<grid, kWarps * 32, kBytes, stream>>>(
+          values, out, value_count, plan.tasks, plan.task_count, plan.offsets,
+          plan.partials, plan.control,
+          Limits{value_count, plan.segment_count, plan.partial_slots});
+  return cudaGetLastError();
+}
+
+template <class Op>
+static cudaError_t persistent_dispatch(const float *values, float *out,
+                                       int32_t value_count,
+                                       const DevicePlan &plan,
+                                       cudaStream_t stream, bool configure) {
+  return persistent_launch<Op, 7, 3>(values, out, value_count, plan, stream,
+                                     configure);
+}
+
 cudaError_t configure_segreduce_kernels() {
   cudaError_t e;
-  e = cudaFuncSetAttribute(segreduce_persistent_kernel<SumOp>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           kRingStages * kStageBytes);
+  DevicePlan none;
+  e = persistent_dispatch<SumOp>(nullptr, nullptr, 0, none, nullptr, true);
   if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(segreduce_persistent_kernel<MaxOp>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           kRingStages * kStageBytes);
+  e = persistent_dispatch<MaxOp>(nullptr, nullptr, 0, none, nullptr, true);
   if (e != cudaSuccess) return e;
   e = cudaFuncSetAttribute(segreduce_split_kernel<SumOp>,
                            cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           kStageBytes);
+                           kSplitBytes);
   if (e != cudaSuccess) return e;
   return cudaFuncSetAttribute(segreduce_split_kernel<MaxOp>,
                               cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              kStageBytes);
+                              kSplitBytes);
 }
 
 cudaError_t launch_segreduce_warp(int kind, const float *values,
@@ -504,17 +629,20 @@ cudaError_t launch_segreduce_split(int kind, const float *values, float *out,
                                    int32_t value_count, const DevicePlan &plan,
                                    cudaStream_t stream, const Probe *probe) {
   if (plan.task_count == 0) return cudaSuccess;
+  const unsigned grid =
+      (unsigned)((plan.task_count + kSplitWarps - 1) / kSplitWarps);
+  const Limits limits{value_count, plan.segment_count, plan.partial_slots};
   probe_begin(probe, stream);
   if (kind == SWG_KIND_SUM)
     segreduce_split_kernel<SumOp>
-        <<<(unsigned)plan.task_count, kConsumerThreads, kStageBytes, stream>>>(
-            values, out, value_count, plan.tasks, plan.offsets, plan.partials,
-            plan.control);
+        <<<grid, kSplitWarps * 32, kSplitBytes, stream>>>(
+            values, out, value_count, plan.tasks, plan.task_count,
+            plan.offsets, plan.partials, plan.control, limits);
   else
     segreduce_split_kernel<MaxOp>
-        <<<(unsigned)plan.task_count, kConsumerThreads, kStageBytes, stream>>>(
-            values, out, value_count, plan.tasks, plan.offsets, plan.partials,
-            plan.control);
+        <<<grid, kSplitWarps * 32, kSplitBytes, stream>>>(
+            values, out, value_count, plan.tasks, plan.task_count,
+            plan.offsets, plan.partials, plan.control, limits);
   probe_end(probe, stream);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
@@ -527,22 +655,14 @@ cudaError_t launch_segreduce_persistent(int kind, const float *values,
                                         cudaStream_t stream,
                                         const Probe *probe) {
   if (plan.task_count == 0) return cudaSuccess;
-  int grid = plan.sm_count;
-  if (grid > plan.task_count) grid = plan.task_count;
-  const size_t smem = (size_t)kRingStages * kStageBytes;
   probe_begin(probe, stream);
-  if (kind == SWG_KIND_SUM)
-    segreduce_persistent_kernel<SumOp>
-        <<<grid, kConsumerThreads + 32, smem, stream>>>(
-            values, out, value_count, plan.tasks, plan.task_count, plan.offsets,
-            plan.partials, plan.control);
-  else
-    segreduce_persistent_kernel<MaxOp>
-        <<<grid, kConsumerThreads + 32, smem, stream>>>(
-            values, out, value_count, plan.tasks, plan.task_count, plan.offsets,
-            plan.partials, plan.control);
+  cudaError_t e =
+      kind == SWG_KIND_SUM
+          ? persistent_dispatch<SumOp>(values, out, value_count, plan, stream,
+                                       false)
+          : persistent_dispatch<MaxOp>(values, out, value_count, plan, stream,
+                                       false);
   probe_end(probe, stream);
-  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   return launch_combine(kind, plan, out, stream);
 }
@@ -641,6 +761,7 @@ cudaError_t launch_segreduce_static(int kind, const float *values, float *out,
   dev.sm_count = sm_count;
   dev.tasks = d_tasks;
   dev.task_count = (int32_t)plan.tasks.size();
+  dev.segment_count = segment_count;
   dev.offsets = d_off;
   dev.splits = d_splits;
   dev.split_count = (int32_t)plan.splits.size();

@@ -101,7 +101,7 @@ def check_tasks_cover_everything(offsets, tasks, info):
         covered[vbegin] += 1
         covered[vbegin + vcount] -= 1
         if kind == 0:
-            assert 1 <= count <= 2048
+            assert 1 <= count <= info["tile_max_segments"]
             assert vbegin == offsets[seg]
             assert vbegin + vcount == offsets[seg + count]
             seen[seg:seg + count] += 1
@@ -134,6 +134,7 @@ def check_tasks_cover_everything(offsets, tasks, info):
 @pytest.mark.parametrize("lengths", [
     [0], [1], [128], [129], [4097], [33, 33, 33, 33], [1, 257, 2, 3837],
     [0, 2, 0, 0, 3], [0] * 5000, [8192], [8193], [2048, 2049, 1, 0, 100000],
+    [1024, 1025, 2047, 2048, 2049, 2050, 4095, 4096, 4097],
     [3] * 10000,
 ], ids=str)
 def test_planner_tasks_partition_the_input(lengths, native_library):
