@@ -57,6 +57,9 @@ def parse_arguments():
     parser.add_argument("--allgather", action="store_true")
     parser.add_argument("--e2e-steps", type=int, default=None)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--shrink", type=int, default=1,
+                        help="divide the c5 workload by this power of two "
+                             "(profiling captures only; not a bench value)")
     return parser.parse_args()
 
 
@@ -74,8 +77,18 @@ def measured_peak():
 # workload description
 # ---------------------------------------------------------------------------
 
-def describe_workload(name):
-    """(operation, kind, offsets or None, element count, description)."""
+def describe_workload(name, shrink=1):
+    """(operation, kind, offsets or None, description)."""
+    if name == "c5" and shrink > 1:
+        offsets = workloads.c5_offsets(
+            segments=(1 << 22) // shrink, total=(1 << 30) // shrink,
+            giants=max(1, 64 // shrink))
+        return "reduce", "sum", offsets, \
+            f"extreme skew shrunk {shrink}x (profiling only)"
+    if name == "c4" and shrink > 1:
+        return "softmax", None, \
+            workloads.c4_offsets(segments=262144 // shrink), \
+            f"softmax shrunk {shrink}x (profiling only)"
     if name == "c1":
         offsets = workloads.c1_offsets()
         return "reduce", "sum", offsets, "canonical 4096 segments U{0..2048}"
@@ -218,7 +231,8 @@ def run_reference(args):
     import oracle
 
     oracle.build()
-    operation, kind, offsets, text = describe_workload(args.workload)
+    operation, kind, offsets, text = describe_workload(args.workload,
+                                                       args.shrink)
     threads = oracle.max_threads()
     full_count = int(offsets[-1]) if offsets is not None else (1 << 28) - 37
     # probe the throughput on a small sample, then size the timed sample so
@@ -295,7 +309,8 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
-    operation, kind, offsets, text = describe_workload(args.workload)
+    operation, kind, offsets, text = describe_workload(args.workload,
+                                                       args.shrink)
     peak, peak_source = measured_peak()
 
     @sw.jit
@@ -343,7 +358,8 @@ def run_ours(args):
         else:
             out = torch.empty(count, device=device)
             bytes_per_step = workloads.softmax_bytes(count, segments)
-            plan = None
+            plan = plan_segments(torch.from_numpy(local_offsets), count,
+                                 op="softmax")
     gathered = None
     if args.allgather and world > 1 and operation == "reduce":
         longest = max(cuts[g + 1] - cuts[g] for g in range(world))
@@ -367,7 +383,7 @@ def run_ours(args):
                 padded[:segments].copy_(out)
                 dist.all_gather_into_tensor(gathered, padded)
         else:
-            launch_softmax_gpu(values, device_offsets, out,
+            launch_softmax_gpu(values, device_offsets, out, plan=plan,
                                schedule=args.schedule,
                                _validated=(count, segments))
 
@@ -401,11 +417,15 @@ def run_ours(args):
     # kernels per step: planned reduce = tile kernel + combine pass (when any
     # segment is split); everything else = one kernel
     per_step = 1
-    if plan is not None:
+    if plan is not None and operation == "reduce":
         info = plan.describe()
-        uses_tiles = args.schedule in ("auto", "split", "persistent")
+        uses_tiles = (args.schedule in ("split", "persistent")
+                      or (args.schedule == "auto" and info["schedule"] >= 3))
         if uses_tiles and info["split_segments"] > 0:
             per_step = 2
+    if plan is not None and operation == "softmax":
+        info = plan.describe()
+        per_step = sum(1 for n in info["softmax_buckets"] if n > 0)
     launches_per_step[0] = per_step
 
     # ---- end to end through the public call, host buffers ----

@@ -380,6 +380,17 @@ def launch_softmax_gpu(values, offsets, output, *, plan=None, schedule="auto",
 
     from . import _native
 
+    if plan is None and (
+        code in (_native.SCHED_SPLIT, _native.SCHED_PERSISTENT)
+        or (code == _native.SCHED_AUTO
+            and value_count + segment_count >= _PLAN_THRESHOLD)
+    ):
+        host = getattr(_last_host_offsets, "value", None)
+        if host is None or host.numel() != segment_count + 1:
+            host = offsets.detach().cpu()
+        plan = _cached_plan(
+            host, value_count, "softmax", torch.cuda.current_device()
+        )
     _last_host_offsets.value = None
     stream = torch.cuda.current_stream()
     _native.segsoftmax(

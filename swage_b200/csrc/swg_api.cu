@@ -104,6 +104,7 @@ void release(swg::DevicePlan &dev) {
   cudaFree(dev.offsets);
   cudaFree(dev.splits);
   cudaFree(dev.partials);
+  cudaFree(dev.softmax_segments);
   cudaFree(dev.control);
   dev = swg::DevicePlan();
 }
@@ -205,6 +206,15 @@ int swg_plan_create(const int32_t *host_offsets, int32_t segment_count,
   if (status == SWG_OK)
     status = upload<float>(&dev.partials, nullptr, 0,
                            (size_t)dev.partial_slots, "cudaMalloc(partials)");
+  for (int b = 0; b < swg::kSoftmaxBuckets; ++b) {
+    dev.softmax_begin[b] = plan->host.softmax_begin[b];
+    dev.softmax_count[b] = plan->host.softmax_count[b];
+  }
+  if (status == SWG_OK)
+    status = upload(&dev.softmax_segments, plan->host.softmax_segments.data(),
+                    plan->host.softmax_segments.size(),
+                    plan->host.softmax_segments.size(),
+                    "cudaMalloc(softmax buckets)");
   if (status == SWG_OK)
     status = upload<uint32_t>(&dev.control, nullptr, 0, 4,
                               "cudaMalloc(control)");
@@ -216,6 +226,7 @@ int swg_plan_create(const int32_t *host_offsets, int32_t segment_count,
   // host vectors are no longer needed once uploaded
   std::vector<swg::Task>().swap(plan->host.tasks);
   std::vector<swg::SplitSegment>().swap(plan->host.splits);
+  std::vector<int32_t>().swap(plan->host.softmax_segments);
   *plan_out = plan;
   return SWG_OK;
 }
@@ -325,7 +336,8 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
   int status = current_device(&device, &sm_count);
   if (status != SWG_OK) return status;
   if (plan) {
-    if (plan->host.segment_count != segment_count ||
+    if (plan->host.op != SWG_OP_REDUCE ||
+        plan->host.segment_count != segment_count ||
         plan->host.value_count > value_count || plan->dev.device != device) {
       swg::set_error(
           "plan was built for %d segments / %d values on device %d, launch "
@@ -443,15 +455,29 @@ int swg_segsoftmax_f32(const float *values, const int32_t *offsets, float *out,
   int device = 0, sm_count = 0;
   int status = current_device(&device, &sm_count);
   if (status != SWG_OK) return status;
-  (void)plan;
+  if (plan) {
+    if (plan->host.op != SWG_OP_SOFTMAX ||
+        plan->host.segment_count != segment_count ||
+        plan->host.value_count > value_count || plan->dev.device != device) {
+      swg::set_error("plan was not built for this softmax launch");
+      return SWG_ERR_PLAN_MISMATCH;
+    }
+  } else if (schedule == SWG_SCHED_SPLIT || schedule == SWG_SCHED_PERSISTENT) {
+    swg::set_error("the planned softmax schedule needs a plan");
+    return SWG_ERR_UNSUPPORTED;
+  }
   if (schedule == SWG_SCHED_AUTO)
-    schedule = (int64_t)value_count >= (int64_t)segment_count * 1024
+    schedule = plan ? SWG_SCHED_SPLIT
+               : (int64_t)value_count >= (int64_t)segment_count * 1024
                    ? SWG_SCHED_CTA
                    : SWG_SCHED_WARP;
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t e;
   const swg::Probe *probe = next_probe();
-  if (schedule == SWG_SCHED_WARP)
+  if (plan && (schedule == SWG_SCHED_SPLIT || schedule == SWG_SCHED_PERSISTENT))
+    e = swg::launch_segsoftmax_planned(values, offsets, out, plan->dev, s,
+                                       probe);
+  else if (schedule == SWG_SCHED_WARP)
     e = swg::launch_segsoftmax_warp(values, offsets, out, segment_count,
                                     sm_count, s, probe);
   else

@@ -20,6 +20,9 @@ struct DevicePlan {
   int32_t split_count = 0;
   float *partials = nullptr;       // one float per partial slot
   int32_t partial_slots = 0;
+  int32_t *softmax_segments = nullptr;  // bucketed segment ids
+  int32_t softmax_begin[kSoftmaxBuckets] = {0, 0, 0, 0};
+  int32_t softmax_count[kSoftmaxBuckets] = {0, 0, 0, 0};
   uint32_t *control = nullptr;     // [0] ticket, [1] finished, [2] error, [3] detail
 };
 
@@ -81,6 +84,13 @@ cudaError_t launch_segsoftmax_warp(const float *values, const int32_t *offsets,
                                    float *out, int32_t segment_count,
                                    int sm_count, cudaStream_t stream,
                                    const Probe *probe);
+
+// Planned softmax: the streamed bucket first, then the three
+// register-resident buckets.
+cudaError_t launch_segsoftmax_planned(const float *values,
+                                      const int32_t *offsets, float *out,
+                                      const DevicePlan &plan,
+                                      cudaStream_t stream, const Probe *probe);
 
 const char *last_error_text();
 

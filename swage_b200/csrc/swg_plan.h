@@ -40,14 +40,12 @@ struct SplitSegment {
   int32_t pad;
 };
 
-// Softmax units.  Short and medium segments are packed into tiles like PACK
-// tasks; a long segment is one task on its own.
-struct SoftmaxTask {
-  int32_t seg;
-  int32_t count;   // number of whole segments (1 for a long segment)
-  int32_t vbegin;
-  int32_t vcount;
-};
+// Softmax buckets by segment length: the first three are held in the
+// registers of a warp / a 128-thread CTA / a 512-thread CTA (16 values per
+// thread; read once, written once), longer segments are streamed by a CTA in
+// two sweeps.
+constexpr int kSoftmaxBuckets = 4;
+constexpr int kSoftmaxLimit[kSoftmaxBuckets - 1] = {512, 2048, 8192};
 
 struct HostPlan {
   int32_t segment_count = 0;
@@ -60,7 +58,12 @@ struct HostPlan {
   double mean_length = 0.0;
   std::vector<Task> tasks;
   std::vector<SplitSegment> splits;
-  std::vector<SoftmaxTask> softmax_tasks;
+  // softmax: ids of the non-empty segments, bucket after bucket; the last
+  // (streamed) bucket is ordered by decreasing length bin so that a
+  // round-robin over it is balanced
+  std::vector<int32_t> softmax_segments;
+  int32_t softmax_begin[kSoftmaxBuckets] = {0, 0, 0, 0};
+  int32_t softmax_count[kSoftmaxBuckets] = {0, 0, 0, 0};
   int32_t partial_slots = 0;
   int64_t pack_tasks = 0, chunk_tasks = 0;
 };

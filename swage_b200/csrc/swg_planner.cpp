@@ -160,6 +160,52 @@ void plan_reduce(const int32_t *offsets, int32_t segment_count,
   packer.flush();
 }
 
+// Softmax: bucket the non-empty segments by length.  Inside the streamed
+// bucket segments are emitted bin by bin from the longest (a counting sort on
+// the histogram bins), so that CTAs walking it round-robin get similar work.
+static inline int softmax_bucket(int64_t length) {
+  for (int b = 0; b < kSoftmaxBuckets - 1; ++b)
+    if (length <= kSoftmaxLimit[b]) return b;
+  return kSoftmaxBuckets - 1;
+}
+
+void plan_softmax(const int32_t *offsets, int32_t segment_count,
+                  HostPlan *plan) {
+  // slot = bucket for the resident buckets, 3 + (bins - 1 - bin) for the
+  // streamed one: one counting sort over all of them
+  const int slots = kSoftmaxBuckets - 1 + kHistogramBins;
+  std::vector<int64_t> fill((size_t)slots, 0), start((size_t)slots, 0);
+  auto slot_of = [](int64_t length) {
+    const int bucket = softmax_bucket(length);
+    if (bucket < kSoftmaxBuckets - 1) return bucket;
+    return kSoftmaxBuckets - 1 + (kHistogramBins - 1 - length_bin(length));
+  };
+  int64_t total = 0;
+  for (int32_t seg = 0; seg < segment_count; ++seg) {
+    const int64_t length = (int64_t)offsets[seg + 1] - offsets[seg];
+    if (length <= 0) continue;
+    fill[(size_t)slot_of(length)]++;
+    total++;
+  }
+  int64_t at = 0;
+  for (int slot = 0; slot < slots; ++slot) {
+    start[(size_t)slot] = at;
+    at += fill[(size_t)slot];
+  }
+  for (int b = 0; b < kSoftmaxBuckets; ++b) {
+    plan->softmax_begin[b] = (int32_t)start[(size_t)b];
+    plan->softmax_count[b] = (int32_t)fill[(size_t)b];
+  }
+  plan->softmax_count[kSoftmaxBuckets - 1] =
+      (int32_t)(total - start[(size_t)(kSoftmaxBuckets - 1)]);
+  plan->softmax_segments.assign((size_t)total, 0);
+  for (int32_t seg = 0; seg < segment_count; ++seg) {
+    const int64_t length = (int64_t)offsets[seg + 1] - offsets[seg];
+    if (length <= 0) continue;
+    plan->softmax_segments[(size_t)start[(size_t)slot_of(length)]++] = seg;
+  }
+}
+
 }  // namespace
 
 void build_host_plan(const int32_t *offsets, int32_t segment_count, int op,
@@ -176,6 +222,11 @@ void build_host_plan(const int32_t *offsets, int32_t segment_count, int op,
   }
   plan->mean_length =
       segment_count > 0 ? (double)plan->value_count / segment_count : 0.0;
+  if (op == SWG_OP_SOFTMAX) {
+    plan_softmax(offsets, segment_count, plan);
+    plan->schedule = SWG_SCHED_SPLIT;
+    return;
+  }
   plan_reduce(offsets, segment_count, plan);
   // Schedule choice from the histogram (measured on B200):
   //  - every segment of moderate length and none long: one warp per segment
@@ -198,12 +249,13 @@ std::string describe_host_plan(const HostPlan &plan) {
            "\"pack_tasks\": %lld, \"chunk_tasks\": %lld, "
            "\"split_segments\": %zu, \"partial_slots\": %d, "
            "\"tile_values\": %d, \"tile_max_segments\": %d, "
-           "\"long_segment\": %d, ",
+           "\"long_segment\": %d, \"softmax_buckets\": [%d, %d, %d, %d], ",
            plan.segment_count, plan.value_count, plan.op, plan.schedule,
            plan.mean_length, (long long)plan.max_length, plan.tasks.size(),
            (long long)plan.pack_tasks, (long long)plan.chunk_tasks,
            plan.splits.size(), plan.partial_slots, kTileValues, kTileMaxSegments,
-           kLongSegment);
+           kLongSegment, plan.softmax_count[0], plan.softmax_count[1],
+           plan.softmax_count[2], plan.softmax_count[3]);
   text += buffer;
   text += "\"histogram\": [";
   for (int bin = 0; bin < kHistogramBins; ++bin) {

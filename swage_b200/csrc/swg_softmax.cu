@@ -160,6 +160,252 @@ segsoftmax_warp_kernel(const float *__restrict__ values,
   }
 }
 
+// ---------------------------------------------------------------------------
+// Planned schedule.
+// ---------------------------------------------------------------------------
+
+// Resident buckets: a segment of at most kThreads * kResidentRows values is
+// held in the registers of kThreads threads (one warp, or a CTA of 128 or 512
+// threads): every value is read from HBM exactly once and written exactly
+// once, with coalesced 4-byte accesses, so no alignment case exists.
+constexpr int kResidentRows = 16;
+
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads == 32 ? 256 : kThreads,
+                                  kThreads == 512 ? 3 : 1)
+segsoftmax_resident_kernel(const float *__restrict__ values,
+                           const int32_t *__restrict__ offsets,
+                           float *__restrict__ out,
+                           const int32_t *__restrict__ segments,
+                           int32_t count) {
+  __shared__ float scratch[32];
+  const int t = kThreads == 32 ? (int)(threadIdx.x & 31) : (int)threadIdx.x;
+  const int64_t which =
+      kThreads == 32
+          ? (((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5)
+          : (int64_t)blockIdx.x;
+  if (which >= count) return;
+  const int32_t seg = __ldg(segments + which);
+  const int64_t begin = __ldg(offsets + seg);
+  const int length = (int)(__ldg(offsets + seg + 1) - begin);
+  const float *p = values + begin + t;
+  float x[kResidentRows];
+#pragma unroll
+  for (int r = 0; r < kResidentRows; ++r)
+    x[r] = (r * kThreads + t < length) ? __ldcs(p + r * kThreads)
+                                       : MaxOp::identity();
+  float m = x[0];
+#pragma unroll
+  for (int r = 1; r < kResidentRows; ++r) m = MaxOp::apply(m, x[r]);
+  m = kThreads == 32 ? warp_reduce<MaxOp>(m) : cta_reduce<MaxOp>(m, scratch);
+  float d = 0.0f;
+#pragma unroll
+  for (int r = 0; r < kResidentRows; ++r) {
+    // padding slots are masked: exp(-inf - m) is 0 only for an ordered m
+    const float e = (r * kThreads + t < length) ? exp_neg(x[r] - m) : 0.0f;
+    x[r] = e;
+    d += e;
+  }
+  d = kThreads == 32 ? warp_reduce<SumOp>(d) : cta_reduce<SumOp>(d, scratch);
+  const float inv = 1.0f / d;
+  float *o = out + begin + t;
+#pragma unroll
+  for (int r = 0; r < kResidentRows; ++r)
+    if (r * kThreads + t < length) __stcs(o + r * kThreads, x[r] * inv);
+}
+
+// Long bucket: one CTA per segment, two sweeps.  Sweep A reads the segment
+// from HBM once (loads carry an L2 evict-last policy so the lines stay for
+// sweep B) and keeps a running (maximum, sum of exp) pair per thread,
+// rescaling the sum only when a batch of 32 values raises the maximum; sweep
+// B re-reads the segment from L2 and writes the normalised values with
+// streaming stores.  Both sweeps issue a batch of independent 128-bit loads
+// before touching any of them.  Two 512-thread CTAs per SM keep the set of
+// live segments (296 of them) far below the L2 capacity.
+constexpr int kLongThreads = 512;
+constexpr int kLongBatch = 8;  // 128-bit loads in flight per thread, sweep A
+
+struct MaxSum {
+  float m, d;
+};
+
+__device__ __forceinline__ uint64_t policy_evict_last() {
+  uint64_t policy;
+  asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+
+__device__ __forceinline__ float4 ld_keep4(const float4 *p, uint64_t policy) {
+  float4 q;
+  asm volatile("ld.global.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=f"(q.x), "=f"(q.y), "=f"(q.z), "=f"(q.w)
+               : "l"(p), "l"(policy));
+  return q;
+}
+
+__device__ __forceinline__ float max4(const float4 q) {
+  return MaxOp::apply(MaxOp::apply(q.x, q.y), MaxOp::apply(q.z, q.w));
+}
+
+// s.m only ever takes ordered values: a NaN batch maximum fails `lm > s.m`.
+// NaN is tracked by the caller's NaN-propagating maximum instead.
+__device__ __forceinline__ void online_raise(MaxSum &s, const float lm) {
+  if (lm > s.m) {
+    s.d *= exp_neg(s.m - lm);
+    s.m = lm;
+  }
+}
+
+__device__ __forceinline__ float expsum4(const float4 q, const float m) {
+  return (exp_neg(q.x - m) + exp_neg(q.y - m)) +
+         (exp_neg(q.z - m) + exp_neg(q.w - m));
+}
+
+__device__ __forceinline__ void online_add1(MaxSum &s, const float v) {
+  online_raise(s, v);
+  // while only -inf has been seen every term is exp(-inf) = 0 against any
+  // finite final maximum; adding exp(-inf - -inf) = NaN would poison the sum
+  if (s.m > -CUDART_INF_F) s.d += exp_neg(v - s.m);
+}
+
+__device__ __forceinline__ float4 normalise4(const float4 q, const float m,
+                                             const float inv) {
+  float4 r;
+  r.x = exp_neg(q.x - m) * inv;
+  r.y = exp_neg(q.y - m) * inv;
+  r.z = exp_neg(q.z - m) * inv;
+  r.w = exp_neg(q.w - m) * inv;
+  return r;
+}
+
+__global__ void __launch_bounds__(kLongThreads, 2)
+segsoftmax_long_kernel(const float *__restrict__ values,
+                       const int32_t *__restrict__ offsets,
+                       float *__restrict__ out,
+                       const int32_t *__restrict__ segments, int32_t count) {
+  __shared__ float scratch[32];
+  const int tid = threadIdx.x;
+  const uint64_t keep = policy_evict_last();
+  constexpr int64_t T = kLongThreads;
+  for (int64_t j = blockIdx.x; j < count; j += gridDim.x) {
+    const int32_t seg = __ldg(segments + j);
+    const int64_t begin = __ldg(offsets + seg);
+    const int64_t end = __ldg(offsets + seg + 1);
+    const float *p = values + begin;
+    float *o = out + begin;
+    const int64_t len = end - begin;
+    int head = head_elems(p);
+    if (head > len) head = (int)len;
+    const float4 *body = reinterpret_cast<const float4 *>(p + head);
+    const int64_t nvec = (len - head) >> 2;
+    const int64_t tail = head + (nvec << 2);
+    const int tail_count = (int)(len - tail);
+
+    // ---- sweep A ----
+    MaxSum s{-CUDART_INF_F, 0.0f};
+    float any = MaxOp::identity();  // NaN-propagating maximum
+    if (tid < head) {
+      online_add1(s, p[tid]);
+      any = MaxOp::apply(any, p[tid]);
+    }
+    int64_t i = tid;
+    for (; i + (kLongBatch - 1) * T < nvec; i += kLongBatch * T) {
+      float4 q[kLongBatch];
+#pragma unroll
+      for (int k = 0; k < kLongBatch; ++k) q[k] = ld_keep4(body + i + k * T, keep);
+      float lm = max4(q[0]);
+#pragma unroll
+      for (int k = 1; k < kLongBatch; ++k) lm = MaxOp::apply(lm, max4(q[k]));
+      any = MaxOp::apply(any, lm);
+      online_raise(s, lm);
+      if (s.m > -CUDART_INF_F) {
+        float d0 = 0.0f, d1 = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kLongBatch; k += 2) {
+          d0 += expsum4(q[k], s.m);
+          d1 += expsum4(q[k + 1], s.m);
+        }
+        s.d += d0 + d1;
+      }
+    }
+    for (; i < nvec; i += T) {
+      const float4 q = ld_keep4(body + i, keep);
+      const float lm = max4(q);
+      any = MaxOp::apply(any, lm);
+      online_raise(s, lm);
+      if (s.m > -CUDART_INF_F) s.d += expsum4(q, s.m);
+    }
+    if (tid < tail_count) {
+      online_add1(s, p[tail + tid]);
+      any = MaxOp::apply(any, p[tail + tid]);
+    }
+    // combine: the segment maximum first (NaN-propagating), then the sums
+    // rescaled to it
+    const float m = cta_reduce<MaxOp>(any, scratch);
+    const float mine = s.d == 0.0f ? 0.0f : s.d * exp_neg(s.m - m);
+    const float d = cta_reduce<SumOp>(mine, scratch);
+    const float inv = 1.0f / d;
+
+    // ---- sweep B ----
+    const bool same_phase = (((uintptr_t)p ^ (uintptr_t)o) & 15u) == 0;
+    if (!same_phase) {
+      for (int64_t e = tid; e < len; e += T)
+        __stcs(o + e, exp_neg(p[e] - m) * inv);
+      continue;
+    }
+    if (tid < head) __stcs(o + tid, exp_neg(p[tid] - m) * inv);
+    float4 *obody = reinterpret_cast<float4 *>(o + head);
+    i = tid;
+    for (; i + 3 * T < nvec; i += 4 * T) {
+      const float4 q0 = __ldcs(body + i), q1 = __ldcs(body + i + T),
+                   q2 = __ldcs(body + i + 2 * T), q3 = __ldcs(body + i + 3 * T);
+      __stcs(obody + i, normalise4(q0, m, inv));
+      __stcs(obody + i + T, normalise4(q1, m, inv));
+      __stcs(obody + i + 2 * T, normalise4(q2, m, inv));
+      __stcs(obody + i + 3 * T, normalise4(q3, m, inv));
+    }
+    for (; i < nvec; i += T)
+      __stcs(obody + i, normalise4(__ldcs(body + i), m, inv));
+    if (tid < tail_count)
+      __stcs(o + tail + tid, exp_neg(p[tail + tid] - m) * inv);
+  }
+}
+
+cudaError_t launch_segsoftmax_planned(const float *values,
+                                      const int32_t *offsets, float *out,
+                                      const DevicePlan &plan,
+                                      cudaStream_t stream,
+                                      const Probe *probe) {
+  probe_begin(probe, stream);
+  // longest first: the streamed bucket keeps the whole GPU busy for longest,
+  // the resident buckets fill in behind it
+  const int32_t *list = plan.softmax_segments;
+  const int32_t n_stream = plan.softmax_count[3];
+  if (n_stream > 0) {
+    int grid = plan.sm_count * 2;
+    if (grid > n_stream) grid = n_stream;
+    segsoftmax_long_kernel<<<grid, kLongThreads, 0, stream>>>(
+        values, offsets, out, list + plan.softmax_begin[3], n_stream);
+  }
+  if (plan.softmax_count[2] > 0)
+    segsoftmax_resident_kernel<512>
+        <<<(unsigned)plan.softmax_count[2], 512, 0, stream>>>(
+            values, offsets, out, list + plan.softmax_begin[2],
+            plan.softmax_count[2]);
+  if (plan.softmax_count[1] > 0)
+    segsoftmax_resident_kernel<128>
+        <<<(unsigned)plan.softmax_count[1], 128, 0, stream>>>(
+            values, offsets, out, list + plan.softmax_begin[1],
+            plan.softmax_count[1]);
+  if (plan.softmax_count[0] > 0)
+    segsoftmax_resident_kernel<32>
+        <<<(unsigned)((plan.softmax_count[0] + 7) / 8), 256, 0, stream>>>(
+            values, offsets, out, list + plan.softmax_begin[0],
+            plan.softmax_count[0]);
+  probe_end(probe, stream);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_segsoftmax_cta(const float *values, const int32_t *offsets,
                                   float *out, int32_t segment_count,
                                   int sm_count, cudaStream_t stream,

@@ -10,7 +10,7 @@ from gpu_util import launch_softmax_gpu, offsets_from_lengths
 
 pytestmark = pytest.mark.gpu
 
-SCHEDULES = ["auto", "warp", "cta"]
+SCHEDULES = ["auto", "warp", "cta", "split"]
 
 
 def check_softmax(values, offsets, schedule, poison=True):
@@ -42,7 +42,9 @@ def check_softmax(values, offsets, schedule, poison=True):
 def test_small_cases(schedule):
     rng = np.random.default_rng(4)
     for lengths in ([1], [0], [0, 2, 0, 0, 3], [33, 33, 33, 33],
-                    [1, 257, 2, 3837], [4097], [129, 0, 128, 127, 1]):
+                    [1, 257, 2, 3837], [4097], [129, 0, 128, 127, 1],
+                    [511, 512, 513], [2047, 2048, 2049], [8191, 8192, 8193],
+                    [16384, 3, 20000]):
         offsets = offsets_from_lengths(lengths)
         values = (2 * rng.standard_normal(offsets[-1] + 2)).astype(np.float32)
         result = check_softmax(values, offsets, schedule)
@@ -78,16 +80,52 @@ def test_misaligned_pointers(schedule, shift):
     assert np.allclose(output.cpu().numpy(), exact, rtol=4e-6, atol=1e-10)
 
 
-def test_nan_and_empty_semantics():
+@pytest.mark.parametrize("schedule", SCHEDULES)
+def test_nan_and_empty_semantics(schedule):
     values = torch.tensor([1.0, float("nan"), 3.0, 4.0, 5.0], device="cuda")
     offsets = torch.tensor([0, 3, 3, 5], dtype=torch.int32, device="cuda")
     output = torch.zeros(5, device="cuda")
-    launch_softmax_gpu(values, offsets, output)
+    launch_softmax_gpu(values, offsets, output, schedule=schedule)
     torch.cuda.synchronize()
     host = output.cpu().numpy()
     assert np.isnan(host[:3]).all()
     assert np.allclose(host[3:], [1 / (1 + np.e), np.e / (1 + np.e)],
                        rtol=1e-6)
+
+
+@pytest.mark.parametrize("schedule", SCHEDULES)
+@pytest.mark.parametrize("length", [5, 700, 1024, 1025, 5000, 70000])
+def test_infinities_follow_the_oracle(schedule, length):
+    """-inf entries get probability 0; a NaN or +inf poisons its segment."""
+    rng = np.random.default_rng(length)
+    base = (2 * rng.standard_normal(length)).astype(np.float32)
+    cases = []
+    minus = base.copy()
+    minus[rng.choice(length, size=max(1, length // 3), replace=False)] = -np.inf
+    cases.append(minus)
+    front = base.copy()
+    front[: length - 1] = -np.inf          # one finite value at the very end
+    cases.append(front)
+    nan = base.copy()
+    nan[length // 2] = np.nan
+    cases.append(nan)
+    plus = base.copy()
+    plus[length // 3] = np.inf
+    cases.append(plus)
+    cases.append(np.full(length, -np.inf, dtype=np.float32))
+    values = np.concatenate(cases)
+    offsets = (np.arange(len(cases) + 1) * length).astype(np.int32)
+    output = torch.full((values.size,), 7.0, device="cuda")
+    launch_softmax_gpu(torch.as_tensor(values).cuda(),
+                       torch.as_tensor(offsets).cuda(), output,
+                       schedule=schedule)
+    torch.cuda.synchronize()
+    got = output.cpu().numpy().astype(np.float64)
+    with np.errstate(invalid="ignore"):
+        exact = oracle.segsoftmax_f64(values, offsets)
+    assert np.array_equal(np.isnan(got), np.isnan(exact))
+    finite = ~np.isnan(exact)
+    assert np.allclose(got[finite], exact[finite], rtol=4e-6, atol=1e-10)
 
 
 def test_rejects_aliasing_and_short_output():
@@ -120,6 +158,13 @@ def test_full_size_softmax_properties():
     output = torch.empty(count, device="cuda")
     launch_softmax_gpu(values, device_offsets, output)
     torch.cuda.synchronize()
+    # the planned schedule (chosen automatically at this size) and the
+    # plan-free CTA schedule agree to rounding
+    other = torch.empty(count, device="cuda")
+    launch_softmax_gpu(values, device_offsets, other, schedule="cta")
+    torch.cuda.synchronize()
+    assert float((output - other).abs().max()) < 1e-6
+    del other
     assert bool(((output >= 0) & (output <= 1)).all())
     lengths = torch.as_tensor(np.diff(offsets).astype(np.int64)).cuda()
     sums = torch.segment_reduce(output.double(), "sum", lengths=lengths)
