@@ -11,6 +11,8 @@
 // a segment that does not fit in registers or shared memory are served by L2
 // (loads keep the default caching policy on the first sweep for that reason,
 // stores are streaming).
+#include <mutex>
+
 #include "swg_common.cuh"
 #include "swg_launch.h"
 
@@ -371,14 +373,50 @@ segsoftmax_long_kernel(const float *__restrict__ values,
   }
 }
 
+// Side streams so the four bucket kernels of one call run concurrently (the
+// streamed bucket leaves half of every SM's thread slots free): created once
+// per device, joined back into the caller's stream before the call returns
+// control to it.
+namespace {
+struct Fork {
+  bool ready = false;
+  cudaStream_t side[3];
+  cudaEvent_t begin;
+  cudaEvent_t done[3];
+};
+std::mutex g_fork_lock;
+Fork g_fork[64];
+
+cudaError_t fork_for(int device, Fork **fork) {
+  std::lock_guard<std::mutex> guard(g_fork_lock);
+  Fork &f = g_fork[device];
+  if (!f.ready) {
+    cudaError_t e =
+        cudaEventCreateWithFlags(&f.begin, cudaEventDisableTiming);
+    for (int i = 0; i < 3 && e == cudaSuccess; ++i) {
+      e = cudaStreamCreateWithFlags(&f.side[i], cudaStreamNonBlocking);
+      if (e == cudaSuccess)
+        e = cudaEventCreateWithFlags(&f.done[i], cudaEventDisableTiming);
+    }
+    if (e != cudaSuccess) return e;
+    f.ready = true;
+  }
+  *fork = &f;
+  return cudaSuccess;
+}
+}  // namespace
+
 cudaError_t launch_segsoftmax_planned(const float *values,
                                       const int32_t *offsets, float *out,
                                       const DevicePlan &plan,
                                       cudaStream_t stream,
                                       const Probe *probe) {
+  Fork *fork = nullptr;
+  cudaError_t e = fork_for(plan.device, &fork);
+  if (e != cudaSuccess) return e;
   probe_begin(probe, stream);
-  // longest first: the streamed bucket keeps the whole GPU busy for longest,
-  // the resident buckets fill in behind it
+  e = cudaEventRecord(fork->begin, stream);
+  if (e != cudaSuccess) return e;
   const int32_t *list = plan.softmax_segments;
   const int32_t n_stream = plan.softmax_count[3];
   if (n_stream > 0) {
@@ -387,21 +425,28 @@ cudaError_t launch_segsoftmax_planned(const float *values,
     segsoftmax_long_kernel<<<grid, kLongThreads, 0, stream>>>(
         values, offsets, out, list + plan.softmax_begin[3], n_stream);
   }
-  if (plan.softmax_count[2] > 0)
-    segsoftmax_resident_kernel<512>
-        <<<(unsigned)plan.softmax_count[2], 512, 0, stream>>>(
-            values, offsets, out, list + plan.softmax_begin[2],
-            plan.softmax_count[2]);
-  if (plan.softmax_count[1] > 0)
-    segsoftmax_resident_kernel<128>
-        <<<(unsigned)plan.softmax_count[1], 128, 0, stream>>>(
-            values, offsets, out, list + plan.softmax_begin[1],
-            plan.softmax_count[1]);
-  if (plan.softmax_count[0] > 0)
-    segsoftmax_resident_kernel<32>
-        <<<(unsigned)((plan.softmax_count[0] + 7) / 8), 256, 0, stream>>>(
-            values, offsets, out, list + plan.softmax_begin[0],
-            plan.softmax_count[0]);
+  for (int b = 2; b >= 0; --b) {
+    const int32_t n = plan.softmax_count[b];
+    if (n == 0) continue;
+    cudaStream_t side = fork->side[b];
+    e = cudaStreamWaitEvent(side, fork->begin, 0);
+    if (e != cudaSuccess) return e;
+    const int32_t *bucket = list + plan.softmax_begin[b];
+    if (b == 2)
+      segsoftmax_resident_kernel<512>
+          <<<(unsigned)n, 512, 0, side>>>(values, offsets, out, bucket, n);
+    else if (b == 1)
+      segsoftmax_resident_kernel<128>
+          <<<(unsigned)n, 128, 0, side>>>(values, offsets, out, bucket, n);
+    else
+      segsoftmax_resident_kernel<32>
+          <<<(unsigned)((n + 7) / 8), 256, 0, side>>>(values, offsets, out,
+                                                      bucket, n);
+    e = cudaEventRecord(fork->done[b], side);
+    if (e != cudaSuccess) return e;
+    e = cudaStreamWaitEvent(stream, fork->done[b], 0);
+    if (e != cudaSuccess) return e;
+  }
   probe_end(probe, stream);
   return cudaGetLastError();
 }
