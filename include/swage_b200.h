@@ -191,11 +191,13 @@ int swg_shard_offsets(const int32_t *host_offsets, int32_t segment_count,
  * the only kernel otherwise).  The library records a pair of CUDA events
  * around that kernel on the launch stream.  swg_profile_stop synchronises
  * those events, writes up to `capacity` durations in milliseconds and the
- * number of launches seen.  At most `capacity` launches given to start are
- * recorded; later ones run untimed.  No reference counterpart: the reference
+ * number of launches recorded.  Every `stride`-th call is recorded (stride 1 =
+ * every call; a pair of event records costs a few microseconds of stream
+ * time, so a sparse sample perturbs a timed loop less), at most `capacity` of
+ * them; the rest run untimed.  No reference counterpart: the reference
  * has no timing facility (its debugging switches are the SWAGE_DUMP_*
  * variables, python/swage/_runtime.py:381-396). */
-int swg_profile_start(int32_t capacity);
+int swg_profile_start(int32_t capacity, int32_t stride);
 int swg_profile_stop(float *milliseconds, int32_t capacity, int32_t *count);
 
 #ifdef __cplusplus

@@ -86,7 +86,7 @@ def _declare(lib):
     lib.swg_segreduce_f32_noalloc.argtypes = [
         c_int, ptr, ptr, ptr, c_i32, c_i32, ptr]
     lib.swg_profile_start.restype = c_int
-    lib.swg_profile_start.argtypes = [c_i32]
+    lib.swg_profile_start.argtypes = [c_i32, c_i32]
     lib.swg_profile_stop.restype = c_int
     lib.swg_profile_stop.argtypes = [ptr, c_i32, ctypes.POINTER(c_i32)]
 
@@ -229,8 +229,8 @@ def shard_offsets(host_ptr, segment_count, shards):
     return list(cuts)
 
 
-def profile_start(capacity):
-    check(library().swg_profile_start(capacity), "swg_profile_start")
+def profile_start(capacity, stride=1):
+    check(library().swg_profile_start(capacity, stride), "swg_profile_start")
 
 
 def profile_stop(capacity):

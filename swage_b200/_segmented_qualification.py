@@ -293,12 +293,17 @@ def _schedule_code(schedule):
     return _native.SCHEDULES[schedule]
 
 
+_thread_limits = {}
+
+
 def _check_block(block_size, torch):
     if type(block_size) is not int or block_size <= 0:
         raise ValueError("block size must be a positive integer")
-    limit = torch.cuda.get_device_properties(
-        torch.cuda.current_device()
-    ).max_threads_per_block
+    device = torch.cuda.current_device()
+    limit = _thread_limits.get(device)
+    if limit is None:
+        limit = torch.cuda.get_device_properties(device).max_threads_per_block
+        _thread_limits[device] = limit
     if block_size > limit:
         raise ValueError(
             f"block size {block_size} exceeds device limit {limit}"

@@ -30,13 +30,16 @@ struct Profile {
   bool active = false;
   std::vector<swg::Probe> probes;
   size_t used = 0;
+  int64_t calls = 0;
+  int64_t stride = 1;
 };
 Profile g_profile;
 
 const swg::Probe *next_probe() {
   std::lock_guard<std::mutex> guard(g_lock);
-  if (!g_profile.active || g_profile.used >= g_profile.probes.size())
-    return nullptr;
+  if (!g_profile.active) return nullptr;
+  const bool sampled = (g_profile.calls++ % g_profile.stride) == 0;
+  if (!sampled || g_profile.used >= g_profile.probes.size()) return nullptr;
   return &g_profile.probes[g_profile.used++];
 }
 
@@ -47,6 +50,7 @@ void drop_probes() {
   }
   g_profile.probes.clear();
   g_profile.used = 0;
+  g_profile.calls = 0;
   g_profile.active = false;
 }
 
@@ -191,6 +195,7 @@ int swg_plan_create(const int32_t *host_offsets, int32_t segment_count,
   dev.task_count = (int32_t)plan->host.tasks.size();
   dev.segment_count = segment_count;
   dev.split_count = (int32_t)plan->host.splits.size();
+  dev.big_split_count = plan->host.big_split_count;
   dev.partial_slots = plan->host.partial_slots;
   const size_t noffsets = (size_t)segment_count + 1;
   const size_t padded = ((noffsets + 3) / 4) * 4 + 4;
@@ -493,14 +498,16 @@ int swg_shard_offsets(const int32_t *host_offsets, int32_t segment_count,
   return swg::shard_offsets(host_offsets, segment_count, shards, seg_begin);
 }
 
-int swg_profile_start(int32_t capacity) {
+int swg_profile_start(int32_t capacity, int32_t stride) {
   swg::clear_error();
-  if (capacity < 1 || capacity > (1 << 20)) {
-    swg::set_error("swg_profile_start: capacity must be in [1, 2^20]");
+  if (capacity < 1 || capacity > (1 << 20) || stride < 1) {
+    swg::set_error(
+        "swg_profile_start: capacity must be in [1, 2^20] and stride >= 1");
     return SWG_ERR_INVALID_ARGUMENT;
   }
   std::lock_guard<std::mutex> guard(g_lock);
   drop_probes();
+  g_profile.stride = stride;
   g_profile.probes.reserve((size_t)capacity);
   for (int32_t i = 0; i < capacity; ++i) {
     swg::Probe probe;

@@ -18,6 +18,7 @@ struct DevicePlan {
   int32_t *offsets = nullptr;      // aligned, padded copy of the CSR offsets
   SplitSegment *splits = nullptr;
   int32_t split_count = 0;
+  int32_t big_split_count = 0;     // leading splits that get a CTA each
   float *partials = nullptr;       // one float per partial slot
   int32_t partial_slots = 0;
   int32_t *softmax_segments = nullptr;  // bucketed segment ids

@@ -15,6 +15,7 @@ namespace swg {
 constexpr int kTileValues = 2048;      // values per tile task (8 KiB of fp32)
 constexpr int kTileMaxSegments = 512;  // segments per packed tile task
 constexpr int kLongSegment = 1024;     // longer segments become chunk tasks
+constexpr int kBigSplit = 256;         // partials from which a merge gets a whole CTA
 constexpr int kHistogramBins = 33;     // bin b: len == 0 | 2^(b-1) <= len < 2^b
 
 // One schedulable unit.  16 bytes so a task is one 128-bit load.
@@ -65,6 +66,7 @@ struct HostPlan {
   int32_t softmax_begin[kSoftmaxBuckets] = {0, 0, 0, 0};
   int32_t softmax_count[kSoftmaxBuckets] = {0, 0, 0, 0};
   int32_t partial_slots = 0;
+  int32_t big_split_count = 0;  // splits are ordered big ones first
   int64_t pack_tasks = 0, chunk_tasks = 0;
 };
 

@@ -158,6 +158,13 @@ void plan_reduce(const int32_t *offsets, int32_t segment_count,
     }
   }
   packer.flush();
+  // merge pass: segments with many partials first, a CTA each
+  auto big = [](const SplitSegment &split) {
+    return split.slot_count >= kBigSplit;
+  };
+  auto middle =
+      std::stable_partition(plan->splits.begin(), plan->splits.end(), big);
+  plan->big_split_count = (int32_t)(middle - plan->splits.begin());
 }
 
 // Softmax: bucket the non-empty segments by length.  Inside the streamed

@@ -359,6 +359,9 @@ segreduce_split_kernel(const float *__restrict__ values,
   __shared__ WarpScratch scratch[kSplitWarps];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int mis = (int)(((uintptr_t)values >> 2) & 3);
+  // let the merge kernel that follows be placed as soon as slots free up; it
+  // waits for this grid to finish before it reads a partial
+  asm volatile("griddepcontrol.launch_dependents;");
   const int64_t index = (int64_t)blockIdx.x * kSplitWarps + warp;
   if (index >= task_count) return;
   if (lane == 0) {
@@ -493,24 +496,52 @@ segreduce_persistent_kernel(const float *__restrict__ values,
 }
 
 // Second pass of the split / persistent schedules: merge the partials of each
-// chunked segment in slot order (fixed tree: lane-strided, then butterfly).
+// chunked segment in a fixed order.  The plan lists the segments with at
+// least kBigSplit partials first: each of those gets a whole CTA (CTAs
+// 0..big_count-1), the rest get one warp each.  Thread-strided partial sums
+// then a butterfly, so the result does not depend on timing.
+// Launched with programmatic stream serialisation: its CTAs may be placed
+// while the tile kernel drains, and wait here until that kernel's writes are
+// visible.
+constexpr int kCombineThreads = 256;
+
 template <class Op>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kCombineThreads)
 segreduce_combine_kernel(const SplitSegment *__restrict__ splits,
-                         int32_t split_count,
+                         int32_t split_count, int32_t big_count,
                          const float *__restrict__ partials,
                          float *__restrict__ out) {
+  __shared__ float scratch[32];
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int lane = threadIdx.x & 31;
-  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  for (int64_t j = warp; j < split_count; j += nwarps) {
-    const SplitSegment s = splits[j];
-    float acc = Op::identity();
-    for (int i = lane; i < s.slot_count; i += 32)
-      acc = Op::apply(acc, partials[s.slot_begin + i]);
-    acc = warp_reduce<Op>(acc);
-    if (lane == 0) out[s.seg] = acc;
+  if ((int32_t)blockIdx.x < big_count) {
+    const SplitSegment s = splits[blockIdx.x];
+    const float *p = partials + s.slot_begin;
+    float a0 = Op::identity(), a1 = Op::identity(), a2 = Op::identity(),
+          a3 = Op::identity();
+    int i = threadIdx.x;
+    for (; i + 3 * kCombineThreads < s.slot_count; i += 4 * kCombineThreads) {
+      a0 = Op::apply(a0, p[i]);
+      a1 = Op::apply(a1, p[i + kCombineThreads]);
+      a2 = Op::apply(a2, p[i + 2 * kCombineThreads]);
+      a3 = Op::apply(a3, p[i + 3 * kCombineThreads]);
+    }
+    for (; i < s.slot_count; i += kCombineThreads) a0 = Op::apply(a0, p[i]);
+    const float r = cta_reduce<Op>(
+        Op::apply(Op::apply(a0, a1), Op::apply(a2, a3)), scratch);
+    if (threadIdx.x == 0) out[s.seg] = r;
+    return;
   }
+  const int64_t j = (int64_t)big_count +
+                    ((int64_t)(blockIdx.x - big_count) * kCombineThreads +
+                     threadIdx.x) / 32;
+  if (j >= split_count) return;
+  const SplitSegment s = splits[j];
+  float acc = Op::identity();
+  for (int i = lane; i < s.slot_count; i += 32)
+    acc = Op::apply(acc, partials[s.slot_begin + i]);
+  acc = warp_reduce<Op>(acc);
+  if (lane == 0) out[s.seg] = acc;
 }
 
 // ---------------------------------------------------------------------------
@@ -610,19 +641,32 @@ cudaError_t launch_segreduce_cta(int kind, const float *values,
   return cudaGetLastError();
 }
 
+template <class Op>
+static cudaError_t launch_combine_as(const DevicePlan &plan, float *out,
+                                     cudaStream_t stream) {
+  const int32_t small = plan.split_count - plan.big_split_count;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(
+      (unsigned)((int64_t)plan.big_split_count + ((int64_t)small + 7) / 8));
+  config.blockDim = dim3(kCombineThreads);
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, segreduce_combine_kernel<Op>,
+                            (const SplitSegment *)plan.splits,
+                            plan.split_count, plan.big_split_count,
+                            (const float *)plan.partials, out);
+}
+
 static cudaError_t launch_combine(int kind, const DevicePlan &plan, float *out,
                                   cudaStream_t stream) {
   if (plan.split_count == 0) return cudaSuccess;
-  int64_t grid = ((int64_t)plan.split_count + 7) / 8;
-  const int64_t cap = (int64_t)plan.sm_count * 8;
-  if (grid > cap) grid = cap;
-  if (kind == SWG_KIND_SUM)
-    segreduce_combine_kernel<SumOp><<<(unsigned)grid, 256, 0, stream>>>(
-        plan.splits, plan.split_count, plan.partials, out);
-  else
-    segreduce_combine_kernel<MaxOp><<<(unsigned)grid, 256, 0, stream>>>(
-        plan.splits, plan.split_count, plan.partials, out);
-  return cudaGetLastError();
+  return kind == SWG_KIND_SUM ? launch_combine_as<SumOp>(plan, out, stream)
+                              : launch_combine_as<MaxOp>(plan, out, stream);
 }
 
 cudaError_t launch_segreduce_split(int kind, const float *values, float *out,
@@ -765,6 +809,7 @@ cudaError_t launch_segreduce_static(int kind, const float *values, float *out,
   dev.offsets = d_off;
   dev.splits = d_splits;
   dev.split_count = (int32_t)plan.splits.size();
+  dev.big_split_count = plan.big_split_count;
   dev.partials = d_partials;
   dev.partial_slots = plan.partial_slots;
   dev.control = d_control;
