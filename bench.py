@@ -297,7 +297,7 @@ def run_ours(args):
 
     import swage_b200 as sw
     import swage_b200.language as sl
-    from swage_b200 import _native
+    from swage_b200 import _native, multi_gpu
     from swage_b200._segmented_qualification import (
         launch_gpu,
         launch_softmax_gpu,
@@ -344,9 +344,10 @@ def run_ours(args):
         local_offsets = None
     else:
         total_elements = int(offsets[-1])
-        cuts = _native.shard_offsets(offsets.ctypes.data, len(offsets) - 1,
-                                     world)
-        local_offsets, begin, end = workloads.shard(offsets, cuts, rank)
+        host_offsets = torch.from_numpy(offsets)
+        cuts = multi_gpu.shard_cuts(host_offsets, world)
+        local, begin, end = multi_gpu.local_shard(host_offsets, cuts, rank)
+        local_offsets = local.numpy()
         full = make_values(args.workload, offsets, device)
         values = full[begin:end].clone() if world > 1 else full
         del full
@@ -363,11 +364,7 @@ def run_ours(args):
             bytes_per_step = workloads.softmax_bytes(count, segments)
             plan = plan_segments(torch.from_numpy(local_offsets), count,
                                  op="softmax")
-    gathered = None
-    if args.allgather and world > 1 and operation == "reduce":
-        longest = max(cuts[g + 1] - cuts[g] for g in range(world))
-        padded = torch.zeros(longest, device=device)
-        gathered = torch.empty(world * longest, device=device)
+    gather = args.allgather and world > 1 and operation == "reduce"
 
     launches_per_step = [0]
 
@@ -382,9 +379,8 @@ def run_ours(args):
             launch_gpu(values, device_offsets, out, kind, args.block,
                        plan=plan, schedule=args.schedule,
                        _validated=(count, segments))
-            if gathered is not None:
-                padded[:segments].copy_(out)
-                dist.all_gather_into_tensor(gathered, padded)
+            if gather:
+                multi_gpu.gather_results(out, cuts)
         else:
             launch_softmax_gpu(values, device_offsets, out, plan=plan,
                                schedule=args.schedule,
@@ -541,7 +537,7 @@ def run_ours(args):
                 "sharding": f"{world} element-balanced contiguous segment "
                             "ranges, no collective"
                             + (" + NCCL all-gather of results"
-                               if gathered is not None else ""),
+                               if gather else ""),
                 "l2": "inputs larger than L2" if bytes_per_step > 3e8
                       else "inputs fit in L2 (warm)",
             },

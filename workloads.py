@@ -109,14 +109,6 @@ def c3_values(offsets, device, seed=SEEDS["c3"]):
     return values
 
 
-def shard(offsets, cuts, rank):
-    """Rebased offsets and the value range of shard ``rank``."""
-    first, last = cuts[rank], cuts[rank + 1]
-    begin, end = int(offsets[first]), int(offsets[last])
-    local = (offsets[first:last + 1].astype(np.int64) - begin).astype(np.int32)
-    return local, begin, end
-
-
 def reduce_bytes(value_count, segment_count):
     """Algorithmic bytes of one segmented sum or max."""
     return 4 * value_count + 4 * (segment_count + 1) + 4 * segment_count
