@@ -13,8 +13,10 @@ namespace swg {
 
 // Geometry shared by the planner and the tile kernels.
 constexpr int kTileValues = 2048;      // values per tile task (8 KiB of fp32)
-constexpr int kTileMaxSegments = 512;  // segments per packed tile task
-constexpr int kLongSegment = 1024;     // longer segments become chunk tasks
+constexpr int kTileItems = 2032;       // values + segments of a packed task:
+                                       // its offsets share the tile's stage
+constexpr int kTileMaxSegments = 1024; // segments per packed tile task
+constexpr int kLongSegment = 1792;     // longer segments become chunk tasks
 constexpr int kBigSplit = 256;         // partials from which a merge gets a whole CTA
 constexpr int kHistogramBins = 33;     // bin b: len == 0 | 2^(b-1) <= len < 2^b
 

@@ -103,8 +103,9 @@ struct Packer {
   }
 
   void add(int32_t seg, int32_t start, int32_t length) {
-    if (nseg > 0 &&
-        (vcount + length > kTileValues || nseg >= kTileMaxSegments))
+    // a packed task's values and its offsets share one shared-memory stage
+    if (nseg > 0 && (vcount + length + nseg + 1 > kTileItems ||
+                     nseg >= kTileMaxSegments))
       flush();
     if (nseg == 0) {
       seg_begin = seg;
@@ -255,12 +256,14 @@ std::string describe_host_plan(const HostPlan &plan) {
            "\"mean_length\": %.3f, \"max_length\": %lld, \"tasks\": %zu, "
            "\"pack_tasks\": %lld, \"chunk_tasks\": %lld, "
            "\"split_segments\": %zu, \"partial_slots\": %d, "
-           "\"tile_values\": %d, \"tile_max_segments\": %d, "
+           "\"tile_values\": %d, \"tile_items\": %d, "
+           "\"tile_max_segments\": %d, "
            "\"long_segment\": %d, \"softmax_buckets\": [%d, %d, %d, %d], ",
            plan.segment_count, plan.value_count, plan.op, plan.schedule,
            plan.mean_length, (long long)plan.max_length, plan.tasks.size(),
            (long long)plan.pack_tasks, (long long)plan.chunk_tasks,
-           plan.splits.size(), plan.partial_slots, kTileValues, kTileMaxSegments,
+           plan.splits.size(), plan.partial_slots, kTileValues, kTileItems,
+           kTileMaxSegments,
            kLongSegment, plan.softmax_count[0], plan.softmax_count[1],
            plan.softmax_count[2], plan.softmax_count[3]);
   text += buffer;

@@ -78,19 +78,26 @@ __global__ void segreduce_cta_kernel(const float *__restrict__ values,
 // ---------------------------------------------------------------------------
 constexpr int kLaneSegment = 16;    // reduced by a single lane inside a tile
 constexpr int kGroupSegment = 256;  // up to here by a group of eight lanes
+// One stage holds the task's values and, for a packed task, its offsets right
+// behind them (the planner bounds values + segments by kTileItems so both
+// fit): element i sits at tile[i - origin], offset j of the aligned offsets
+// range at ((int*)tile)[offsets_base + j].
 constexpr int kTileFloats = kTileValues + 8;
-constexpr int kTileOffsets = kTileMaxSegments + 8;
-constexpr int kStageTileBytes = kTileFloats * 4;
-constexpr int kStageOffsetBytes = kTileOffsets * 4;
-constexpr int kStageBytes =
-    ((kStageTileBytes + kStageOffsetBytes + 127) / 128) * 128;
+constexpr int kStageBytes = ((kTileFloats * 4 + 127) / 128) * 128;
+static_assert(kTileItems + 3 + 3 + 8 <= kTileFloats,
+              "values, padding and offsets of a packed task fit one stage");
+
+// First tile slot of the offsets of a packed task: the 16-byte line after
+// its values.
+__device__ __forceinline__ int offsets_base(int shift, int vcount) {
+  return (shift + vcount + 3) & ~3;
+}
 constexpr uint32_t kTaskStop = 15u;  // sentinel kind: no more tasks
 
 constexpr int kSplitWarps = 4;       // split: tasks per CTA, one stage each
 
 struct Stage {
   float *tile;
-  int32_t *soff;
 };
 
 // Per-warp lists of the segments (of the current 32) that more than one lane
@@ -105,7 +112,6 @@ __device__ __forceinline__ Stage stage_at(unsigned char *base, int index) {
   unsigned char *p = base + (size_t)index * kStageBytes;
   Stage s;
   s.tile = reinterpret_cast<float *>(p);
-  s.soff = reinterpret_cast<int32_t *>(p + kStageTileBytes);
   return s;
 }
 
@@ -158,6 +164,7 @@ __device__ __forceinline__ bool task_ok(const Task &t, const Limits &limits) {
     return false;
   if (kind == kTaskPack)
     return t.count >= 1 && t.count <= kTileMaxSegments &&
+           vcount + t.count <= kTileItems &&
            (int64_t)t.seg + t.count <= limits.segment_count;
   if (kind == kTaskChunk)
     return t.count >= -1 && t.count < limits.partial_slots;
@@ -203,7 +210,9 @@ __device__ __forceinline__ void issue_task(const Task &task,
   }
   mbar_arrive_expect_tx(full, bytes_v + bytes_o);
   if (bytes_v) bulk_g2s(stage.tile + (lo - origin), values + lo, bytes_v, full);
-  if (bytes_o) bulk_g2s(stage.soff, d_off + o_lo, bytes_o, full);
+  if (bytes_o)
+    bulk_g2s(stage.tile + offsets_base((int)(vb - origin), (int)(ve - vb)),
+             d_off + o_lo, bytes_o, full);
 }
 
 // Warp-collective: reduce one staged task.
@@ -265,7 +274,9 @@ __device__ __forceinline__ void process_task(const Task &task,
   // Listed results come back through the warp's scratch to their owning
   // lanes, so the 32 results leave in one coalesced store.  Tile-relative
   // bounds of segment k are soff[k] - origin and soff[k + 1] - origin.
-  const int32_t *soff = stage.soff + (task.seg & 3);
+  const int32_t *soff =
+      reinterpret_cast<const int32_t *>(tile + offsets_base(shift, vcount)) +
+      (task.seg & 3);
   const int origin = task.vbegin - shift;
   const unsigned below = (1u << lane) - 1u;
   const int group = lane >> 3, sub = lane & 7;
@@ -578,7 +589,7 @@ static cudaError_t persistent_dispatch(const float *values, float *out,
                                        int32_t value_count,
                                        const DevicePlan &plan,
                                        cudaStream_t stream, bool configure) {
-  return persistent_launch<Op, 7, 3>(values, out, value_count, plan, stream,
+  return persistent_launch<Op, 9, 3>(values, out, value_count, plan, stream,
                                      configure);
 }
 

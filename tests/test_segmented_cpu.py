@@ -102,6 +102,7 @@ def check_tasks_cover_everything(offsets, tasks, info):
         covered[vbegin + vcount] -= 1
         if kind == 0:
             assert 1 <= count <= info["tile_max_segments"]
+            assert vcount + count <= info["tile_items"]
             assert vbegin == offsets[seg]
             assert vbegin + vcount == offsets[seg + count]
             seen[seg:seg + count] += 1
