@@ -94,7 +94,10 @@ __device__ __forceinline__ int offsets_base(int shift, int vcount) {
 }
 constexpr uint32_t kTaskStop = 15u;  // sentinel kind: no more tasks
 
-constexpr int kSplitWarps = 4;       // split: tasks per CTA, one stage each
+#ifndef SWG_SPLIT_WARPS
+#define SWG_SPLIT_WARPS 2
+#endif
+constexpr int kSplitWarps = SWG_SPLIT_WARPS;  // split: tasks per CTA, one stage each
 
 struct Stage {
   float *tile;
