@@ -219,13 +219,28 @@ segsoftmax_resident_kernel(const float *__restrict__ values,
 // Long bucket: one CTA per segment, two sweeps.  Sweep A reads the segment
 // from HBM once (loads carry an L2 evict-last policy so the lines stay for
 // sweep B) and keeps a running (maximum, sum of exp) pair per thread,
-// rescaling the sum only when a batch of 32 values raises the maximum; sweep
+// rescaling the sum only when a batch of 16 values raises the maximum; sweep
 // B re-reads the segment from L2 and writes the normalised values with
 // streaming stores.  Both sweeps issue a batch of independent 128-bit loads
 // before touching any of them.  Two 512-thread CTAs per SM keep the set of
-// live segments (296 of them) far below the L2 capacity.
-constexpr int kLongThreads = 512;
-constexpr int kLongBatch = 8;  // 128-bit loads in flight per thread, sweep A
+// live segments (296 of them) far below the L2 capacity; the register cap
+// (room for three CTAs) leaves space for the resident buckets' CTAs to run
+// beside them.
+#ifndef SWG_SOFTMAX_LONG_THREADS
+#define SWG_SOFTMAX_LONG_THREADS 512
+#endif
+#ifndef SWG_SOFTMAX_LONG_CTAS
+#define SWG_SOFTMAX_LONG_CTAS 2
+#endif
+constexpr int kLongThreads = SWG_SOFTMAX_LONG_THREADS;
+constexpr int kLongCtasPerSm = SWG_SOFTMAX_LONG_CTAS;
+#ifndef SWG_SOFTMAX_LONG_BATCH
+#define SWG_SOFTMAX_LONG_BATCH 4
+#endif
+#ifndef SWG_SOFTMAX_LONG_MINBLOCKS
+#define SWG_SOFTMAX_LONG_MINBLOCKS 3
+#endif
+constexpr int kLongBatch = SWG_SOFTMAX_LONG_BATCH;  // 128-bit loads in flight per thread, sweep A
 
 struct MaxSum {
   float m, d;
@@ -280,7 +295,7 @@ __device__ __forceinline__ float4 normalise4(const float4 q, const float m,
   return r;
 }
 
-__global__ void __launch_bounds__(kLongThreads, 2)
+__global__ void __launch_bounds__(kLongThreads, SWG_SOFTMAX_LONG_MINBLOCKS)
 segsoftmax_long_kernel(const float *__restrict__ values,
                        const int32_t *__restrict__ offsets,
                        float *__restrict__ out,
@@ -420,7 +435,7 @@ cudaError_t launch_segsoftmax_planned(const float *values,
   const int32_t *list = plan.softmax_segments;
   const int32_t n_stream = plan.softmax_count[3];
   if (n_stream > 0) {
-    int grid = plan.sm_count * 2;
+    int grid = plan.sm_count * kLongCtasPerSm;
     if (grid > n_stream) grid = n_stream;
     segsoftmax_long_kernel<<<grid, kLongThreads, 0, stream>>>(
         values, offsets, out, list + plan.softmax_begin[3], n_stream);
