@@ -119,9 +119,11 @@ int swg_plan_describe(const swg_plan *plan, char *json, size_t capacity);
 int swg_plan_status(swg_plan *plan);
 
 /* The planner alone, on the host: no device is touched.  Writes up to
- * `task_capacity` tasks as 4 x int32 each {first segment, segment count or
+ * `task_capacity` tasks as 8 x int32 each {first segment, segment count or
  * partial slot (-1 = whole segment), first value, value count | kind << 28
- * (kind 0 = packed whole segments, 1 = chunk of one long segment)}, the total
+ * (kind 0 = packed segments, 1 = chunk of one long segment), partial slot of a
+ * first segment that began in an earlier task (else -1), partial slot of a
+ * last segment that continues in a later task (else -1), 0, 0}, the total
  * number of tasks to *task_count, and the same JSON as swg_plan_describe.
  * `tasks` and `json` may be NULL.  For inspection and for tests. */
 int swg_plan_host_tasks(const int32_t *host_offsets, int32_t segment_count,
@@ -154,9 +156,9 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
  * The planner runs on the host from `host_offsets` (segment_count + 1 entries,
  * validated here) and the task list, an aligned copy of the offsets and the
  * partials of split segments are placed in a fixed array that is part of the
- * library image on every GPU (about 1.8 MB, held until the process exits).
+ * library image on every GPU (about 2.3 MB, held until the process exits).
  * No cudaMalloc, cudaFree or other allocating call is made.
- * Limits: at most 262144 segments, 32768 tile tasks (about 6.7e7 values),
+ * Limits: at most 262144 segments, 32768 tile tasks (about 6.6e7 values),
  * 32768 partials and 8192 split segments; larger inputs are rejected with
  * SWG_ERR_UNSUPPORTED and a message naming the limit.
  * The first call on a device looks up the array's device address; make that

@@ -195,7 +195,7 @@ def plan_host_tasks(host_ptr, segment_count, op=OP_REDUCE):
     """Run the planner on the host only; return ``(tasks, description)``.
 
     ``tasks`` is a list of ``(segment, count_or_slot, value_begin,
-    value_count, kind)`` tuples.
+    value_count, kind, head_slot, tail_slot)`` tuples.
     """
     import json
 
@@ -205,16 +205,16 @@ def plan_host_tasks(host_ptr, segment_count, op=OP_REDUCE):
     check(lib.swg_plan_host_tasks(host_ptr, segment_count, op, None, 0,
                                   ctypes.byref(total), text, len(text)),
           "swg_plan_host_tasks")
-    words = (ctypes.c_int32 * (4 * max(total.value, 1)))()
+    words = (ctypes.c_int32 * (8 * max(total.value, 1)))()
     check(lib.swg_plan_host_tasks(host_ptr, segment_count, op, words,
                                   total.value, ctypes.byref(total), None, 0),
           "swg_plan_host_tasks")
     tasks = []
     for t in range(total.value):
-        seg, count, vbegin, packed = words[4 * t:4 * t + 4]
+        seg, count, vbegin, packed, head, tail = words[8 * t:8 * t + 6]
         packed &= 0xFFFFFFFF
         tasks.append((seg, count, vbegin, packed & ((1 << 28) - 1),
-                      packed >> 28))
+                      packed >> 28, head, tail))
     return tasks, json.loads(text.value.decode())
 
 

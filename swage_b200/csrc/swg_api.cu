@@ -196,6 +196,7 @@ int swg_plan_create(const int32_t *host_offsets, int32_t segment_count,
   dev.segment_count = segment_count;
   dev.split_count = (int32_t)plan->host.splits.size();
   dev.big_split_count = plan->host.big_split_count;
+  dev.medium_split_count = plan->host.medium_split_count;
   dev.partial_slots = plan->host.partial_slots;
   const size_t noffsets = (size_t)segment_count + 1;
   const size_t padded = ((noffsets + 3) / 4) * 4 + 4;
@@ -255,7 +256,7 @@ int swg_plan_host_tasks(const int32_t *host_offsets, int32_t segment_count,
   if (task_count) *task_count = (int64_t)plan.tasks.size();
   if (tasks) {
     const int64_t n = std::min<int64_t>(task_capacity, plan.tasks.size());
-    static_assert(sizeof(swg::Task) == 16, "task is four 32-bit words");
+    static_assert(sizeof(swg::Task) == 32, "task is eight 32-bit words");
     memcpy(tasks, plan.tasks.data(), (size_t)n * sizeof(swg::Task));
   }
   if (json) {

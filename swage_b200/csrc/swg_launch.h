@@ -19,6 +19,7 @@ struct DevicePlan {
   SplitSegment *splits = nullptr;
   int32_t split_count = 0;
   int32_t big_split_count = 0;     // leading splits that get a CTA each
+  int32_t medium_split_count = 0;  // then those that get a warp each
   float *partials = nullptr;       // one float per partial slot
   int32_t partial_slots = 0;
   int32_t *softmax_segments = nullptr;  // bucketed segment ids

@@ -16,26 +16,36 @@ constexpr int kTileValues = 2048;      // values per tile task (8 KiB of fp32)
 constexpr int kTileItems = 2032;       // values + segments of a packed task:
                                        // its offsets share the tile's stage
 constexpr int kTileMaxSegments = 1024; // segments per packed tile task
-constexpr int kLongSegment = 1792;     // longer segments become chunk tasks
+constexpr int kSplitMinimum = 128;     // segments up to here are never cut
+constexpr int kSplitMinimumPiece = 32; // smallest piece left in an open tile
 constexpr int kBigSplit = 256;         // partials from which a merge gets a whole CTA
+constexpr int kTinySplit = 4;          // up to here a merge is done by one thread
 constexpr int kHistogramBins = 33;     // bin b: len == 0 | 2^(b-1) <= len < 2^b
 
-// One schedulable unit.  16 bytes so a task is one 128-bit load.
-//   PACK : `count` whole segments seg .. seg+count-1, whose values
-//          [vbegin, vbegin+vcount) fit one tile; results go straight to out.
-//   CHUNK: a piece [vbegin, vbegin+vcount) of the single long segment `seg`;
-//          count = partial slot to write, or -1 when the piece is the whole
-//          segment and the result goes straight to out[seg].
+// One schedulable unit: what one warp reduces.  32 bytes (two 128-bit loads).
+//   PACK : segments seg .. seg+count-1 and their values
+//          [vbegin, vbegin+vcount).  All of them are whole, except that the
+//          first may have begun in an earlier task (head_slot >= 0) and the
+//          last may continue in a later one (tail_slot >= 0): those two
+//          results go to the given partial slot, the others straight to out.
+//   CHUNK: a 2048-value piece [vbegin, vbegin+vcount) of the single long
+//          segment `seg`; count = partial slot to write, or -1 when the piece
+//          is the whole segment and the result goes straight to out[seg].
 struct Task {
   int32_t seg;
   int32_t count;
   int32_t vbegin;
   uint32_t vcount_kind;  // bits 0..27 value count, bits 28..31 kind
+  int32_t head_slot;     // PACK only, else -1
+  int32_t tail_slot;     // PACK only, else -1
+  int32_t reserved0;
+  int32_t reserved1;
 };
 constexpr uint32_t kTaskPack = 0u, kTaskChunk = 1u;
 constexpr uint32_t kTaskCountMask = (1u << 28) - 1u;
 
-// A long segment whose partials are merged by the combine pass.
+// A segment cut over several tasks; its partials are merged by the second
+// pass.
 struct SplitSegment {
   int32_t seg;
   int32_t slot_begin;
@@ -68,7 +78,10 @@ struct HostPlan {
   int32_t softmax_begin[kSoftmaxBuckets] = {0, 0, 0, 0};
   int32_t softmax_count[kSoftmaxBuckets] = {0, 0, 0, 0};
   int32_t partial_slots = 0;
-  int32_t big_split_count = 0;  // splits are ordered big ones first
+  // splits are ordered: >= kBigSplit partials first, then the middle, then
+  // those with <= kTinySplit partials
+  int32_t big_split_count = 0;
+  int32_t medium_split_count = 0;
   int64_t pack_tasks = 0, chunk_tasks = 0;
 };
 

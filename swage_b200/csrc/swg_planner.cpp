@@ -85,9 +85,18 @@ static inline int length_bin(int64_t length) {
 
 namespace {
 
+// Walks the segments once and cuts the (values + segments) sequence into tile
+// tasks of at most kTileItems items.  A segment that does not fit the open
+// tile is either moved to the next tile whole (short ones: the waste is at
+// most kSplitMinimum items) or cut: a tail piece fills the open tile, whole
+// 2048-value pieces become chunk tasks, and the last piece opens the next
+// tile, so tiles stay full whatever the length mix.
 struct Packer {
   HostPlan *plan;
   int32_t seg_begin = 0, nseg = 0, vbegin = 0, vcount = 0;
+  int32_t head_slot = -1, tail_slot = -1;
+
+  int32_t room() const { return kTileItems - (vcount + nseg); }
 
   void flush() {
     if (nseg == 0) return;
@@ -96,17 +105,18 @@ struct Packer {
     task.count = nseg;
     task.vbegin = vbegin;
     task.vcount_kind = (kTaskPack << 28) | (uint32_t)vcount;
+    task.head_slot = head_slot;
+    task.tail_slot = tail_slot;
+    task.reserved0 = task.reserved1 = 0;
     plan->tasks.push_back(task);
     plan->pack_tasks++;
     nseg = 0;
     vcount = 0;
+    head_slot = tail_slot = -1;
   }
 
-  void add(int32_t seg, int32_t start, int32_t length) {
-    // a packed task's values and its offsets share one shared-memory stage
-    if (nseg > 0 && (vcount + length + nseg + 1 > kTileItems ||
-                     nseg >= kTileMaxSegments))
-      flush();
+  // append `length` values of segment `seg` starting at value `start`
+  void append(int32_t seg, int32_t start, int32_t length) {
     if (nseg == 0) {
       seg_begin = seg;
       vbegin = start;
@@ -114,58 +124,104 @@ struct Packer {
     nseg++;
     vcount += length;
   }
+
+  void chunk(int32_t seg, int32_t start, int32_t length, int32_t slot) {
+    Task task;
+    task.seg = seg;
+    task.count = slot;
+    task.vbegin = start;
+    task.vcount_kind = (kTaskChunk << 28) | (uint32_t)length;
+    task.head_slot = task.tail_slot = -1;
+    task.reserved0 = task.reserved1 = 0;
+    plan->tasks.push_back(task);
+    plan->chunk_tasks++;
+  }
 };
 
 void plan_reduce(const int32_t *offsets, int32_t segment_count,
                  HostPlan *plan) {
   Packer packer{plan};
-  plan->tasks.reserve((size_t)(offsets[segment_count] / kTileValues) + 64);
+  plan->tasks.reserve((size_t)(offsets[segment_count] / kTileItems) + 64);
   for (int32_t seg = 0; seg < segment_count; ++seg) {
     const int32_t start = offsets[seg];
     const int32_t length = offsets[seg + 1] - start;
-    if (length <= kLongSegment) {
-      packer.add(seg, start, length);
+    if (packer.nseg >= kTileMaxSegments) packer.flush();
+    if (length + 1 <= packer.room()) {
+      packer.append(seg, start, length);
       continue;
     }
-    packer.flush();
-    // Chunk boundaries sit on multiples of four elements so that, for a
-    // 16-byte aligned values pointer, every chunk but the first starts on a
-    // 16-byte boundary.
-    const int64_t end = (int64_t)start + length;
-    const int64_t origin = start & ~3;
-    const int64_t nchunks = (end - origin + kTileValues - 1) / kTileValues;
-    int32_t slot = -1;
-    if (nchunks > 1) {
-      SplitSegment split;
-      split.seg = seg;
-      split.slot_begin = plan->partial_slots;
-      split.slot_count = (int32_t)nchunks;
-      split.pad = 0;
-      plan->splits.push_back(split);
-      slot = plan->partial_slots;
-      plan->partial_slots += (int32_t)nchunks;
+    if (length <= kSplitMinimum || length + 1 <= kTileItems) {
+      // short: never cut.  Medium and the open tile nearly full: not worth
+      // a cut either when the whole segment fits a tile and the open tile
+      // has less than a useful piece of room.
+      if (length <= kSplitMinimum ||
+          packer.room() - 1 < kSplitMinimumPiece) {
+        packer.flush();
+        packer.append(seg, start, length);
+        continue;
+      }
     }
-    for (int64_t chunk = 0; chunk < nchunks; ++chunk) {
-      const int64_t lo = std::max<int64_t>(start, origin + chunk * kTileValues);
-      const int64_t hi =
-          std::min<int64_t>(end, origin + (chunk + 1) * kTileValues);
-      Task task;
-      task.seg = seg;
-      task.count = nchunks > 1 ? slot + (int32_t)chunk : -1;
-      task.vbegin = (int32_t)lo;
-      task.vcount_kind = (kTaskChunk << 28) | (uint32_t)(hi - lo);
-      plan->tasks.push_back(task);
-      plan->chunk_tasks++;
+    // Cut the segment.  Pieces, in order: a tail piece that fills the open
+    // tile, whole-tile chunks, and a head piece that opens the next tile.
+    int32_t position = start, remaining = length;
+    int32_t tail_piece = 0;
+    if (packer.nseg > 0 && packer.room() - 1 >= kSplitMinimumPiece)
+      tail_piece = packer.room() - 1;
+    const int32_t after_tail = remaining - tail_piece;
+    const int32_t whole_chunks = after_tail / kTileValues;
+    const int32_t last_piece = after_tail - whole_chunks * kTileValues;
+    const int32_t pieces =
+        (tail_piece > 0) + whole_chunks + (last_piece > 0);
+    if (pieces == 1) {
+      // one chunk on its own (2032..2048 values): straight to out
+      packer.flush();
+      packer.chunk(seg, start, length, -1);
+      continue;
+    }
+    SplitSegment split;
+    split.seg = seg;
+    split.slot_begin = plan->partial_slots;
+    split.slot_count = pieces;
+    split.pad = 0;
+    plan->splits.push_back(split);
+    int32_t slot = plan->partial_slots;
+    plan->partial_slots += pieces;
+    if (tail_piece > 0) {
+      packer.append(seg, position, tail_piece);
+      packer.tail_slot = slot++;
+      position += tail_piece;
+      remaining -= tail_piece;
+    }
+    packer.flush();
+    for (int32_t c = 0; c < whole_chunks; ++c) {
+      packer.chunk(seg, position, kTileValues, slot++);
+      position += kTileValues;
+      remaining -= kTileValues;
+    }
+    if (last_piece > 0) {
+      if (last_piece + 1 <= kTileItems) {
+        packer.append(seg, position, last_piece);
+        packer.head_slot = slot++;
+      } else {
+        packer.chunk(seg, position, last_piece, slot++);
+      }
     }
   }
   packer.flush();
-  // merge pass: segments with many partials first, a CTA each
+  // second pass: segments with many partials first (a CTA each), then the
+  // middle (a warp each), then those with a handful (a thread each)
   auto big = [](const SplitSegment &split) {
     return split.slot_count >= kBigSplit;
   };
-  auto middle =
+  auto not_tiny = [](const SplitSegment &split) {
+    return split.slot_count > kTinySplit;
+  };
+  auto after_big =
       std::stable_partition(plan->splits.begin(), plan->splits.end(), big);
-  plan->big_split_count = (int32_t)(middle - plan->splits.begin());
+  auto after_medium =
+      std::stable_partition(after_big, plan->splits.end(), not_tiny);
+  plan->big_split_count = (int32_t)(after_big - plan->splits.begin());
+  plan->medium_split_count = (int32_t)(after_medium - after_big);
 }
 
 // Softmax: bucket the non-empty segments by length.  Inside the streamed
@@ -258,13 +314,13 @@ std::string describe_host_plan(const HostPlan &plan) {
            "\"split_segments\": %zu, \"partial_slots\": %d, "
            "\"tile_values\": %d, \"tile_items\": %d, "
            "\"tile_max_segments\": %d, "
-           "\"long_segment\": %d, \"softmax_buckets\": [%d, %d, %d, %d], ",
+           "\"split_minimum\": %d, \"softmax_buckets\": [%d, %d, %d, %d], ",
            plan.segment_count, plan.value_count, plan.op, plan.schedule,
            plan.mean_length, (long long)plan.max_length, plan.tasks.size(),
            (long long)plan.pack_tasks, (long long)plan.chunk_tasks,
            plan.splits.size(), plan.partial_slots, kTileValues, kTileItems,
            kTileMaxSegments,
-           kLongSegment, plan.softmax_count[0], plan.softmax_count[1],
+           kSplitMinimum, plan.softmax_count[0], plan.softmax_count[1],
            plan.softmax_count[2], plan.softmax_count[3]);
   text += buffer;
   text += "\"histogram\": [";

@@ -124,6 +124,8 @@ __device__ __forceinline__ Task stop_task() {
   t.count = 0;
   t.vbegin = 0;
   t.vcount_kind = kTaskStop << 28;
+  t.head_slot = t.tail_slot = -1;
+  t.reserved0 = t.reserved1 = 0;
   return t;
 }
 
@@ -138,6 +140,9 @@ __device__ __forceinline__ Task shuffle_task(const Task &mine, int src) {
   t.count = __shfl_sync(kFullMask, mine.count, src);
   t.vbegin = __shfl_sync(kFullMask, mine.vbegin, src);
   t.vcount_kind = __shfl_sync(kFullMask, mine.vcount_kind, src);
+  t.head_slot = __shfl_sync(kFullMask, mine.head_slot, src);
+  t.tail_slot = __shfl_sync(kFullMask, mine.tail_slot, src);
+  t.reserved0 = t.reserved1 = 0;
   return t;
 }
 
@@ -168,7 +173,10 @@ __device__ __forceinline__ bool task_ok(const Task &t, const Limits &limits) {
   if (kind == kTaskPack)
     return t.count >= 1 && t.count <= kTileMaxSegments &&
            vcount + t.count <= kTileItems &&
-           (int64_t)t.seg + t.count <= limits.segment_count;
+           (int64_t)t.seg + t.count <= limits.segment_count &&
+           t.head_slot >= -1 && t.head_slot < limits.partial_slots &&
+           t.tail_slot >= -1 && t.tail_slot < limits.partial_slots &&
+           !(t.count == 1 && t.head_slot >= 0 && t.tail_slot >= 0);
   if (kind == kTaskChunk)
     return t.count >= -1 && t.count < limits.partial_slots;
   return false;
@@ -289,6 +297,14 @@ __device__ __forceinline__ void process_task(const Task &task,
     const bool valid = k < task.count;
     int a = valid ? soff[k] - origin : 0;
     int b = valid ? soff[k + 1] - origin : 0;
+    // the first segment may have begun in an earlier task and the last may
+    // continue in a later one: only the part inside this tile is reduced
+    // here, and the result is a partial
+    const bool head_piece = valid && k == 0 && task.head_slot >= 0;
+    const bool tail_piece =
+        valid && k == task.count - 1 && task.tail_slot >= 0;
+    if (head_piece && a <= shift) a = shift;
+    if (tail_piece && b >= shift + vcount) b = shift + vcount;
     if (valid && (a < shift || b < a || b > shift + vcount)) {
       // offsets that do not match the plan: report, treat as empty
       report(control, kErrBadSegment, (uint32_t)(task.seg + k));
@@ -303,8 +319,11 @@ __device__ __forceinline__ void process_task(const Task &task,
       for (int i = a; i < b; ++i) acc = Op::apply(acc, tile[i]);
     const unsigned medium_mask = __ballot_sync(kFullMask, medium);
     const unsigned wide_mask = __ballot_sync(kFullMask, wide);
+    float *target = out + task.seg + k;
+    if (head_piece) target = partials + task.head_slot;
+    if (tail_piece) target = partials + task.tail_slot;
     if ((medium_mask | wide_mask) == 0) {
-      if (valid) out[task.seg + k] = acc;
+      if (valid) *target = acc;
       continue;
     }
     const int medium_count = __popc(medium_mask);
@@ -354,7 +373,7 @@ __device__ __forceinline__ void process_task(const Task &task,
     }
     __syncwarp();
     if (slot >= 0) acc = scratch->result[slot];
-    if (valid) out[task.seg + k] = acc;
+    if (valid) *target = acc;
     __syncwarp();  // the lists are rewritten by the next 32 segments
   }
 }
@@ -510,26 +529,29 @@ segreduce_persistent_kernel(const float *__restrict__ values,
 }
 
 // Second pass of the split / persistent schedules: merge the partials of each
-// chunked segment in a fixed order.  The plan lists the segments with at
-// least kBigSplit partials first: each of those gets a whole CTA (CTAs
-// 0..big_count-1), the rest get one warp each.  Thread-strided partial sums
-// then a butterfly, so the result does not depend on timing.
-// Launched with programmatic stream serialisation: its CTAs may be placed
-// while the tile kernel drains, and wait here until that kernel's writes are
-// visible.
+// cut segment in slot order.  The plan lists the segments with at least
+// kBigSplit partials first (a CTA each: CTAs 0..big-1), then the middle (a
+// warp each), then those with at most kTinySplit partials (a thread each).
+// Thread-strided partial sums then a butterfly, so the result does not depend
+// on timing.  Launched with programmatic stream serialisation: its CTAs may be
+// placed while the tile kernel drains, and wait here until that kernel's
+// writes are visible.
 constexpr int kCombineThreads = 256;
 
 template <class Op>
 __global__ void __launch_bounds__(kCombineThreads)
 segreduce_combine_kernel(const SplitSegment *__restrict__ splits,
                          int32_t split_count, int32_t big_count,
+                         int32_t medium_count,
                          const float *__restrict__ partials,
                          float *__restrict__ out) {
   __shared__ float scratch[32];
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int lane = threadIdx.x & 31;
-  if ((int32_t)blockIdx.x < big_count) {
-    const SplitSegment s = splits[blockIdx.x];
+  const int32_t medium_ctas = (medium_count + 7) / 8;
+  int32_t block = (int32_t)blockIdx.x;
+  if (block < big_count) {
+    const SplitSegment s = splits[block];
     const float *p = partials + s.slot_begin;
     float a0 = Op::identity(), a1 = Op::identity(), a2 = Op::identity(),
           a3 = Op::identity();
@@ -546,16 +568,27 @@ segreduce_combine_kernel(const SplitSegment *__restrict__ splits,
     if (threadIdx.x == 0) out[s.seg] = r;
     return;
   }
-  const int64_t j = (int64_t)big_count +
-                    ((int64_t)(blockIdx.x - big_count) * kCombineThreads +
-                     threadIdx.x) / 32;
+  block -= big_count;
+  if (block < medium_ctas) {
+    const int32_t j = block * 8 + (int32_t)(threadIdx.x >> 5);
+    if (j >= medium_count) return;
+    const SplitSegment s = splits[big_count + j];
+    float acc = Op::identity();
+    for (int i = lane; i < s.slot_count; i += 32)
+      acc = Op::apply(acc, partials[s.slot_begin + i]);
+    acc = warp_reduce<Op>(acc);
+    if (lane == 0) out[s.seg] = acc;
+    return;
+  }
+  block -= medium_ctas;
+  const int64_t j = (int64_t)big_count + medium_count +
+                    (int64_t)block * kCombineThreads + threadIdx.x;
   if (j >= split_count) return;
   const SplitSegment s = splits[j];
   float acc = Op::identity();
-  for (int i = lane; i < s.slot_count; i += 32)
+  for (int i = 0; i < s.slot_count; ++i)
     acc = Op::apply(acc, partials[s.slot_begin + i]);
-  acc = warp_reduce<Op>(acc);
-  if (lane == 0) out[s.seg] = acc;
+  out[s.seg] = acc;
 }
 
 // ---------------------------------------------------------------------------
@@ -658,10 +691,13 @@ cudaError_t launch_segreduce_cta(int kind, const float *values,
 template <class Op>
 static cudaError_t launch_combine_as(const DevicePlan &plan, float *out,
                                      cudaStream_t stream) {
-  const int32_t small = plan.split_count - plan.big_split_count;
+  const int32_t tiny =
+      plan.split_count - plan.big_split_count - plan.medium_split_count;
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(
-      (unsigned)((int64_t)plan.big_split_count + ((int64_t)small + 7) / 8));
+  config.gridDim = dim3((unsigned)(
+      (int64_t)plan.big_split_count +
+      ((int64_t)plan.medium_split_count + 7) / 8 +
+      ((int64_t)tiny + kCombineThreads - 1) / kCombineThreads));
   config.blockDim = dim3(kCombineThreads);
   config.dynamicSmemBytes = 0;
   config.stream = stream;
@@ -673,6 +709,7 @@ static cudaError_t launch_combine_as(const DevicePlan &plan, float *out,
   return cudaLaunchKernelEx(&config, segreduce_combine_kernel<Op>,
                             (const SplitSegment *)plan.splits,
                             plan.split_count, plan.big_split_count,
+                            plan.medium_split_count,
                             (const float *)plan.partials, out);
 }
 
@@ -824,6 +861,7 @@ cudaError_t launch_segreduce_static(int kind, const float *values, float *out,
   dev.splits = d_splits;
   dev.split_count = (int32_t)plan.splits.size();
   dev.big_split_count = plan.big_split_count;
+  dev.medium_split_count = plan.medium_split_count;
   dev.partials = d_partials;
   dev.partial_slots = plan.partial_slots;
   dev.control = d_control;

@@ -90,44 +90,63 @@ def _plan(lengths):
 
 
 def check_tasks_cover_everything(offsets, tasks, info):
-    """Every segment and every value belongs to exactly one task."""
+    """Every value belongs to exactly one task; every segment is either whole
+    in one packed task or cut into pieces with consecutive partial slots."""
     segments = len(offsets) - 1
-    seen = np.zeros(segments, dtype=np.int64)
+    whole = np.zeros(segments, dtype=np.int64)
     covered = np.zeros(int(offsets[-1]) + 1, dtype=np.int64)
-    tile, long_limit = info["tile_values"], info["long_segment"]
-    chunks = {}
-    for seg, count, vbegin, vcount, kind in tasks:
+    tile, items = info["tile_values"], info["tile_items"]
+    pieces = {}
+    for seg, count, vbegin, vcount, kind, head, tail in tasks:
         assert 0 <= vcount <= tile
         covered[vbegin] += 1
         covered[vbegin + vcount] -= 1
+        vend = vbegin + vcount
         if kind == 0:
             assert 1 <= count <= info["tile_max_segments"]
-            assert vcount + count <= info["tile_items"]
-            assert vbegin == offsets[seg]
-            assert vbegin + vcount == offsets[seg + count]
-            seen[seg:seg + count] += 1
-            assert np.all(np.diff(offsets[seg:seg + count + 1]) <= long_limit)
+            assert vcount + count <= items
+            assert not (count == 1 and head >= 0 and tail >= 0)
+            last = seg + count - 1
+            first_whole, last_whole = seg, last
+            if head >= 0:  # began in an earlier task
+                assert offsets[seg] < vbegin
+                end = min(int(offsets[seg + 1]), vend)
+                pieces.setdefault(seg, []).append((vbegin, end - vbegin, head))
+                first_whole = seg + 1
+            else:
+                assert offsets[seg] == vbegin
+            if tail >= 0:  # continues in a later task
+                assert offsets[last + 1] > vend
+                start = max(int(offsets[last]), vbegin)
+                pieces.setdefault(last, []).append((start, vend - start, tail))
+                last_whole = last - 1
+            else:
+                assert offsets[last + 1] == vend
+            whole[first_whole:last_whole + 1] += 1
         else:
-            assert kind == 1
-            assert offsets[seg + 1] - offsets[seg] > long_limit
-            assert offsets[seg] <= vbegin and vbegin + vcount <= offsets[seg + 1]
-            chunks.setdefault(seg, []).append((vbegin, vcount, count))
-    for seg, pieces in chunks.items():
-        seen[seg] += 1
-        pieces.sort()
-        assert pieces[0][0] == offsets[seg]
-        assert pieces[-1][0] + pieces[-1][1] == offsets[seg + 1]
-        for (b0, c0, _), (b1, _, _) in zip(pieces, pieces[1:]):
+            assert kind == 1 and head == -1 and tail == -1
+            assert offsets[seg] <= vbegin and vend <= offsets[seg + 1]
+            if count < 0:
+                assert offsets[seg] == vbegin and offsets[seg + 1] == vend
+                whole[seg] += 1
+            else:
+                pieces.setdefault(seg, []).append((vbegin, vcount, count))
+    for seg, parts in pieces.items():
+        assert whole[seg] == 0
+        whole[seg] += 1
+        parts.sort()
+        assert len(parts) >= 2
+        assert parts[0][0] == offsets[seg]
+        assert parts[-1][0] + parts[-1][1] == offsets[seg + 1]
+        for (b0, c0, _), (b1, _, _) in zip(parts, parts[1:]):
             assert b0 + c0 == b1
-            assert b1 % 4 == 0  # later chunks start on a 16-byte boundary
-        slots = [slot for _, _, slot in pieces]
-        if len(pieces) == 1:
-            assert slots == [-1]
-        else:
-            assert slots == list(range(slots[0], slots[0] + len(slots)))
-    assert np.all(seen == 1)
+        slots = [slot for _, _, slot in parts]
+        assert slots == list(range(slots[0], slots[0] + len(slots)))
+    assert np.all(whole == 1)
     assert np.all(np.cumsum(covered)[:-1] == 1)
     assert info["tasks"] == len(tasks)
+    assert info["split_segments"] == len(pieces)
+    assert info["partial_slots"] == sum(len(p) for p in pieces.values())
     assert sum(info["histogram"]) == segments
     assert sum(info["elements_in_bin"]) == int(offsets[-1])
 
@@ -136,6 +155,8 @@ def check_tasks_cover_everything(offsets, tasks, info):
     [0], [1], [128], [129], [4097], [33, 33, 33, 33], [1, 257, 2, 3837],
     [0, 2, 0, 0, 3], [0] * 5000, [8192], [8193], [2048, 2049, 1, 0, 100000],
     [1024, 1025, 2047, 2048, 2049, 2050, 4095, 4096, 4097],
+    [2031, 2032, 2033, 1, 2030, 2, 129, 1900, 130, 1901, 128, 1903],
+    [300] * 200, [1500, 700] * 50, [2000, 31, 2000, 33, 2000, 160],
     [3] * 10000,
 ], ids=str)
 def test_planner_tasks_partition_the_input(lengths, native_library):
@@ -151,7 +172,7 @@ def test_planner_on_random_skewed_lengths(native_library):
     offsets, tasks, info = _plan(lengths)
     check_tasks_cover_everything(offsets, tasks, info)
     assert info["max_length"] == int(lengths.max())
-    assert info["split_segments"] == 5
+    assert info["split_segments"] >= 5
     # short bins hold the many tiny segments
     assert sum(info["histogram"][:5]) == 20000 - 5
 
