@@ -78,6 +78,7 @@ int current_device(int *device, int *sm_count) {
   }
   if (!info.configured) {
     e = swg::configure_segreduce_kernels();
+    if (e == cudaSuccess) e = swg::configure_softmax_kernels();
     if (e != cudaSuccess) return cuda_failure("cudaFuncSetAttribute", e);
     info.configured = true;
   }
@@ -481,8 +482,8 @@ int swg_segsoftmax_f32(const float *values, const int32_t *offsets, float *out,
   cudaError_t e;
   const swg::Probe *probe = next_probe();
   if (plan && (schedule == SWG_SCHED_SPLIT || schedule == SWG_SCHED_PERSISTENT))
-    e = swg::launch_segsoftmax_planned(values, offsets, out, plan->dev, s,
-                                       probe);
+    e = swg::launch_segsoftmax_planned(values, offsets, out, value_count,
+                                       plan->dev, s, probe);
   else if (schedule == SWG_SCHED_WARP)
     e = swg::launch_segsoftmax_warp(values, offsets, out, segment_count,
                                     sm_count, s, probe);

@@ -64,6 +64,7 @@ cudaError_t launch_segreduce_persistent(int kind, const float *values,
                                         cudaStream_t stream,
                                         const Probe *probe);
 cudaError_t configure_segreduce_kernels();
+cudaError_t configure_softmax_kernels();
 
 // Allocation-free variant: the split schedule run out of a fixed-size
 // file-scope device array.  Limits of that array:
@@ -87,10 +88,11 @@ cudaError_t launch_segsoftmax_warp(const float *values, const int32_t *offsets,
                                    int sm_count, cudaStream_t stream,
                                    const Probe *probe);
 
-// Planned softmax: the streamed bucket first, then the three
-// register-resident buckets.
+// Planned softmax: the streamed bucket and the three
+// register-resident buckets, concurrently.
 cudaError_t launch_segsoftmax_planned(const float *values,
                                       const int32_t *offsets, float *out,
+                                      int32_t value_count,
                                       const DevicePlan &plan,
                                       cudaStream_t stream, const Probe *probe);
 

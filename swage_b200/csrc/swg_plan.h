@@ -55,10 +55,14 @@ struct SplitSegment {
 
 // Softmax buckets by segment length: the first three are held in the
 // registers of a warp / a 128-thread CTA / a 512-thread CTA (16 values per
-// thread; read once, written once), longer segments are streamed by a CTA in
-// two sweeps.
+// thread), read once and written once; longer segments are streamed through
+// a shared-memory ring by a CTA in two sweeps.
+#ifndef SWG_SOFTMAX_RING_FROM
+#define SWG_SOFTMAX_RING_FROM 8192
+#endif
 constexpr int kSoftmaxBuckets = 4;
-constexpr int kSoftmaxLimit[kSoftmaxBuckets - 1] = {512, 2048, 8192};
+constexpr int kSoftmaxLimit[kSoftmaxBuckets - 1] = {512, 2048,
+                                                    SWG_SOFTMAX_RING_FROM};
 
 struct HostPlan {
   int32_t segment_count = 0;

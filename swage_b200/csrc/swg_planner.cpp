@@ -235,8 +235,8 @@ static inline int softmax_bucket(int64_t length) {
 
 void plan_softmax(const int32_t *offsets, int32_t segment_count,
                   HostPlan *plan) {
-  // slot = bucket for the resident buckets, 3 + (bins - 1 - bin) for the
-  // streamed one: one counting sort over all of them
+  // slot = bucket for the resident buckets, then one slot per length bin,
+  // longest first, for the streamed one: one counting sort over all of them
   const int slots = kSoftmaxBuckets - 1 + kHistogramBins;
   std::vector<int64_t> fill((size_t)slots, 0), start((size_t)slots, 0);
   auto slot_of = [](int64_t length) {

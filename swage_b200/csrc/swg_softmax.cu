@@ -388,8 +388,262 @@ segsoftmax_long_kernel(const float *__restrict__ values,
   }
 }
 
-// Side streams so the four bucket kernels of one call run concurrently (the
-// streamed bucket leaves half of every SM's thread slots free): created once
+// Ring kernel: one CTA per segment, two sweeps through a ring of kRingStages
+// shared-memory stages of kRingChunk values, filled by bulk async copies that
+// thread 0 issues up to a full ring ahead of the readers.
+//
+//   sweep A  chunks 0 .. n-1: running (maximum, sum of exp) per thread;
+//   sweep B  chunks n-1 .. 0: normalise and store.
+//
+// Sweep B walks backwards, so the last kRingStages chunks of sweep A are still
+// in the ring and are not loaded again: a segment of up to kRingStages chunks
+// is read from HBM once and never again, a longer one re-reads all but its
+// tail, most recent lines first, which L2 serves (sweep A loads of chunks
+// that will come back carry an evict-last policy, everything else
+// evict-first).  Chunk c lives in stage c % kRingStages in both sweeps.
+//
+// A chunk is a run of whole 16-byte lines of `values` counted from the line
+// that holds the segment's first value, so every copy is aligned whatever
+// the offsets are; the up-to-three values that share a line with the array's
+// ends are fetched by plain loads.
+//
+// Every stage has a `full` barrier (one arrival + the copy's bytes per load)
+// and an `empty` barrier (one arrival per warp, after the last read of what
+// was loaded).  All waits are bounded; a wait that gives up raises the
+// plan's timeout flag and the CTA walks to the end without touching the ring.
+#ifndef SWG_RING_STAGES
+#define SWG_RING_STAGES 8
+#endif
+constexpr int kRingStages = SWG_RING_STAGES;
+constexpr int kRingChunk = 2048;
+constexpr int kRingThreads = 256;
+constexpr int kRingWarps = kRingThreads / 32;
+constexpr int kRingVectors = kRingChunk / 4 / kRingThreads;  // per thread
+static_assert(kRingStages >= 2 && kRingStages <= 27, "ring size");
+constexpr int kRingBytes = kRingStages * kRingChunk * 4;
+// CTAs that fit an SM's 227 KB of shared memory (1 KB reserved per CTA)
+constexpr int kRingCtasPerSm =
+    (227 * 1024) / (kRingBytes + 1024 + 256) < 2048 / kRingThreads
+        ? (227 * 1024) / (kRingBytes + 1024 + 256)
+        : 2048 / kRingThreads;
+#ifndef SWG_SOFTMAX_RING
+#define SWG_SOFTMAX_RING 1
+#endif
+
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t policy;
+  asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+
+__device__ __forceinline__ void bulk_g2s_hint(void *dst_smem,
+                                              const void *src_gmem,
+                                              uint32_t bytes, uint64_t *bar,
+                                              uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(dst_smem)),
+      "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+
+struct RingSegment {
+  int64_t begin, end;  // the segment's values
+  int64_t origin;      // index of slot 0: the aligned line holding `begin`
+  int64_t last_line;   // first index past the last whole line of the array
+  int64_t line_end;    // index past the line holding the segment's last value
+  int mis;             // (values pointer / 4) mod 4
+};
+
+// Thread 0 only: waits until the stage's previous contents have been read by
+// every warp, then starts the copy of chunk `c` into it.
+__device__ __forceinline__ bool ring_issue(const RingSegment &g,
+                                           const float *__restrict__ values,
+                                           float *ring, uint64_t *full,
+                                           uint64_t *empty, int64_t c,
+                                           uint32_t &loaded,
+                                           uint32_t &empty_parity,
+                                           uint64_t policy) {
+  const int stage = (int)(c % kRingStages);
+  const uint32_t bit = 1u << stage;
+  if (loaded & bit) {
+    if (!mbar_wait(&empty[stage], (empty_parity & bit) ? 1u : 0u)) return false;
+    empty_parity ^= bit;
+  }
+  loaded |= bit;
+  float *slot = ring + stage * kRingChunk;
+  const int64_t g0 = g.origin + c * kRingChunk;
+  int64_t g1 = g0 + kRingChunk;
+  if (g1 > g.line_end) g1 = g.line_end;
+  int64_t lo = g0 < 0 ? g0 + 4 : g0;
+  int64_t hi = g1 > g.last_line ? g.last_line : g1;
+  if (hi < lo) hi = lo;
+  const int64_t vb = g.begin > g0 ? g.begin : g0;
+  const int64_t ve = g.end < g1 ? g.end : g1;
+  for (int64_t i = vb; i < ve && i < lo; ++i) slot[i - g0] = values[i];
+  for (int64_t i = hi > vb ? hi : vb; i < ve; ++i) slot[i - g0] = values[i];
+  const uint32_t bytes = (uint32_t)(hi - lo) * 4u;
+  mbar_arrive_expect_tx(&full[stage], bytes);
+  if (bytes)
+    bulk_g2s_hint(slot + (lo - g0), values + lo, bytes, &full[stage], policy);
+  return true;
+}
+
+__global__ void __launch_bounds__(kRingThreads)
+segsoftmax_ring_kernel(const float *__restrict__ values,
+                       const int32_t *__restrict__ offsets,
+                       float *__restrict__ out,
+                       const int32_t *__restrict__ segments, int32_t count,
+                       int32_t value_count, uint32_t *__restrict__ control) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  float *ring = reinterpret_cast<float *>(smem);
+  __shared__ uint64_t full[kRingStages], empty[kRingStages];
+  __shared__ float scratch[32];
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  if (tid == 0) {
+    for (int s = 0; s < kRingStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kRingWarps);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const uint64_t keep = policy_evict_last();
+  const uint64_t once = policy_evict_first();
+  RingSegment g;
+  g.mis = (int)(((uintptr_t)values >> 2) & 3);
+  g.last_line = (int64_t)value_count - ((value_count + g.mis) & 3);
+  const bool same_phase =
+      (int)(((uintptr_t)out >> 2) & 3) == g.mis;  // lines of out = lines of values
+  uint32_t full_parity = 0;                // every thread, one bit per stage
+  uint32_t empty_parity = 0, loaded = 0;   // thread 0
+  bool failed = false;
+
+  for (int64_t j = blockIdx.x; j < count; j += gridDim.x) {
+    const int32_t seg = __ldg(segments + j);
+    g.begin = __ldg(offsets + seg);
+    g.end = __ldg(offsets + seg + 1);
+    const int shift = (int)((g.begin + g.mis) & 3);
+    g.origin = g.begin - shift;
+    g.line_end = g.end + ((4 - ((g.end + g.mis) & 3)) & 3);
+    const int64_t slots = (int64_t)shift + (g.end - g.begin);  // valid: [shift, slots)
+    const int64_t n = (slots + kRingChunk - 1) / kRingChunk;
+    const int64_t resident_from = n > kRingStages ? n - kRingStages : 0;
+
+    if (tid == 0 && !failed)
+      for (int64_t c = 0; c < n && c < kRingStages && !failed; ++c)
+        failed = !ring_issue(g, values, ring, full, empty, c, loaded,
+                             empty_parity, c < resident_from ? keep : once);
+
+    // ---- sweep A ----
+    MaxSum s{-CUDART_INF_F, 0.0f};
+    float any = MaxOp::identity();  // NaN-propagating maximum
+    for (int64_t c = 0; c < n && !failed; ++c) {
+      if (tid == 0 && c >= 1 && c + kRingStages - 1 < n) {
+        const int64_t ahead = c + kRingStages - 1;
+        if (!ring_issue(g, values, ring, full, empty, ahead, loaded,
+                        empty_parity, ahead < resident_from ? keep : once)) {
+          failed = true;
+          break;
+        }
+      }
+      const int stage = (int)(c % kRingStages);
+      const uint32_t bit = 1u << stage;
+      if (!mbar_wait(&full[stage], (full_parity & bit) ? 1u : 0u)) {
+        failed = true;
+        break;
+      }
+      full_parity ^= bit;
+      const float4 *slot =
+          reinterpret_cast<const float4 *>(ring + stage * kRingChunk);
+      // valid local slots of this chunk: [l0, l1)
+      const int l0 = c == 0 ? shift : 0;
+      const int64_t left = slots - c * kRingChunk;
+      const int l1 = left < kRingChunk ? (int)left : kRingChunk;
+      float4 q[kRingVectors];
+#pragma unroll
+      for (int k = 0; k < kRingVectors; ++k) {
+        const int i = tid + k * kRingThreads;
+        q[k] = slot[i];
+        if (4 * i < l0 || 4 * i + 4 > l1) {
+          if (4 * i + 0 < l0 || 4 * i + 0 >= l1) q[k].x = MaxOp::identity();
+          if (4 * i + 1 < l0 || 4 * i + 1 >= l1) q[k].y = MaxOp::identity();
+          if (4 * i + 2 < l0 || 4 * i + 2 >= l1) q[k].z = MaxOp::identity();
+          if (4 * i + 3 < l0 || 4 * i + 3 >= l1) q[k].w = MaxOp::identity();
+        }
+      }
+      if (c < resident_from) {  // will be loaded again for sweep B
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[stage]);
+      }
+      float lm = max4(q[0]);
+#pragma unroll
+      for (int k = 1; k < kRingVectors; ++k) lm = MaxOp::apply(lm, max4(q[k]));
+      any = MaxOp::apply(any, lm);
+      online_raise(s, lm);
+      if (s.m > -CUDART_INF_F) {
+        float d0 = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kRingVectors; ++k) d0 += expsum4(q[k], s.m);
+        s.d += d0;
+      }
+    }
+    if (failed) atomicCAS(control + 2, 0u, 1u);
+    // the segment maximum first (NaN-propagating), then the sums rescaled to it
+    const float m = cta_reduce<MaxOp>(any, scratch);
+    const float mine = s.d == 0.0f ? 0.0f : s.d * exp_neg(s.m - m);
+    const float d = cta_reduce<SumOp>(mine, scratch);
+    const float inv = 1.0f / d;
+
+    // ---- sweep B ----
+    for (int64_t c = n - 1; c >= 0 && !failed; --c) {
+      if (tid == 0 && c <= n - 2 && c + 1 - kRingStages >= 0) {
+        if (!ring_issue(g, values, ring, full, empty, c + 1 - kRingStages,
+                        loaded, empty_parity, once)) {
+          failed = true;
+          break;
+        }
+      }
+      const int stage = (int)(c % kRingStages);
+      const uint32_t bit = 1u << stage;
+      if (c < resident_from) {
+        if (!mbar_wait(&full[stage], (full_parity & bit) ? 1u : 0u)) {
+          failed = true;
+          break;
+        }
+        full_parity ^= bit;
+      }
+      const float4 *slot =
+          reinterpret_cast<const float4 *>(ring + stage * kRingChunk);
+      const int l0 = c == 0 ? shift : 0;
+      const int64_t left = slots - c * kRingChunk;
+      const int l1 = left < kRingChunk ? (int)left : kRingChunk;
+      float *o = out + (g.origin + c * kRingChunk);  // local slot 0
+      float4 q[kRingVectors];
+#pragma unroll
+      for (int k = 0; k < kRingVectors; ++k) q[k] = slot[tid + k * kRingThreads];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[stage]);
+#pragma unroll
+      for (int k = 0; k < kRingVectors; ++k) {
+        const int i = tid + k * kRingThreads;
+        const float4 r = normalise4(q[k], m, inv);
+        if (same_phase && 4 * i >= l0 && 4 * i + 4 <= l1) {
+          __stcs(reinterpret_cast<float4 *>(o) + i, r);
+        } else {
+          if (4 * i + 0 >= l0 && 4 * i + 0 < l1) __stcs(o + 4 * i + 0, r.x);
+          if (4 * i + 1 >= l0 && 4 * i + 1 < l1) __stcs(o + 4 * i + 1, r.y);
+          if (4 * i + 2 >= l0 && 4 * i + 2 < l1) __stcs(o + 4 * i + 2, r.z);
+          if (4 * i + 3 >= l0 && 4 * i + 3 < l1) __stcs(o + 4 * i + 3, r.w);
+        }
+      }
+    }
+    if (failed) atomicCAS(control + 2, 0u, 1u);
+  }
+}
+
+// Side streams so the bucket kernels of one call run concurrently: created once
 // per device, joined back into the caller's stream before the call returns
 // control to it.
 namespace {
@@ -421,8 +675,15 @@ cudaError_t fork_for(int device, Fork **fork) {
 }
 }  // namespace
 
+cudaError_t configure_softmax_kernels() {
+  return cudaFuncSetAttribute(segsoftmax_ring_kernel,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              kRingBytes);
+}
+
 cudaError_t launch_segsoftmax_planned(const float *values,
                                       const int32_t *offsets, float *out,
+                                      int32_t value_count,
                                       const DevicePlan &plan,
                                       cudaStream_t stream,
                                       const Probe *probe) {
@@ -435,10 +696,18 @@ cudaError_t launch_segsoftmax_planned(const float *values,
   const int32_t *list = plan.softmax_segments;
   const int32_t n_stream = plan.softmax_count[3];
   if (n_stream > 0) {
+#if SWG_SOFTMAX_RING
+    int grid = plan.sm_count * kRingCtasPerSm;
+    if (grid > n_stream) grid = n_stream;
+    segsoftmax_ring_kernel<<<grid, kRingThreads, kRingBytes, stream>>>(
+        values, offsets, out, list + plan.softmax_begin[3], n_stream,
+        value_count, plan.control);
+#else
     int grid = plan.sm_count * kLongCtasPerSm;
     if (grid > n_stream) grid = n_stream;
     segsoftmax_long_kernel<<<grid, kLongThreads, 0, stream>>>(
         values, offsets, out, list + plan.softmax_begin[3], n_stream);
+#endif
   }
   for (int b = 2; b >= 0; --b) {
     const int32_t n = plan.softmax_count[b];

@@ -44,7 +44,8 @@ def test_small_cases(schedule):
     for lengths in ([1], [0], [0, 2, 0, 0, 3], [33, 33, 33, 33],
                     [1, 257, 2, 3837], [4097], [129, 0, 128, 127, 1],
                     [511, 512, 513], [2047, 2048, 2049], [8191, 8192, 8193],
-                    [16384, 3, 20000]):
+                    [16384, 3, 20000], [8192, 8193, 8200, 65535, 65536, 65537],
+                    [9001, 30011, 12345]):
         offsets = offsets_from_lengths(lengths)
         values = (2 * rng.standard_normal(offsets[-1] + 2)).astype(np.float32)
         result = check_softmax(values, offsets, schedule)
@@ -94,7 +95,7 @@ def test_nan_and_empty_semantics(schedule):
 
 
 @pytest.mark.parametrize("schedule", SCHEDULES)
-@pytest.mark.parametrize("length", [5, 700, 1024, 1025, 5000, 70000])
+@pytest.mark.parametrize("length", [5, 700, 1024, 1025, 5000, 30001, 70000])
 def test_infinities_follow_the_oracle(schedule, length):
     """-inf entries get probability 0; a NaN or +inf poisons its segment."""
     rng = np.random.default_rng(length)
