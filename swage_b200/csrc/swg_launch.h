@@ -23,8 +23,8 @@ struct DevicePlan {
   float *partials = nullptr;       // one float per partial slot
   int32_t partial_slots = 0;
   int32_t *softmax_segments = nullptr;  // bucketed segment ids
-  int32_t softmax_begin[kSoftmaxBuckets] = {0, 0, 0, 0};
-  int32_t softmax_count[kSoftmaxBuckets] = {0, 0, 0, 0};
+  int32_t softmax_begin[kSoftmaxBuckets] = {0};
+  int32_t softmax_count[kSoftmaxBuckets] = {0};
   uint32_t *control = nullptr;     // [0] ticket, [1] finished, [2] error, [3] detail
 };
 
@@ -88,8 +88,8 @@ cudaError_t launch_segsoftmax_warp(const float *values, const int32_t *offsets,
                                    int sm_count, cudaStream_t stream,
                                    const Probe *probe);
 
-// Planned softmax: the streamed bucket and the three
-// register-resident buckets, concurrently.
+// Planned softmax: the ring buckets and the register-resident buckets,
+// concurrently.
 cudaError_t launch_segsoftmax_planned(const float *values,
                                       const int32_t *offsets, float *out,
                                       int32_t value_count,

@@ -54,15 +54,13 @@ struct SplitSegment {
 };
 
 // Softmax buckets by segment length: the first three are held in the
-// registers of a warp / a 128-thread CTA / a 512-thread CTA (16 values per
-// thread), read once and written once; longer segments are streamed through
-// a shared-memory ring by a CTA in two sweeps.
-#ifndef SWG_SOFTMAX_RING_FROM
-#define SWG_SOFTMAX_RING_FROM 8192
-#endif
-constexpr int kSoftmaxBuckets = 4;
-constexpr int kSoftmaxLimit[kSoftmaxBuckets - 1] = {512, 2048,
-                                                    SWG_SOFTMAX_RING_FROM};
+// registers of eight lanes / a warp / a 128-thread CTA; the longer ones go
+// through shared-memory rings whose size grows with the class, so that a
+// segment of the fourth to sixth class -- and of the seventh, up to 57344
+// values -- stays on the SM between its two sweeps.
+constexpr int kSoftmaxBuckets = 7;
+constexpr int kSoftmaxLimit[kSoftmaxBuckets - 1] = {64,   512,   2048,
+                                                    8192, 16384, 28672};
 
 struct HostPlan {
   int32_t segment_count = 0;
@@ -79,8 +77,8 @@ struct HostPlan {
   // (streamed) bucket is ordered by decreasing length bin so that a
   // round-robin over it is balanced
   std::vector<int32_t> softmax_segments;
-  int32_t softmax_begin[kSoftmaxBuckets] = {0, 0, 0, 0};
-  int32_t softmax_count[kSoftmaxBuckets] = {0, 0, 0, 0};
+  int32_t softmax_begin[kSoftmaxBuckets] = {0};
+  int32_t softmax_count[kSoftmaxBuckets] = {0};
   int32_t partial_slots = 0;
   // splits are ordered: >= kBigSplit partials first, then the middle, then
   // those with <= kTinySplit partials

@@ -314,14 +314,15 @@ std::string describe_host_plan(const HostPlan &plan) {
            "\"split_segments\": %zu, \"partial_slots\": %d, "
            "\"tile_values\": %d, \"tile_items\": %d, "
            "\"tile_max_segments\": %d, "
-           "\"split_minimum\": %d, \"softmax_buckets\": [%d, %d, %d, %d], ",
+           "\"split_minimum\": %d, \"softmax_buckets\": [%d, %d, %d, %d, %d, %d, %d], ",
            plan.segment_count, plan.value_count, plan.op, plan.schedule,
            plan.mean_length, (long long)plan.max_length, plan.tasks.size(),
            (long long)plan.pack_tasks, (long long)plan.chunk_tasks,
            plan.splits.size(), plan.partial_slots, kTileValues, kTileItems,
            kTileMaxSegments,
            kSplitMinimum, plan.softmax_count[0], plan.softmax_count[1],
-           plan.softmax_count[2], plan.softmax_count[3]);
+           plan.softmax_count[2], plan.softmax_count[3], plan.softmax_count[4],
+           plan.softmax_count[5], plan.softmax_count[6]);
   text += buffer;
   text += "\"histogram\": [";
   for (int bin = 0; bin < kHistogramBins; ++bin) {

@@ -166,82 +166,59 @@ segsoftmax_warp_kernel(const float *__restrict__ values,
 // Planned schedule.
 // ---------------------------------------------------------------------------
 
-// Resident buckets: a segment of at most kThreads * kResidentRows values is
-// held in the registers of kThreads threads (one warp, or a CTA of 128 or 512
-// threads): every value is read from HBM exactly once and written exactly
-// once, with coalesced 4-byte accesses, so no alignment case exists.
-constexpr int kResidentRows = 16;
-
-template <int kThreads>
-__global__ void __launch_bounds__(kThreads == 32 ? 256 : kThreads,
-                                  kThreads == 512 ? 3 : 1)
+// Resident buckets: a segment of at most kThreads * kRows values is held in
+// the registers of kThreads threads (an eighth of a warp, a warp, or a CTA of
+// 128 threads): every value is read from HBM exactly once and written exactly
+// once, with coalesced 4-byte accesses, so no alignment case exists.  Groups
+// narrower than a CTA share a 256-thread CTA.
+template <int kThreads, int kRows>
+__global__ void __launch_bounds__(kThreads <= 32 ? 256 : kThreads)
 segsoftmax_resident_kernel(const float *__restrict__ values,
                            const int32_t *__restrict__ offsets,
                            float *__restrict__ out,
                            const int32_t *__restrict__ segments,
                            int32_t count) {
   __shared__ float scratch[32];
-  const int t = kThreads == 32 ? (int)(threadIdx.x & 31) : (int)threadIdx.x;
+  constexpr bool kGroup = kThreads <= 32;
+  const int t = kGroup ? (int)(threadIdx.x % kThreads) : (int)threadIdx.x;
   const int64_t which =
-      kThreads == 32
-          ? (((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5)
-          : (int64_t)blockIdx.x;
-  if (which >= count) return;
-  const int32_t seg = __ldg(segments + which);
-  const int64_t begin = __ldg(offsets + seg);
-  const int length = (int)(__ldg(offsets + seg + 1) - begin);
+      kGroup ? ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / kThreads
+             : (int64_t)blockIdx.x;
+  // a group past the end of the list keeps in step with the rest of its warp
+  int64_t begin = 0;
+  int length = 0;
+  if (which < count) {
+    const int32_t seg = __ldg(segments + which);
+    begin = __ldg(offsets + seg);
+    length = (int)(__ldg(offsets + seg + 1) - begin);
+  }
   const float *p = values + begin + t;
-  float x[kResidentRows];
+  float x[kRows];
 #pragma unroll
-  for (int r = 0; r < kResidentRows; ++r)
+  for (int r = 0; r < kRows; ++r)
     x[r] = (r * kThreads + t < length) ? __ldcs(p + r * kThreads)
                                        : MaxOp::identity();
   float m = x[0];
 #pragma unroll
-  for (int r = 1; r < kResidentRows; ++r) m = MaxOp::apply(m, x[r]);
-  m = kThreads == 32 ? warp_reduce<MaxOp>(m) : cta_reduce<MaxOp>(m, scratch);
+  for (int r = 1; r < kRows; ++r) m = MaxOp::apply(m, x[r]);
+  m = kGroup ? group_reduce<MaxOp>(m, kThreads) : cta_reduce<MaxOp>(m, scratch);
   float d = 0.0f;
 #pragma unroll
-  for (int r = 0; r < kResidentRows; ++r) {
+  for (int r = 0; r < kRows; ++r) {
     // padding slots are masked: exp(-inf - m) is 0 only for an ordered m
     const float e = (r * kThreads + t < length) ? exp_neg(x[r] - m) : 0.0f;
     x[r] = e;
     d += e;
   }
-  d = kThreads == 32 ? warp_reduce<SumOp>(d) : cta_reduce<SumOp>(d, scratch);
+  d = kGroup ? group_reduce<SumOp>(d, kThreads) : cta_reduce<SumOp>(d, scratch);
   const float inv = 1.0f / d;
   float *o = out + begin + t;
 #pragma unroll
-  for (int r = 0; r < kResidentRows; ++r)
+  for (int r = 0; r < kRows; ++r)
     if (r * kThreads + t < length) __stcs(o + r * kThreads, x[r] * inv);
 }
 
-// Long bucket: one CTA per segment, two sweeps.  Sweep A reads the segment
-// from HBM once (loads carry an L2 evict-last policy so the lines stay for
-// sweep B) and keeps a running (maximum, sum of exp) pair per thread,
-// rescaling the sum only when a batch of 16 values raises the maximum; sweep
-// B re-reads the segment from L2 and writes the normalised values with
-// streaming stores.  Both sweeps issue a batch of independent 128-bit loads
-// before touching any of them.  Two 512-thread CTAs per SM keep the set of
-// live segments (296 of them) far below the L2 capacity; the register cap
-// (room for three CTAs) leaves space for the resident buckets' CTAs to run
-// beside them.
-#ifndef SWG_SOFTMAX_LONG_THREADS
-#define SWG_SOFTMAX_LONG_THREADS 512
-#endif
-#ifndef SWG_SOFTMAX_LONG_CTAS
-#define SWG_SOFTMAX_LONG_CTAS 2
-#endif
-constexpr int kLongThreads = SWG_SOFTMAX_LONG_THREADS;
-constexpr int kLongCtasPerSm = SWG_SOFTMAX_LONG_CTAS;
-#ifndef SWG_SOFTMAX_LONG_BATCH
-#define SWG_SOFTMAX_LONG_BATCH 4
-#endif
-#ifndef SWG_SOFTMAX_LONG_MINBLOCKS
-#define SWG_SOFTMAX_LONG_MINBLOCKS 3
-#endif
-constexpr int kLongBatch = SWG_SOFTMAX_LONG_BATCH;  // 128-bit loads in flight per thread, sweep A
-
+// Pieces of the streamed (two-sweep) schedule.
 struct MaxSum {
   float m, d;
 };
@@ -250,14 +227,6 @@ __device__ __forceinline__ uint64_t policy_evict_last() {
   uint64_t policy;
   asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
   return policy;
-}
-
-__device__ __forceinline__ float4 ld_keep4(const float4 *p, uint64_t policy) {
-  float4 q;
-  asm volatile("ld.global.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
-               : "=f"(q.x), "=f"(q.y), "=f"(q.z), "=f"(q.w)
-               : "l"(p), "l"(policy));
-  return q;
 }
 
 __device__ __forceinline__ float max4(const float4 q) {
@@ -295,140 +264,41 @@ __device__ __forceinline__ float4 normalise4(const float4 q, const float m,
   return r;
 }
 
-__global__ void __launch_bounds__(kLongThreads, SWG_SOFTMAX_LONG_MINBLOCKS)
-segsoftmax_long_kernel(const float *__restrict__ values,
-                       const int32_t *__restrict__ offsets,
-                       float *__restrict__ out,
-                       const int32_t *__restrict__ segments, int32_t count) {
-  __shared__ float scratch[32];
-  const int tid = threadIdx.x;
-  const uint64_t keep = policy_evict_last();
-  constexpr int64_t T = kLongThreads;
-  for (int64_t j = blockIdx.x; j < count; j += gridDim.x) {
-    const int32_t seg = __ldg(segments + j);
-    const int64_t begin = __ldg(offsets + seg);
-    const int64_t end = __ldg(offsets + seg + 1);
-    const float *p = values + begin;
-    float *o = out + begin;
-    const int64_t len = end - begin;
-    int head = head_elems(p);
-    if (head > len) head = (int)len;
-    const float4 *body = reinterpret_cast<const float4 *>(p + head);
-    const int64_t nvec = (len - head) >> 2;
-    const int64_t tail = head + (nvec << 2);
-    const int tail_count = (int)(len - tail);
-
-    // ---- sweep A ----
-    MaxSum s{-CUDART_INF_F, 0.0f};
-    float any = MaxOp::identity();  // NaN-propagating maximum
-    if (tid < head) {
-      online_add1(s, p[tid]);
-      any = MaxOp::apply(any, p[tid]);
-    }
-    int64_t i = tid;
-    for (; i + (kLongBatch - 1) * T < nvec; i += kLongBatch * T) {
-      float4 q[kLongBatch];
-#pragma unroll
-      for (int k = 0; k < kLongBatch; ++k) q[k] = ld_keep4(body + i + k * T, keep);
-      float lm = max4(q[0]);
-#pragma unroll
-      for (int k = 1; k < kLongBatch; ++k) lm = MaxOp::apply(lm, max4(q[k]));
-      any = MaxOp::apply(any, lm);
-      online_raise(s, lm);
-      if (s.m > -CUDART_INF_F) {
-        float d0 = 0.0f, d1 = 0.0f;
-#pragma unroll
-        for (int k = 0; k < kLongBatch; k += 2) {
-          d0 += expsum4(q[k], s.m);
-          d1 += expsum4(q[k + 1], s.m);
-        }
-        s.d += d0 + d1;
-      }
-    }
-    for (; i < nvec; i += T) {
-      const float4 q = ld_keep4(body + i, keep);
-      const float lm = max4(q);
-      any = MaxOp::apply(any, lm);
-      online_raise(s, lm);
-      if (s.m > -CUDART_INF_F) s.d += expsum4(q, s.m);
-    }
-    if (tid < tail_count) {
-      online_add1(s, p[tail + tid]);
-      any = MaxOp::apply(any, p[tail + tid]);
-    }
-    // combine: the segment maximum first (NaN-propagating), then the sums
-    // rescaled to it
-    const float m = cta_reduce<MaxOp>(any, scratch);
-    const float mine = s.d == 0.0f ? 0.0f : s.d * exp_neg(s.m - m);
-    const float d = cta_reduce<SumOp>(mine, scratch);
-    const float inv = 1.0f / d;
-
-    // ---- sweep B ----
-    const bool same_phase = (((uintptr_t)p ^ (uintptr_t)o) & 15u) == 0;
-    if (!same_phase) {
-      for (int64_t e = tid; e < len; e += T)
-        __stcs(o + e, exp_neg(p[e] - m) * inv);
-      continue;
-    }
-    if (tid < head) __stcs(o + tid, exp_neg(p[tid] - m) * inv);
-    float4 *obody = reinterpret_cast<float4 *>(o + head);
-    i = tid;
-    for (; i + 3 * T < nvec; i += 4 * T) {
-      const float4 q0 = __ldcs(body + i), q1 = __ldcs(body + i + T),
-                   q2 = __ldcs(body + i + 2 * T), q3 = __ldcs(body + i + 3 * T);
-      __stcs(obody + i, normalise4(q0, m, inv));
-      __stcs(obody + i + T, normalise4(q1, m, inv));
-      __stcs(obody + i + 2 * T, normalise4(q2, m, inv));
-      __stcs(obody + i + 3 * T, normalise4(q3, m, inv));
-    }
-    for (; i < nvec; i += T)
-      __stcs(obody + i, normalise4(__ldcs(body + i), m, inv));
-    if (tid < tail_count)
-      __stcs(o + tail + tid, exp_neg(p[tail + tid] - m) * inv);
-  }
-}
-
-// Ring kernel: one CTA per segment, two sweeps through a ring of kRingStages
-// shared-memory stages of kRingChunk values, filled by bulk async copies that
-// thread 0 issues up to a full ring ahead of the readers.
+// Ring kernel: one CTA per segment, two sweeps.  The segment is cut into
+// chunks of kRingChunk values dealt round-robin to the CTA's warps, and every
+// warp streams its chunks through a private ring of kStages shared-memory
+// stages filled by bulk async copies that its lane 0 issues:
 //
-//   sweep A  chunks 0 .. n-1: running (maximum, sum of exp) per thread;
-//   sweep B  chunks n-1 .. 0: normalise and store.
+//   sweep A  its chunks in ascending order: running (maximum, sum of exp) per
+//            lane; a stage is refilled as soon as the warp has read it;
+//   sweep B  its chunks in descending order: normalise and store.
 //
-// Sweep B walks backwards, so the last kRingStages chunks of sweep A are still
-// in the ring and are not loaded again: a segment of up to kRingStages chunks
-// is read from HBM once and never again, a longer one re-reads all but its
-// tail, most recent lines first, which L2 serves (sweep A loads of chunks
-// that will come back carry an evict-last policy, everything else
-// evict-first).  Chunk c lives in stage c % kRingStages in both sweeps.
+// Sweep B walks backwards, so the last kStages chunks a warp saw in sweep A
+// are still in its ring and are not loaded again: a segment of up to
+// warps * kStages chunks is read from HBM once and never again, a longer one
+// re-reads all but that tail, most recent lines first, which L2 serves (sweep
+// A loads of chunks that will come back carry an evict-last policy,
+// everything else evict-first).  A stage has a single reader -- the warp that
+// owns it -- so handing it back to the copy engine needs no barrier, only a
+// warp vote that depends on the loaded values; each stage has one mbarrier
+// counting the copy's bytes.
+//
+// The stages that sweep B empties for good are refilled at once with the
+// first chunks of the CTA's next segment, so the copy engine never idles
+// between segments.  For the order in which sweep B frees stages (last chunk
+// first) to be the order in which the next sweep A wants them (first chunk
+// first), the chunk -> stage map runs upwards on even segments and downwards
+// on odd ones.
 //
 // A chunk is a run of whole 16-byte lines of `values` counted from the line
 // that holds the segment's first value, so every copy is aligned whatever
 // the offsets are; the up-to-three values that share a line with the array's
 // ends are fetched by plain loads.
 //
-// Every stage has a `full` barrier (one arrival + the copy's bytes per load)
-// and an `empty` barrier (one arrival per warp, after the last read of what
-// was loaded).  All waits are bounded; a wait that gives up raises the
-// plan's timeout flag and the CTA walks to the end without touching the ring.
-#ifndef SWG_RING_STAGES
-#define SWG_RING_STAGES 8
-#endif
-constexpr int kRingStages = SWG_RING_STAGES;
-constexpr int kRingChunk = 2048;
-constexpr int kRingThreads = 256;
-constexpr int kRingWarps = kRingThreads / 32;
-constexpr int kRingVectors = kRingChunk / 4 / kRingThreads;  // per thread
-static_assert(kRingStages >= 2 && kRingStages <= 27, "ring size");
-constexpr int kRingBytes = kRingStages * kRingChunk * 4;
-// CTAs that fit an SM's 227 KB of shared memory (1 KB reserved per CTA)
-constexpr int kRingCtasPerSm =
-    (227 * 1024) / (kRingBytes + 1024 + 256) < 2048 / kRingThreads
-        ? (227 * 1024) / (kRingBytes + 1024 + 256)
-        : 2048 / kRingThreads;
-#ifndef SWG_SOFTMAX_RING
-#define SWG_SOFTMAX_RING 1
-#endif
+// All waits are bounded; a wait that gives up raises the plan's timeout flag
+// and the CTA walks to the end without touching the ring.
+constexpr int kRingChunk = 512;
+constexpr int kRingVectors = kRingChunk / 128;  // 128-bit loads per lane per chunk
 
 __device__ __forceinline__ uint64_t policy_evict_first() {
   uint64_t policy;
@@ -450,197 +320,294 @@ __device__ __forceinline__ void bulk_g2s_hint(void *dst_smem,
 struct RingSegment {
   int64_t begin, end;  // the segment's values
   int64_t origin;      // index of slot 0: the aligned line holding `begin`
-  int64_t last_line;   // first index past the last whole line of the array
   int64_t line_end;    // index past the line holding the segment's last value
-  int mis;             // (values pointer / 4) mod 4
+  int64_t slots;       // valid slots: [shift, slots)
+  int chunks;          // chunks of the segment (0: no such segment)
+  int shift;           // begin - origin
 };
 
-// Thread 0 only: waits until the stage's previous contents have been read by
-// every warp, then starts the copy of chunk `c` into it.
-__device__ __forceinline__ bool ring_issue(const RingSegment &g,
+// [begin, end) of the j-th segment of the list; {0, 0} past its end.
+__device__ __forceinline__ int2
+ring_bounds(const int32_t *__restrict__ offsets,
+            const int32_t *__restrict__ segments, int64_t j, int32_t count) {
+  if (j >= count) return make_int2(0, 0);
+  const int32_t seg = __ldg(segments + j);
+  return make_int2(__ldg(offsets + seg), __ldg(offsets + seg + 1));
+}
+
+__device__ __forceinline__ RingSegment ring_segment(const int2 bounds,
+                                                    int mis) {
+  RingSegment g;
+  g.begin = bounds.x;
+  g.end = bounds.y;
+  g.shift = (int)((g.begin + mis) & 3);
+  g.origin = g.begin - g.shift;
+  g.line_end = g.end + ((4 - ((g.end + mis) & 3)) & 3);
+  g.slots = (int64_t)g.shift + (g.end - g.begin);
+  g.chunks =
+      bounds.y > bounds.x ? (int)((g.slots + kRingChunk - 1) / kRingChunk) : 0;
+  return g;
+}
+
+// One lane: starts the copy of the segment's chunk `c` into `slot`.  The
+// caller has made sure that nobody reads the slot any more.
+__device__ __forceinline__ void ring_issue(const RingSegment &g,
                                            const float *__restrict__ values,
-                                           float *ring, uint64_t *full,
-                                           uint64_t *empty, int64_t c,
-                                           uint32_t &loaded,
-                                           uint32_t &empty_parity,
+                                           int64_t last_line, float *slot,
+                                           uint64_t *full, int c,
                                            uint64_t policy) {
-  const int stage = (int)(c % kRingStages);
-  const uint32_t bit = 1u << stage;
-  if (loaded & bit) {
-    if (!mbar_wait(&empty[stage], (empty_parity & bit) ? 1u : 0u)) return false;
-    empty_parity ^= bit;
+  const int64_t g0 = g.origin + (int64_t)c * kRingChunk;
+  if (c > 0 && c < g.chunks - 1) {  // whole lines well inside the array
+    mbar_arrive_expect_tx(full, kRingChunk * 4);
+    bulk_g2s_hint(slot, values + g0, kRingChunk * 4, full, policy);
+    return;
   }
-  loaded |= bit;
-  float *slot = ring + stage * kRingChunk;
-  const int64_t g0 = g.origin + c * kRingChunk;
   int64_t g1 = g0 + kRingChunk;
   if (g1 > g.line_end) g1 = g.line_end;
   int64_t lo = g0 < 0 ? g0 + 4 : g0;
-  int64_t hi = g1 > g.last_line ? g.last_line : g1;
+  int64_t hi = g1 > last_line ? last_line : g1;
   if (hi < lo) hi = lo;
   const int64_t vb = g.begin > g0 ? g.begin : g0;
   const int64_t ve = g.end < g1 ? g.end : g1;
   for (int64_t i = vb; i < ve && i < lo; ++i) slot[i - g0] = values[i];
   for (int64_t i = hi > vb ? hi : vb; i < ve; ++i) slot[i - g0] = values[i];
   const uint32_t bytes = (uint32_t)(hi - lo) * 4u;
-  mbar_arrive_expect_tx(&full[stage], bytes);
-  if (bytes)
-    bulk_g2s_hint(slot + (lo - g0), values + lo, bytes, &full[stage], policy);
-  return true;
+  mbar_arrive_expect_tx(full, bytes);
+  if (bytes) bulk_g2s_hint(slot + (lo - g0), values + lo, bytes, full, policy);
 }
 
-__global__ void __launch_bounds__(kRingThreads)
+// Returns once every lane of the warp HOLDS what it loaded from a stage.  A
+// bulk copy into the stage may only be started after this: __syncwarp alone
+// orders the issue of the loads, not their completion, and a copy served by
+// L2 can land before a shared-memory load that is still queued behind the
+// SM's global stores.  The vote consumes one word of every 128-bit load, so
+// it cannot issue before the loads have returned.
+__device__ __forceinline__ void ring_loads_landed(
+    const float4 (&q)[kRingVectors]) {
+  uint32_t word = 0;
+#pragma unroll
+  for (int v = 0; v < kRingVectors; ++v) word |= __float_as_uint(q[v].w);
+  const unsigned seen = __ballot_sync(kFullMask, word != 0x7fedcba9u);
+  asm volatile("" ::"r"(seen) : "memory");
+}
+
+template <int kWarps, int kStages, int kCtasPerSm>
+__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
 segsoftmax_ring_kernel(const float *__restrict__ values,
                        const int32_t *__restrict__ offsets,
                        float *__restrict__ out,
                        const int32_t *__restrict__ segments, int32_t count,
                        int32_t value_count, uint32_t *__restrict__ control) {
+  static_assert(kWarps <= 32 && kStages >= 1 && kStages <= 16, "ring shape");
   extern __shared__ __align__(128) unsigned char smem[];
-  float *ring = reinterpret_cast<float *>(smem);
-  __shared__ uint64_t full[kRingStages], empty[kRingStages];
+  __shared__ uint64_t full_all[kWarps * kStages];
   __shared__ float scratch[32];
   const int tid = threadIdx.x;
-  const int lane = tid & 31;
-  if (tid == 0) {
-    for (int s = 0; s < kRingStages; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], kRingWarps);
-    }
+  const int lane = tid & 31, warp = tid >> 5;
+  float *ring = reinterpret_cast<float *>(smem) + warp * kStages * kRingChunk;
+  uint64_t *full = full_all + warp * kStages;
+  if (lane == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
     fence_mbar_init();
   }
   __syncthreads();
   const uint64_t keep = policy_evict_last();
   const uint64_t once = policy_evict_first();
-  RingSegment g;
-  g.mis = (int)(((uintptr_t)values >> 2) & 3);
-  g.last_line = (int64_t)value_count - ((value_count + g.mis) & 3);
+  const int mis = (int)(((uintptr_t)values >> 2) & 3);
+  const int64_t last_line = (int64_t)value_count - ((value_count + mis) & 3);
   const bool same_phase =
-      (int)(((uintptr_t)out >> 2) & 3) == g.mis;  // lines of out = lines of values
-  uint32_t full_parity = 0;                // every thread, one bit per stage
-  uint32_t empty_parity = 0, loaded = 0;   // thread 0
+      (int)(((uintptr_t)out >> 2) & 3) == mis;  // lines of out = lines of values
+  uint32_t parity = 0;  // one bit per stage of this warp's ring
   bool failed = false;
+  // this warp's chunks of a segment: warp, warp + kWarps, ...
+  auto share = [&](const RingSegment &r) {
+    return r.chunks > warp ? (r.chunks - warp + kWarps - 1) / kWarps : 0;
+  };
 
-  for (int64_t j = blockIdx.x; j < count; j += gridDim.x) {
-    const int32_t seg = __ldg(segments + j);
-    g.begin = __ldg(offsets + seg);
-    g.end = __ldg(offsets + seg + 1);
-    const int shift = (int)((g.begin + g.mis) & 3);
-    g.origin = g.begin - shift;
-    g.line_end = g.end + ((4 - ((g.end + g.mis) & 3)) & 3);
-    const int64_t slots = (int64_t)shift + (g.end - g.begin);  // valid: [shift, slots)
-    const int64_t n = (slots + kRingChunk - 1) / kRingChunk;
-    const int64_t resident_from = n > kRingStages ? n - kRingStages : 0;
+  RingSegment g =
+      ring_segment(ring_bounds(offsets, segments, blockIdx.x, count), mis);
+  int mine = share(g);
+  if (lane == 0)
+    for (int k = 0; k < mine && k < kStages; ++k)
+      ring_issue(g, values, last_line, ring + k * kRingChunk, &full[k],
+                 k * kWarps + warp, k + kStages < mine ? keep : once);
 
-    if (tid == 0 && !failed)
-      for (int64_t c = 0; c < n && c < kRingStages && !failed; ++c)
-        failed = !ring_issue(g, values, ring, full, empty, c, loaded,
-                             empty_parity, c < resident_from ? keep : once);
+  bool down = false;  // direction of the chunk -> stage map
+  for (int64_t j = blockIdx.x; j < count; j += gridDim.x, down = !down) {
+    // the next segment's bounds are fetched now and used after sweep A
+    const int2 next_bounds =
+        ring_bounds(offsets, segments, j + gridDim.x, count);
+    const int resident_from = mine > kStages ? mine - kStages : 0;
+    auto stage_of = [&](int k, bool reversed) {
+      return reversed ? kStages - 1 - k % kStages : k % kStages;
+    };
 
     // ---- sweep A ----
     MaxSum s{-CUDART_INF_F, 0.0f};
     float any = MaxOp::identity();  // NaN-propagating maximum
-    for (int64_t c = 0; c < n && !failed; ++c) {
-      if (tid == 0 && c >= 1 && c + kRingStages - 1 < n) {
-        const int64_t ahead = c + kRingStages - 1;
-        if (!ring_issue(g, values, ring, full, empty, ahead, loaded,
-                        empty_parity, ahead < resident_from ? keep : once)) {
-          failed = true;
-          break;
-        }
-      }
-      const int stage = (int)(c % kRingStages);
+    for (int k = 0; k < mine && !failed; ++k) {
+      const int stage = stage_of(k, down);
       const uint32_t bit = 1u << stage;
-      if (!mbar_wait(&full[stage], (full_parity & bit) ? 1u : 0u)) {
+      const bool ok = mbar_wait(&full[stage], (parity & bit) ? 1u : 0u);
+      if (__any_sync(kFullMask, !ok)) {
         failed = true;
         break;
       }
-      full_parity ^= bit;
-      const float4 *slot =
-          reinterpret_cast<const float4 *>(ring + stage * kRingChunk);
+      parity ^= bit;
+      float *slot = ring + stage * kRingChunk;
+      const int c = k * kWarps + warp;
       // valid local slots of this chunk: [l0, l1)
-      const int l0 = c == 0 ? shift : 0;
-      const int64_t left = slots - c * kRingChunk;
+      const int l0 = c == 0 ? g.shift : 0;
+      const int64_t left = g.slots - (int64_t)c * kRingChunk;
       const int l1 = left < kRingChunk ? (int)left : kRingChunk;
       float4 q[kRingVectors];
 #pragma unroll
-      for (int k = 0; k < kRingVectors; ++k) {
-        const int i = tid + k * kRingThreads;
-        q[k] = slot[i];
-        if (4 * i < l0 || 4 * i + 4 > l1) {
-          if (4 * i + 0 < l0 || 4 * i + 0 >= l1) q[k].x = MaxOp::identity();
-          if (4 * i + 1 < l0 || 4 * i + 1 >= l1) q[k].y = MaxOp::identity();
-          if (4 * i + 2 < l0 || 4 * i + 2 >= l1) q[k].z = MaxOp::identity();
-          if (4 * i + 3 < l0 || 4 * i + 3 >= l1) q[k].w = MaxOp::identity();
-        }
+      for (int v = 0; v < kRingVectors; ++v)
+        q[v] = reinterpret_cast<const float4 *>(slot)[lane + v * 32];
+      if (k < resident_from) {  // comes back for sweep B: refill the stage now
+        ring_loads_landed(q);
+        if (lane == 0)
+          ring_issue(g, values, last_line, slot, &full[stage],
+                     (k + kStages) * kWarps + warp,
+                     k + kStages < resident_from ? keep : once);
       }
-      if (c < resident_from) {  // will be loaded again for sweep B
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[stage]);
+      if (l0 > 0 || l1 < kRingChunk) {
+#pragma unroll
+        for (int v = 0; v < kRingVectors; ++v) {
+          const int i = 4 * (lane + v * 32);
+          if (i + 0 < l0 || i + 0 >= l1) q[v].x = MaxOp::identity();
+          if (i + 1 < l0 || i + 1 >= l1) q[v].y = MaxOp::identity();
+          if (i + 2 < l0 || i + 2 >= l1) q[v].z = MaxOp::identity();
+          if (i + 3 < l0 || i + 3 >= l1) q[v].w = MaxOp::identity();
+        }
       }
       float lm = max4(q[0]);
 #pragma unroll
-      for (int k = 1; k < kRingVectors; ++k) lm = MaxOp::apply(lm, max4(q[k]));
+      for (int v = 1; v < kRingVectors; ++v) lm = MaxOp::apply(lm, max4(q[v]));
       any = MaxOp::apply(any, lm);
       online_raise(s, lm);
       if (s.m > -CUDART_INF_F) {
         float d0 = 0.0f;
 #pragma unroll
-        for (int k = 0; k < kRingVectors; ++k) d0 += expsum4(q[k], s.m);
+        for (int v = 0; v < kRingVectors; ++v) d0 += expsum4(q[v], s.m);
         s.d += d0;
       }
     }
     if (failed) atomicCAS(control + 2, 0u, 1u);
     // the segment maximum first (NaN-propagating), then the sums rescaled to it
     const float m = cta_reduce<MaxOp>(any, scratch);
-    const float mine = s.d == 0.0f ? 0.0f : s.d * exp_neg(s.m - m);
-    const float d = cta_reduce<SumOp>(mine, scratch);
+    const float part = s.d == 0.0f ? 0.0f : s.d * exp_neg(s.m - m);
+    const float d = cta_reduce<SumOp>(part, scratch);
     const float inv = 1.0f / d;
 
+    // ---- the CTA's next segment: its first chunks go into the stages this
+    // segment did not use, then into each stage sweep B is done with
+    const RingSegment next = ring_segment(next_bounds, mis);
+    const int next_mine = share(next);
+    const int used = mine < kStages ? mine : kStages;
+    __syncwarp();
+    if (lane == 0 && !failed)
+      for (int k = 0; k < kStages - used && k < next_mine; ++k) {
+        const int stage = stage_of(k, !down);
+        ring_issue(next, values, last_line, ring + stage * kRingChunk,
+                   &full[stage], k * kWarps + warp,
+                   k + kStages < next_mine ? keep : once);
+      }
+
     // ---- sweep B ----
-    for (int64_t c = n - 1; c >= 0 && !failed; --c) {
-      if (tid == 0 && c <= n - 2 && c + 1 - kRingStages >= 0) {
-        if (!ring_issue(g, values, ring, full, empty, c + 1 - kRingStages,
-                        loaded, empty_parity, once)) {
-          failed = true;
-          break;
-        }
-      }
-      const int stage = (int)(c % kRingStages);
+    for (int k = mine - 1; k >= 0 && !failed; --k) {
+      const int stage = stage_of(k, down);
       const uint32_t bit = 1u << stage;
-      if (c < resident_from) {
-        if (!mbar_wait(&full[stage], (full_parity & bit) ? 1u : 0u)) {
+      if (k < resident_from) {  // loaded again
+        const bool ok = mbar_wait(&full[stage], (parity & bit) ? 1u : 0u);
+        if (__any_sync(kFullMask, !ok)) {
           failed = true;
           break;
         }
-        full_parity ^= bit;
+        parity ^= bit;
       }
-      const float4 *slot =
-          reinterpret_cast<const float4 *>(ring + stage * kRingChunk);
-      const int l0 = c == 0 ? shift : 0;
-      const int64_t left = slots - c * kRingChunk;
+      float *slot = ring + stage * kRingChunk;
+      const int c = k * kWarps + warp;
+      const int l0 = c == 0 ? g.shift : 0;
+      const int64_t left = g.slots - (int64_t)c * kRingChunk;
       const int l1 = left < kRingChunk ? (int)left : kRingChunk;
-      float *o = out + (g.origin + c * kRingChunk);  // local slot 0
+      float *o = out + (g.origin + (int64_t)c * kRingChunk);  // local slot 0
       float4 q[kRingVectors];
 #pragma unroll
-      for (int k = 0; k < kRingVectors; ++k) q[k] = slot[tid + k * kRingThreads];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[stage]);
-#pragma unroll
-      for (int k = 0; k < kRingVectors; ++k) {
-        const int i = tid + k * kRingThreads;
-        const float4 r = normalise4(q[k], m, inv);
-        if (same_phase && 4 * i >= l0 && 4 * i + 4 <= l1) {
-          __stcs(reinterpret_cast<float4 *>(o) + i, r);
+      for (int v = 0; v < kRingVectors; ++v)
+        q[v] = reinterpret_cast<const float4 *>(slot)[lane + v * 32];
+      ring_loads_landed(q);
+      if (lane == 0) {
+        if (k >= kStages) {
+          ring_issue(g, values, last_line, slot, &full[stage],
+                     (k - kStages) * kWarps + warp, once);
         } else {
-          if (4 * i + 0 >= l0 && 4 * i + 0 < l1) __stcs(o + 4 * i + 0, r.x);
-          if (4 * i + 1 >= l0 && 4 * i + 1 < l1) __stcs(o + 4 * i + 1, r.y);
-          if (4 * i + 2 >= l0 && 4 * i + 2 < l1) __stcs(o + 4 * i + 2, r.z);
-          if (4 * i + 3 >= l0 && 4 * i + 3 < l1) __stcs(o + 4 * i + 3, r.w);
+          const int k_next = kStages - 1 - k;  // same stage, opposite map
+          if (k_next < next_mine)
+            ring_issue(next, values, last_line, slot, &full[stage],
+                       k_next * kWarps + warp,
+                       k_next + kStages < next_mine ? keep : once);
+        }
+      }
+      if (same_phase && l0 == 0 && l1 == kRingChunk) {
+#pragma unroll
+        for (int v = 0; v < kRingVectors; ++v)
+          __stcs(reinterpret_cast<float4 *>(o) + lane + v * 32,
+                 normalise4(q[v], m, inv));
+      } else {
+#pragma unroll
+        for (int v = 0; v < kRingVectors; ++v) {
+          const int i = 4 * (lane + v * 32);
+          const float4 r = normalise4(q[v], m, inv);
+          if (same_phase && i >= l0 && i + 4 <= l1) {
+            __stcs(reinterpret_cast<float4 *>(o + i), r);
+          } else {
+            if (i + 0 >= l0 && i + 0 < l1) __stcs(o + i + 0, r.x);
+            if (i + 1 >= l0 && i + 1 < l1) __stcs(o + i + 1, r.y);
+            if (i + 2 >= l0 && i + 2 < l1) __stcs(o + i + 2, r.z);
+            if (i + 3 >= l0 && i + 3 < l1) __stcs(o + i + 3, r.w);
+          }
         }
       }
     }
     if (failed) atomicCAS(control + 2, 0u, 1u);
+    g = next;
+    mine = next_mine;
   }
+}
+
+// Ring shapes (warps, stages per warp, CTAs per SM), one per length class:
+// the smallest ring that still holds a whole segment of the class, so that as
+// many CTAs as possible share an SM while every value is read from HBM once.
+//   bucket 3  (2048, 8192]    4 warps x 4 stages, 6 CTAs/SM   32 KB each
+//   bucket 4  (8192, 16384]   8 warps x 4 stages, 3 CTAs/SM   64 KB each
+//   bucket 5  (16384, 28672] 14 warps x 4 stages, 2 CTAs/SM  112 KB each
+//   bucket 6  longer         16 warps x 7 stages, 1 CTA/SM   224 KB: whole
+//             up to 57344 values, above that all but the last 57344 values of
+//             a segment are read a second time (from L2 when they are still
+//             there)
+constexpr int kFirstRingBucket = 3;
+
+template <int kWarps, int kStages, int kCtasPerSm>
+static cudaError_t ring_launch(const float *values, const int32_t *offsets,
+                               float *out, const int32_t *segments,
+                               int32_t count, int32_t value_count,
+                               const DevicePlan &plan, cudaStream_t stream,
+                               bool configure) {
+  constexpr int kBytes = kWarps * kStages * kRingChunk * 4;
+  static_assert((kBytes + 1024 + 8 * kWarps * kStages + 128) * kCtasPerSm <=
+                    228 * 1024,
+                "rings exceed shared memory");
+  if (configure)
+    return cudaFuncSetAttribute(
+        segsoftmax_ring_kernel<kWarps, kStages, kCtasPerSm>,
+        cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
+  int grid = plan.sm_count * kCtasPerSm;
+  if (grid > count) grid = count;
+  segsoftmax_ring_kernel<kWarps, kStages, kCtasPerSm>
+      <<<grid, kWarps * 32, kBytes, stream>>>(values, offsets, out, segments,
+                                              count, value_count, plan.control);
+  return cudaGetLastError();
 }
 
 // Side streams so the bucket kernels of one call run concurrently: created once
@@ -649,9 +616,9 @@ segsoftmax_ring_kernel(const float *__restrict__ values,
 namespace {
 struct Fork {
   bool ready = false;
-  cudaStream_t side[3];
+  cudaStream_t side[kSoftmaxBuckets - 1];
   cudaEvent_t begin;
-  cudaEvent_t done[3];
+  cudaEvent_t done[kSoftmaxBuckets - 1];
 };
 std::mutex g_fork_lock;
 Fork g_fork[64];
@@ -662,7 +629,7 @@ cudaError_t fork_for(int device, Fork **fork) {
   if (!f.ready) {
     cudaError_t e =
         cudaEventCreateWithFlags(&f.begin, cudaEventDisableTiming);
-    for (int i = 0; i < 3 && e == cudaSuccess; ++i) {
+    for (int i = 0; i < kSoftmaxBuckets - 1 && e == cudaSuccess; ++i) {
       e = cudaStreamCreateWithFlags(&f.side[i], cudaStreamNonBlocking);
       if (e == cudaSuccess)
         e = cudaEventCreateWithFlags(&f.done[i], cudaEventDisableTiming);
@@ -675,10 +642,36 @@ cudaError_t fork_for(int device, Fork **fork) {
 }
 }  // namespace
 
+template <bool kConfigure>
+static cudaError_t ring_bucket(int bucket, const float *values,
+                               const int32_t *offsets, float *out,
+                               const int32_t *segments, int32_t count,
+                               int32_t value_count, const DevicePlan &plan,
+                               cudaStream_t stream) {
+  switch (bucket) {
+    case 3:
+      return ring_launch<4, 4, 6>(values, offsets, out, segments, count,
+                                  value_count, plan, stream, kConfigure);
+    case 4:
+      return ring_launch<8, 4, 3>(values, offsets, out, segments, count,
+                                  value_count, plan, stream, kConfigure);
+    case 5:
+      return ring_launch<14, 4, 2>(values, offsets, out, segments, count,
+                                   value_count, plan, stream, kConfigure);
+    default:
+      return ring_launch<16, 7, 1>(values, offsets, out, segments, count,
+                                   value_count, plan, stream, kConfigure);
+  }
+}
+
 cudaError_t configure_softmax_kernels() {
-  return cudaFuncSetAttribute(segsoftmax_ring_kernel,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              kRingBytes);
+  DevicePlan none;
+  for (int bucket = kFirstRingBucket; bucket < kSoftmaxBuckets; ++bucket) {
+    cudaError_t e = ring_bucket<true>(bucket, nullptr, nullptr, nullptr,
+                                      nullptr, 0, 0, none, nullptr);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
 }
 
 cudaError_t launch_segsoftmax_planned(const float *values,
@@ -687,6 +680,9 @@ cudaError_t launch_segsoftmax_planned(const float *values,
                                       const DevicePlan &plan,
                                       cudaStream_t stream,
                                       const Probe *probe) {
+  static_assert(kSoftmaxBuckets == 7 && kSoftmaxLimit[0] == 8 * 8 &&
+                    kSoftmaxLimit[1] == 32 * 16 && kSoftmaxLimit[2] == 128 * 16,
+                "bucket limits are the capacities of the resident kernels");
   Fork *fork = nullptr;
   cudaError_t e = fork_for(plan.device, &fork);
   if (e != cudaSuccess) return e;
@@ -694,38 +690,39 @@ cudaError_t launch_segsoftmax_planned(const float *values,
   e = cudaEventRecord(fork->begin, stream);
   if (e != cudaSuccess) return e;
   const int32_t *list = plan.softmax_segments;
-  const int32_t n_stream = plan.softmax_count[3];
-  if (n_stream > 0) {
-#if SWG_SOFTMAX_RING
-    int grid = plan.sm_count * kRingCtasPerSm;
-    if (grid > n_stream) grid = n_stream;
-    segsoftmax_ring_kernel<<<grid, kRingThreads, kRingBytes, stream>>>(
-        values, offsets, out, list + plan.softmax_begin[3], n_stream,
-        value_count, plan.control);
-#else
-    int grid = plan.sm_count * kLongCtasPerSm;
-    if (grid > n_stream) grid = n_stream;
-    segsoftmax_long_kernel<<<grid, kLongThreads, 0, stream>>>(
-        values, offsets, out, list + plan.softmax_begin[3], n_stream);
-#endif
+  // the longest class on the caller's stream, the others beside it, longest
+  // first
+  constexpr int kLast = kSoftmaxBuckets - 1;
+  if (plan.softmax_count[kLast] > 0) {
+    e = ring_bucket<false>(kLast, values, offsets, out,
+                           list + plan.softmax_begin[kLast],
+                           plan.softmax_count[kLast], value_count, plan,
+                           stream);
+    if (e != cudaSuccess) return e;
   }
-  for (int b = 2; b >= 0; --b) {
+  for (int b = kLast - 1; b >= 0; --b) {
     const int32_t n = plan.softmax_count[b];
     if (n == 0) continue;
     cudaStream_t side = fork->side[b];
     e = cudaStreamWaitEvent(side, fork->begin, 0);
     if (e != cudaSuccess) return e;
     const int32_t *bucket = list + plan.softmax_begin[b];
-    if (b == 2)
-      segsoftmax_resident_kernel<512>
-          <<<(unsigned)n, 512, 0, side>>>(values, offsets, out, bucket, n);
-    else if (b == 1)
-      segsoftmax_resident_kernel<128>
+    if (b >= kFirstRingBucket) {
+      e = ring_bucket<false>(b, values, offsets, out, bucket, n, value_count,
+                             plan, side);
+      if (e != cudaSuccess) return e;
+    } else if (b == 2) {
+      segsoftmax_resident_kernel<128, 16>
           <<<(unsigned)n, 128, 0, side>>>(values, offsets, out, bucket, n);
-    else
-      segsoftmax_resident_kernel<32>
+    } else if (b == 1) {
+      segsoftmax_resident_kernel<32, 16>
           <<<(unsigned)((n + 7) / 8), 256, 0, side>>>(values, offsets, out,
                                                       bucket, n);
+    } else {
+      segsoftmax_resident_kernel<8, 8>
+          <<<(unsigned)((n + 31) / 32), 256, 0, side>>>(values, offsets, out,
+                                                        bucket, n);
+    }
     e = cudaEventRecord(fork->done[b], side);
     if (e != cudaSuccess) return e;
     e = cudaStreamWaitEvent(stream, fork->done[b], 0);

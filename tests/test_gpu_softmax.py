@@ -45,7 +45,9 @@ def test_small_cases(schedule):
                     [1, 257, 2, 3837], [4097], [129, 0, 128, 127, 1],
                     [511, 512, 513], [2047, 2048, 2049], [8191, 8192, 8193],
                     [16384, 3, 20000], [8192, 8193, 8200, 65535, 65536, 65537],
-                    [9001, 30011, 12345]):
+                    [9001, 30011, 12345], [63, 64, 65, 1, 8, 9, 7, 0, 64],
+                    [16383, 16384, 16385, 28671, 28672, 28673, 57343, 57344,
+                     57345]):
         offsets = offsets_from_lengths(lengths)
         values = (2 * rng.standard_normal(offsets[-1] + 2)).astype(np.float32)
         result = check_softmax(values, offsets, schedule)
