@@ -55,11 +55,11 @@ struct SplitSegment {
 
 // Softmax buckets by segment length: the first three are held in the
 // registers of eight lanes / a warp / a 128-thread CTA; the longer ones go
-// through shared-memory rings whose size grows with the class, so that a
-// segment of the fourth to sixth class -- and of the seventh, up to 57344
-// values -- stays on the SM between its two sweeps.
-constexpr int kSoftmaxBuckets = 7;
-constexpr int kSoftmaxLimit[kSoftmaxBuckets - 1] = {64,   512,   2048,
+// through shared-memory rings whose size doubles from class to class, so that
+// a segment -- in the last class, one of up to 57344 values -- stays on the SM
+// between its two sweeps.
+constexpr int kSoftmaxBuckets = 8;
+constexpr int kSoftmaxLimit[kSoftmaxBuckets - 1] = {64,   512,  2048, 4096,
                                                     8192, 16384, 28672};
 
 struct HostPlan {

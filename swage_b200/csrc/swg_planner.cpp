@@ -224,9 +224,12 @@ void plan_reduce(const int32_t *offsets, int32_t segment_count,
   plan->medium_split_count = (int32_t)(after_medium - after_big);
 }
 
-// Softmax: bucket the non-empty segments by length.  Inside the streamed
-// bucket segments are emitted bin by bin from the longest (a counting sort on
-// the histogram bins), so that CTAs walking it round-robin get similar work.
+// Softmax: bucket the non-empty segments by length.  Inside a bucket segments
+// keep their order in memory: CTAs walking the bucket side by side then read
+// neighbouring addresses, which measured several per cent faster than any
+// order by length.  The last bucket has no upper limit, so there segments are
+// emitted bin by bin from the longest (a counting sort on the histogram
+// bins): a few giant segments must start first.
 static inline int softmax_bucket(int64_t length) {
   for (int b = 0; b < kSoftmaxBuckets - 1; ++b)
     if (length <= kSoftmaxLimit[b]) return b;
@@ -235,8 +238,8 @@ static inline int softmax_bucket(int64_t length) {
 
 void plan_softmax(const int32_t *offsets, int32_t segment_count,
                   HostPlan *plan) {
-  // slot = bucket for the resident buckets, then one slot per length bin,
-  // longest first, for the streamed one: one counting sort over all of them
+  // slot = bucket for all buckets but the last, then one slot per length
+  // bin, longest first, for the last: one counting sort over all of them
   const int slots = kSoftmaxBuckets - 1 + kHistogramBins;
   std::vector<int64_t> fill((size_t)slots, 0), start((size_t)slots, 0);
   auto slot_of = [](int64_t length) {
@@ -314,7 +317,7 @@ std::string describe_host_plan(const HostPlan &plan) {
            "\"split_segments\": %zu, \"partial_slots\": %d, "
            "\"tile_values\": %d, \"tile_items\": %d, "
            "\"tile_max_segments\": %d, "
-           "\"split_minimum\": %d, \"softmax_buckets\": [%d, %d, %d, %d, %d, %d, %d], ",
+           "\"split_minimum\": %d, \"softmax_buckets\": [%d, %d, %d, %d, %d, %d, %d, %d], ",
            plan.segment_count, plan.value_count, plan.op, plan.schedule,
            plan.mean_length, (long long)plan.max_length, plan.tasks.size(),
            (long long)plan.pack_tasks, (long long)plan.chunk_tasks,
@@ -322,7 +325,7 @@ std::string describe_host_plan(const HostPlan &plan) {
            kTileMaxSegments,
            kSplitMinimum, plan.softmax_count[0], plan.softmax_count[1],
            plan.softmax_count[2], plan.softmax_count[3], plan.softmax_count[4],
-           plan.softmax_count[5], plan.softmax_count[6]);
+           plan.softmax_count[5], plan.softmax_count[6], plan.softmax_count[7]);
   text += buffer;
   text += "\"histogram\": [";
   for (int bin = 0; bin < kHistogramBins; ++bin) {

@@ -579,13 +579,16 @@ segsoftmax_ring_kernel(const float *__restrict__ values,
 // Ring shapes (warps, stages per warp, CTAs per SM), one per length class:
 // the smallest ring that still holds a whole segment of the class, so that as
 // many CTAs as possible share an SM while every value is read from HBM once.
-//   bucket 3  (2048, 8192]    4 warps x 4 stages, 6 CTAs/SM   32 KB each
-//   bucket 4  (8192, 16384]   8 warps x 4 stages, 3 CTAs/SM   64 KB each
-//   bucket 5  (16384, 28672] 14 warps x 4 stages, 2 CTAs/SM  112 KB each
-//   bucket 6  longer         16 warps x 7 stages, 1 CTA/SM   224 KB: whole
+//   bucket 3  (2048, 4096]    2 warps x 4 stages, 12 CTAs/SM  16 KB each
+//   bucket 4  (4096, 8192]    4 warps x 4 stages,  6 CTAs/SM  32 KB each
+//   bucket 5  (8192, 16384]   8 warps x 4 stages,  3 CTAs/SM  64 KB each
+//   bucket 6  (16384, 28672] 14 warps x 4 stages,  2 CTAs/SM 112 KB each
+//   bucket 7  longer         16 warps x 7 stages,  1 CTA/SM  224 KB: whole
 //             up to 57344 values, above that all but the last 57344 values of
 //             a segment are read a second time (from L2 when they are still
 //             there)
+// (A one-warp ring for (512, 2048] measured slower than the 128-thread
+// register kernel, which keeps that class.)
 constexpr int kFirstRingBucket = 3;
 
 template <int kWarps, int kStages, int kCtasPerSm>
@@ -650,12 +653,15 @@ static cudaError_t ring_bucket(int bucket, const float *values,
                                cudaStream_t stream) {
   switch (bucket) {
     case 3:
+      return ring_launch<2, 4, 12>(values, offsets, out, segments, count,
+                                   value_count, plan, stream, kConfigure);
+    case 4:
       return ring_launch<4, 4, 6>(values, offsets, out, segments, count,
                                   value_count, plan, stream, kConfigure);
-    case 4:
+    case 5:
       return ring_launch<8, 4, 3>(values, offsets, out, segments, count,
                                   value_count, plan, stream, kConfigure);
-    case 5:
+    case 6:
       return ring_launch<14, 4, 2>(values, offsets, out, segments, count,
                                    value_count, plan, stream, kConfigure);
     default:
@@ -680,7 +686,7 @@ cudaError_t launch_segsoftmax_planned(const float *values,
                                       const DevicePlan &plan,
                                       cudaStream_t stream,
                                       const Probe *probe) {
-  static_assert(kSoftmaxBuckets == 7 && kSoftmaxLimit[0] == 8 * 8 &&
+  static_assert(kSoftmaxBuckets == 8 && kSoftmaxLimit[0] == 8 * 8 &&
                     kSoftmaxLimit[1] == 32 * 16 && kSoftmaxLimit[2] == 128 * 16,
                 "bucket limits are the capacities of the resident kernels");
   Fork *fork = nullptr;
