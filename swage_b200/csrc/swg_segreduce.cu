@@ -226,6 +226,34 @@ __device__ __forceinline__ void issue_task(const Task &task,
              d_off + o_lo, bytes_o, full);
 }
 
+// Warp-collective: reduces tile[lo, hi) -- scalar ends, 128-bit body, four
+// independent accumulators per lane -- and returns the result to every lane.
+template <class Op>
+__device__ __forceinline__ float warp_range(const float *tile, int lo, int hi,
+                                            int lane) {
+  int blo = (lo + 3) & ~3, bhi = hi & ~3;
+  if (blo > bhi) blo = bhi = hi;  // too short for an aligned body
+  const int head_end = blo < hi ? blo : hi;
+  float a0 = Op::identity(), a1 = Op::identity(), a2 = Op::identity(),
+        a3 = Op::identity();
+  if (lo + lane < head_end) a0 = Op::apply(a0, tile[lo + lane]);
+  const float4 *body = reinterpret_cast<const float4 *>(tile);
+  const int vlo = blo >> 2, vhi = bhi >> 2;
+  int v = vlo + lane;
+  for (; v + 96 < vhi; v += 128) {
+    const float4 q0 = body[v], q1 = body[v + 32], q2 = body[v + 64],
+                 q3 = body[v + 96];
+    a0 = fold4<Op>(a0, q0);
+    a1 = fold4<Op>(a1, q1);
+    a2 = fold4<Op>(a2, q2);
+    a3 = fold4<Op>(a3, q3);
+  }
+  for (; v < vhi; v += 32) a0 = fold4<Op>(a0, body[v]);
+  const int tail = bhi > head_end ? bhi : head_end;
+  if (tail + lane < hi) a1 = Op::apply(a1, tile[tail + lane]);
+  return warp_reduce<Op>(Op::apply(Op::apply(a0, a1), Op::apply(a2, a3)));
+}
+
 // Warp-collective: reduce one staged task.
 template <class Op>
 __device__ __forceinline__ void process_task(const Task &task,
@@ -245,31 +273,8 @@ __device__ __forceinline__ void process_task(const Task &task,
   const float *tile = stage.tile;
 
   if (kind == kTaskChunk) {
-    // One piece of a long segment occupies tile[shift, shift + vcount):
-    // scalar ends, 128-bit body, four independent accumulators per lane.
-    const int lo = shift, hi = shift + vcount;
-    int blo = (lo + 3) & ~3, bhi = hi & ~3;
-    if (blo > bhi) blo = bhi = hi;  // too short for an aligned body
-    const int head_end = blo < hi ? blo : hi;
-    float a0 = Op::identity(), a1 = Op::identity(), a2 = Op::identity(),
-          a3 = Op::identity();
-    if (lo + lane < head_end) a0 = Op::apply(a0, tile[lo + lane]);
-    const float4 *body = reinterpret_cast<const float4 *>(tile);
-    const int vlo = blo >> 2, vhi = bhi >> 2;
-    int v = vlo + lane;
-    for (; v + 96 < vhi; v += 128) {
-      const float4 q0 = body[v], q1 = body[v + 32], q2 = body[v + 64],
-                   q3 = body[v + 96];
-      a0 = fold4<Op>(a0, q0);
-      a1 = fold4<Op>(a1, q1);
-      a2 = fold4<Op>(a2, q2);
-      a3 = fold4<Op>(a3, q3);
-    }
-    for (; v < vhi; v += 32) a0 = fold4<Op>(a0, body[v]);
-    const int tail = bhi > head_end ? bhi : head_end;
-    if (tail + lane < hi) a1 = Op::apply(a1, tile[tail + lane]);
-    const float r =
-        warp_reduce<Op>(Op::apply(Op::apply(a0, a1), Op::apply(a2, a3)));
+    // One piece of a long segment occupies tile[shift, shift + vcount).
+    const float r = warp_range<Op>(tile, shift, shift + vcount, lane);
     if (lane == 0) {
       if (task.count < 0) out[task.seg] = r;
       else partials[task.count] = r;
@@ -356,19 +361,8 @@ __device__ __forceinline__ void process_task(const Task &task,
     }
     __syncwarp();
     for (int e = medium_count; e < listed; ++e) {
-      const int ea = scratch->begin[e], eb = scratch->end[e];
-      float p0 = Op::identity(), p1 = Op::identity(), p2 = Op::identity(),
-            p3 = Op::identity();
-      int i = ea + lane;
-      for (; i + 96 < eb; i += 128) {
-        p0 = Op::apply(p0, tile[i]);
-        p1 = Op::apply(p1, tile[i + 32]);
-        p2 = Op::apply(p2, tile[i + 64]);
-        p3 = Op::apply(p3, tile[i + 96]);
-      }
-      for (; i < eb; i += 32) p0 = Op::apply(p0, tile[i]);
       const float r =
-          warp_reduce<Op>(Op::apply(Op::apply(p0, p1), Op::apply(p2, p3)));
+          warp_range<Op>(tile, scratch->begin[e], scratch->end[e], lane);
       if (lane == 0) scratch->result[e] = r;
     }
     __syncwarp();

@@ -149,6 +149,25 @@ def test_config_softmax_reduced(schedule):
     check_softmax(values.cpu().numpy(), offsets, schedule)
 
 
+def test_softmax_is_reproducible_run_to_run():
+    """The same launch repeated gives the same bits.  (A stage of the ring
+    kernel handed back to the copy engine before every lane had its values
+    showed up as one 128-value row differing in about every second run.)"""
+    offsets = workloads.c4_offsets(segments=4096)
+    values = workloads.normal_values(int(offsets[-1]), "cuda",
+                                     workloads.SEEDS["c4"], scale=2.0)
+    device_offsets = torch.as_tensor(offsets).cuda()
+    first = None
+    for _ in range(6):
+        output = torch.full((values.numel(),), float("nan"), device="cuda")
+        launch_softmax_gpu(values, device_offsets, output)
+        torch.cuda.synchronize()
+        if first is None:
+            first = output
+        else:
+            assert torch.equal(first, output)
+
+
 def test_full_size_softmax_properties():
     """262144 segments, about 1.13e9 values: every segment sums to one, the
     output is a valid probability everywhere, and a sample of segments
