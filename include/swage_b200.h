@@ -118,6 +118,32 @@ int swg_plan_describe(const swg_plan *plan, char *json, size_t capacity);
  * else SWG_OK. */
 int swg_plan_status(swg_plan *plan);
 
+/* The same rules, order and reason codes as swg_validate_offsets_i32, for
+ * offsets[0 .. segment_count] that live on the GPU: one pass on the device, one
+ * small read-back (`stream` is synchronised).  *hash (optional) receives a
+ * 64-bit digest of the offsets' content, *last_offset offsets[segment_count].
+ * No reference counterpart: the reference copies the offsets to the host and
+ * walks them in Python (python/swage/_segmented_qualification.py:30-55,78) and
+ * lists device-only offset validation as future work (DESIGN.md:100-102). */
+int swg_validate_offsets_device(const int32_t *device_offsets,
+                                int32_t segment_count, int32_t value_count,
+                                int64_t output_count, void *stream,
+                                int32_t *reason, int64_t *index,
+                                uint64_t *hash, int32_t *last_offset);
+
+/* swg_plan_create for device-resident offsets: validation (as above), the
+ * length histogram, the tile tasks and merge lists (op = SWG_OP_REDUCE) or the
+ * length-class lists (SWG_OP_SOFTMAX) are all computed on the GPU; the offsets
+ * are never copied to the host.  On SWG_ERR_INVALID_OFFSETS *reason / *index
+ * say which rule broke first and no plan is returned.  The tiles are cut at
+ * fixed item positions (merge-path), not by the host planner's walk, so the
+ * task list differs from swg_plan_create's; results agree to the documented
+ * tolerance (max: bit-exact). */
+int swg_plan_create_device(const int32_t *device_offsets,
+                           int32_t segment_count, int32_t value_count,
+                           int64_t output_count, int op, void *stream,
+                           swg_plan **plan, int32_t *reason, int64_t *index);
+
 /* The planner alone, on the host: no device is touched.  Writes up to
  * `task_capacity` tasks as 8 x int32 each {first segment, segment count or
  * partial slot (-1 = whole segment), first value, value count | kind << 28

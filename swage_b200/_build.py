@@ -20,6 +20,7 @@ SOURCES = (
     "swg_vadd.cu",
     "swg_segreduce.cu",
     "swg_softmax.cu",
+    "swg_device_plan.cu",
     "swg_planner.cpp",
 )
 

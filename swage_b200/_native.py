@@ -40,6 +40,7 @@ EXPORTS = (
     "swg_segreduce_f32",
     "swg_segsoftmax_f32", "swg_shard_offsets", "swg_profile_start",
     "swg_profile_stop", "swg_segreduce_f32_noalloc",
+    "swg_validate_offsets_device", "swg_plan_create_device",
 )
 
 _lock = threading.Lock()
@@ -85,6 +86,15 @@ def _declare(lib):
     lib.swg_segreduce_f32_noalloc.restype = c_int
     lib.swg_segreduce_f32_noalloc.argtypes = [
         c_int, ptr, ptr, ptr, c_i32, c_i32, ptr]
+    lib.swg_validate_offsets_device.restype = c_int
+    lib.swg_validate_offsets_device.argtypes = [
+        ptr, c_i32, c_i32, c_i64, ptr,
+        ctypes.POINTER(c_i32), ctypes.POINTER(c_i64),
+        ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(c_i32)]
+    lib.swg_plan_create_device.restype = c_int
+    lib.swg_plan_create_device.argtypes = [
+        ptr, c_i32, c_i32, c_i64, c_int, ptr, ctypes.POINTER(ptr),
+        ctypes.POINTER(c_i32), ctypes.POINTER(c_i64)]
     lib.swg_profile_start.restype = c_int
     lib.swg_profile_start.argtypes = [c_i32, c_i32]
     lib.swg_profile_stop.restype = c_int
@@ -168,6 +178,45 @@ def validate_offsets(host_ptr, count, value_count, output_count):
         host_ptr, count, value_count, output_count,
         ctypes.byref(reason), ctypes.byref(index))
     return OFFSETS_REASONS[reason.value], index.value
+
+
+_INVALID_OFFSETS = 2  # SWG_ERR_INVALID_OFFSETS
+
+
+def validate_offsets_device(device_ptr, segment_count, value_count,
+                            output_count, stream):
+    """Validate offsets that live on the GPU.
+
+    Returns ``(reason_name, index, content_hash, last_offset)``; synchronises
+    ``stream`` to read the verdict.
+    """
+    reason = ctypes.c_int32(0)
+    index = ctypes.c_int64(-1)
+    digest = ctypes.c_uint64(0)
+    last = ctypes.c_int32(0)
+    status = library().swg_validate_offsets_device(
+        device_ptr, segment_count, value_count, output_count, stream,
+        ctypes.byref(reason), ctypes.byref(index), ctypes.byref(digest),
+        ctypes.byref(last))
+    if status not in (0, _INVALID_OFFSETS):
+        check(status, "swg_validate_offsets_device")
+    return OFFSETS_REASONS[reason.value], index.value, digest.value, last.value
+
+
+def plan_create_device(device_ptr, segment_count, value_count, output_count,
+                       op, stream):
+    """Validate and plan on the GPU; ``(handle, "ok", -1)`` or
+    ``(None, reason_name, index)`` for offsets that break a rule."""
+    handle = ctypes.c_void_p()
+    reason = ctypes.c_int32(0)
+    index = ctypes.c_int64(-1)
+    status = library().swg_plan_create_device(
+        device_ptr, segment_count, value_count, output_count, op, stream,
+        ctypes.byref(handle), ctypes.byref(reason), ctypes.byref(index))
+    if status == _INVALID_OFFSETS:
+        return None, OFFSETS_REASONS[reason.value], index.value
+    check(status, "swg_plan_create_device")
+    return handle, "ok", -1
 
 
 def plan_create(host_ptr, segment_count, value_count, op):

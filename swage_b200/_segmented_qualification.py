@@ -10,14 +10,17 @@ computes a result on the host.
 
 Differences that do not change results:
 
-* offsets are validated by one native pass over the host copy instead of a
-  Python loop over a list (the reference's ``:43-50``);
+* offsets are validated by one native pass instead of a Python loop over a
+  list (the reference's ``:43-50``): on the GPU, without a host copy, when
+  the launch is large enough to be planned (the same rules in the same order,
+  so the same exception for the same input), else over a host copy;
 * no per-call compilation or module load (the reference's ``:144-155``);
 * ``block_size`` is still validated the same way but is only a hint: the
   physical schedule (warp / CTA / split / persistent tile tasks) is chosen by
   a plan built from the segment-length histogram;
-* plans are cached per offsets content (exact comparison of the host copy),
-  so repeated launches over the same CSR structure skip the planner.
+* plans are cached per offsets content (a 64-bit digest computed by the
+  validation pass on the device, or exact comparison of the host copy), so
+  repeated launches over the same CSR structure skip the planner.
 """
 
 import collections
@@ -91,6 +94,13 @@ def _validate_host_offsets(host_offsets, value_count, output_count):
     )
     if reason == "ok":
         return segment_count
+    _raise_offsets_error(reason, segment_count, value_count, output_count,
+                         lambda: int(host_offsets[-1]))
+
+
+def _raise_offsets_error(reason, segment_count, value_count, output_count,
+                         final_offset):
+    """The reference's exception for the first rule the offsets break."""
     if reason == "output_small":
         raise ValueError(
             f"output has {output_count} elements for {segment_count} segments"
@@ -103,7 +113,7 @@ def _validate_host_offsets(host_offsets, value_count, output_count):
         raise ValueError("offsets must be nondecreasing")
     if reason == "exceeds_values":
         raise ValueError(
-            f"final offset {int(host_offsets[-1])} exceeds value count "
+            f"final offset {final_offset()} exceeds value count "
             f"{value_count}"
         )
     if reason == "empty":
@@ -136,10 +146,35 @@ def _validate_tensors(values, offsets, output, *, require_cuda=True,
             raise ValueError(f"{name} must be contiguous")
 
     value_count = values.numel()
+    output_count = output.numel()
+    _last_host_offsets.value = None
+    _last_digest.value = None
+    if _host_offsets is None and _on_current_device(offsets, torch) and (
+        value_count + offsets.numel() - 1 >= _PLAN_THRESHOLD
+    ):
+        # large launch: the offsets stay on the device
+        segment_count = _validate_device_offsets(
+            offsets, value_count,
+            max(offsets.numel() - 1, 0) if elementwise_output
+            else output_count,
+            torch,
+        )
+        if elementwise_output and output_count < value_count:
+            raise ValueError(
+                f"output has {output_count} elements for {value_count} values"
+            )
+        if require_cuda:
+            device = torch.cuda.current_device()
+            for name, tensor in named:
+                if tensor.device.type != "cuda":
+                    raise TypeError(f"{name} must be a CUDA tensor")
+                if tensor.device.index != device:
+                    raise ValueError(
+                        f"{name} must be on the current CUDA device")
+        return value_count, segment_count
     host = _host_offsets
     if host is None:
         host = offsets.detach().cpu()
-    output_count = output.numel()
     if elementwise_output:
         segment_count = _validate_host_offsets(
             host, value_count, max(host.numel() - 1, 0)
@@ -166,24 +201,63 @@ def _validate_tensors(values, offsets, output, *, require_cuda=True,
 # the host copy made by the most recent validation on this thread, so that
 # launch_gpu can hand it to the planner without a second device-to-host copy
 _last_host_offsets = threading.local()
+# or, when that validation ran on the device, the digest of the offsets'
+# content it computed: (data pointer, segment count, hash)
+_last_digest = threading.local()
+
+
+def _on_current_device(tensor, torch):
+    return (
+        tensor.device.type == "cuda"
+        and torch.cuda.is_available()
+        and tensor.device.index == torch.cuda.current_device()
+    )
+
+
+def _validate_device_offsets(offsets, value_count, output_count, torch):
+    """``_validate_offsets`` for a CUDA int32 tensor, without a host copy."""
+    from . import _native
+
+    count = offsets.numel()
+    if count == 0:
+        raise ValueError("offsets must contain at least the initial zero")
+    segment_count = count - 1
+    _validate_counts(value_count, segment_count)
+    stream = torch.cuda.current_stream()
+    reason, _, digest, last = _native.validate_offsets_device(
+        offsets.data_ptr(), segment_count, value_count, output_count,
+        stream.cuda_stream,
+    )
+    if reason != "ok":
+        _raise_offsets_error(reason, segment_count, value_count, output_count,
+                             lambda: last)
+    _last_digest.value = (offsets.data_ptr(), segment_count, digest)
+    return segment_count
 
 
 class SegmentPlan:
-    """A host-built schedule for one CSR offsets array on one device.
+    """A schedule for one CSR offsets array on one device.
 
     Built by the native planner from the segment-length histogram: segments
     are bucketed by length, short ones are packed into tile tasks, long ones
     are cut into chunks whose partials a second pass merges, and a schedule is
-    chosen.  The plan owns device copies of its task list, of the offsets and
-    of the partial scratch.  It stays valid for as long as the offsets hold
-    the same numbers; launches that share a plan must not overlap on the GPU
-    (they share the partial scratch and the ticket counter).
+    chosen.  From a CPU offsets tensor the planner runs on the host; from a
+    CUDA tensor it runs on the GPU and the offsets never leave the device.
+    The plan owns device copies of its task list, of the offsets and of the
+    partial scratch.  It stays valid for as long as the offsets hold the same
+    numbers; launches that share a plan must not overlap on the GPU (they
+    share the partial scratch and the ticket counter).
     """
 
     def __init__(self, host_offsets, value_count, op="reduce"):
         from . import _native
 
         torch = _runtime._import_torch()
+        if isinstance(host_offsets, torch.Tensor) and (
+            host_offsets.device.type == "cuda"
+        ):
+            self._from_device(host_offsets, value_count, op, _native, torch)
+            return
         if (
             not isinstance(host_offsets, torch.Tensor)
             or host_offsets.device.type != "cpu"
@@ -204,6 +278,38 @@ class SegmentPlan:
         self._handle = _native.plan_create(
             host_offsets.data_ptr(), self.segment_count, self.value_count, code
         )
+
+    def _from_device(self, offsets, value_count, op, _native, torch):
+        if (
+            offsets.dtype != torch.int32
+            or offsets.dim() != 1
+            or not offsets.is_contiguous()
+            or offsets.numel() < 1
+            or not _on_current_device(offsets, torch)
+        ):
+            raise TypeError(
+                "plan needs a contiguous rank-one int32 offsets tensor on the "
+                "current CUDA device"
+            )
+        self._native = _native
+        self.segment_count = offsets.numel() - 1
+        self.value_count = int(value_count)
+        self.op = op
+        self.device = torch.cuda.current_device()
+        code = _native.OP_SOFTMAX if op == "softmax" else _native.OP_REDUCE
+        self._handle = None
+        _validate_counts(self.value_count, self.segment_count)
+        stream = torch.cuda.current_stream()
+        handle, reason, _ = _native.plan_create_device(
+            offsets.data_ptr(), self.segment_count, self.value_count,
+            self.segment_count, code, stream.cuda_stream,
+        )
+        if handle is None:
+            _raise_offsets_error(
+                reason, self.segment_count, self.value_count,
+                self.segment_count, lambda: int(offsets[-1]),
+            )
+        self._handle = handle
 
     @property
     def handle(self):
@@ -232,7 +338,12 @@ class SegmentPlan:
 
 
 def plan_segments(offsets, value_count=None, op="reduce"):
-    """Validate ``offsets`` (CPU or CUDA int32) and build a ``SegmentPlan``."""
+    """Validate ``offsets`` (CPU or CUDA int32) and build a ``SegmentPlan``.
+
+    A CUDA tensor on the current device is validated and planned on the GPU
+    (``value_count`` must then be given: reading it off the tensor would
+    copy); a CPU tensor by the host planner.
+    """
     torch = _runtime._import_torch()
     if not isinstance(offsets, torch.Tensor):
         raise TypeError("offsets must be a torch.Tensor")
@@ -240,6 +351,8 @@ def plan_segments(offsets, value_count=None, op="reduce"):
         raise TypeError("offsets must have dtype torch.int32")
     if offsets.dim() != 1:
         raise TypeError("offsets must have rank one")
+    if value_count is not None and _on_current_device(offsets, torch):
+        return SegmentPlan(offsets.detach().contiguous(), value_count, op)
     host = offsets.detach().cpu().contiguous()
     if value_count is None:
         value_count = int(host[-1]) if host.numel() else 0
@@ -274,6 +387,40 @@ def _cached_plan(host_offsets, value_count, op, device):
         return plan
 
 
+_device_plan_cache = collections.OrderedDict()
+
+
+def _cached_device_plan(offsets, value_count, op, device, digest):
+    """Plan built on the GPU for offsets with this content digest."""
+    key = (device, op, offsets.numel(), value_count, digest)
+    with _plan_cache_lock:
+        plan = _device_plan_cache.get(key)
+        if plan is not None:
+            _device_plan_cache.move_to_end(key)
+            return plan
+        plan = SegmentPlan(offsets, value_count, op)
+        _device_plan_cache[key] = plan
+        while len(_device_plan_cache) > _PLAN_CACHE_ENTRIES:
+            _, oldest = _device_plan_cache.popitem(last=False)
+            oldest.close()
+        return plan
+
+
+def _plan_for_launch(offsets, value_count, segment_count, op, torch):
+    """The cached plan for a launch that was just validated on this thread."""
+    device = torch.cuda.current_device()
+    digest = getattr(_last_digest, "value", None)
+    _last_digest.value = None
+    if digest is not None and digest[:2] == (offsets.data_ptr(),
+                                             segment_count):
+        return _cached_device_plan(offsets, value_count, op, device,
+                                   digest[2])
+    host = getattr(_last_host_offsets, "value", None)
+    if host is None or host.numel() != segment_count + 1:
+        host = offsets.detach().cpu()
+    return _cached_plan(host, value_count, op, device)
+
+
 def clear_plan_cache():
     """Drop every cached plan (frees their device memory)."""
     with _plan_cache_lock:
@@ -281,6 +428,9 @@ def clear_plan_cache():
             for _, plan in entries:
                 plan.close()
         _plan_cache.clear()
+        for plan in _device_plan_cache.values():
+            plan.close()
+        _device_plan_cache.clear()
 
 
 def _schedule_code(schedule):
@@ -341,13 +491,10 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
         or (code == _native.SCHED_AUTO
             and value_count + segment_count >= _PLAN_THRESHOLD)
     ):
-        host = getattr(_last_host_offsets, "value", None)
-        if host is None or host.numel() != segment_count + 1:
-            host = offsets.detach().cpu()
-        plan = _cached_plan(
-            host, value_count, "reduce", torch.cuda.current_device()
-        )
+        plan = _plan_for_launch(offsets, value_count, segment_count, "reduce",
+                                torch)
     _last_host_offsets.value = None
+    _last_digest.value = None
     stream = torch.cuda.current_stream()
     _native.segreduce(
         _KINDS[kind], values.data_ptr(), offsets.data_ptr(), output.data_ptr(),
@@ -390,13 +537,10 @@ def launch_softmax_gpu(values, offsets, output, *, plan=None, schedule="auto",
         or (code == _native.SCHED_AUTO
             and value_count + segment_count >= _PLAN_THRESHOLD)
     ):
-        host = getattr(_last_host_offsets, "value", None)
-        if host is None or host.numel() != segment_count + 1:
-            host = offsets.detach().cpu()
-        plan = _cached_plan(
-            host, value_count, "softmax", torch.cuda.current_device()
-        )
+        plan = _plan_for_launch(offsets, value_count, segment_count,
+                                "softmax", torch)
     _last_host_offsets.value = None
+    _last_digest.value = None
     stream = torch.cuda.current_stream()
     _native.segsoftmax(
         values.data_ptr(), offsets.data_ptr(), output.data_ptr(), value_count,

@@ -238,6 +238,97 @@ int swg_plan_create(const int32_t *host_offsets, int32_t segment_count,
   return SWG_OK;
 }
 
+// The checks of validate_offsets that need no offset value, in its order.
+static int precheck_counts(const void *offsets, int64_t segment_count,
+                           int64_t value_count, int64_t output_count,
+                           int32_t *reason, int64_t *index) {
+  const int64_t limit = int64_t(1) << 31;
+  int32_t why = SWG_OFFSETS_OK;
+  if (!offsets || segment_count < 0) why = SWG_OFFSETS_EMPTY;
+  else if (value_count < 0 || value_count >= limit || segment_count >= limit)
+    why = SWG_OFFSETS_COUNT_RANGE;
+  else if (output_count < segment_count) why = SWG_OFFSETS_OUTPUT_SMALL;
+  if (reason) *reason = why;
+  if (index) *index = -1;
+  if (why == SWG_OFFSETS_OK) return SWG_OK;
+  swg::set_error("offsets rejected: reason %d at index -1", (int)why);
+  return SWG_ERR_INVALID_OFFSETS;
+}
+
+int swg_validate_offsets_device(const int32_t *device_offsets,
+                                int32_t segment_count, int32_t value_count,
+                                int64_t output_count, void *stream,
+                                int32_t *reason, int64_t *index,
+                                uint64_t *hash, int32_t *last_offset) {
+  swg::clear_error();
+  int status = precheck_counts(device_offsets, segment_count, value_count,
+                               output_count, reason, index);
+  if (status != SWG_OK) return status;
+  int device = 0, sm_count = 0;
+  status = current_device(&device, &sm_count);
+  if (status != SWG_OK) return status;
+  int32_t why = SWG_OFFSETS_OK;
+  int64_t where = -1;
+  swg::DeviceDigest digest{0, 0, 0};
+  cudaError_t e = swg::device_validate(device_offsets, segment_count,
+                                       value_count, device, sm_count,
+                                       (cudaStream_t)stream, &why, &where,
+                                       &digest);
+  if (e != cudaSuccess) return cuda_failure("device offsets validation", e);
+  if (reason) *reason = why;
+  if (index) *index = where;
+  if (hash) *hash = digest.hash;
+  if (last_offset) *last_offset = digest.last_offset;
+  if (why == SWG_OFFSETS_OK) return SWG_OK;
+  swg::set_error("offsets rejected: reason %d at index %lld", (int)why,
+                 (long long)where);
+  return SWG_ERR_INVALID_OFFSETS;
+}
+
+int swg_plan_create_device(const int32_t *device_offsets,
+                           int32_t segment_count, int32_t value_count,
+                           int64_t output_count, int op, void *stream,
+                           swg_plan **plan_out, int32_t *reason,
+                           int64_t *index) {
+  swg::clear_error();
+  if (!plan_out || (op != SWG_OP_REDUCE && op != SWG_OP_SOFTMAX)) {
+    swg::set_error("swg_plan_create_device: bad arguments");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  *plan_out = nullptr;
+  int status = precheck_counts(device_offsets, segment_count, value_count,
+                               output_count, reason, index);
+  if (status != SWG_OK) return status;
+  int device = 0, sm_count = 0;
+  status = current_device(&device, &sm_count);
+  if (status != SWG_OK) return status;
+  swg_plan *plan = new (std::nothrow) swg_plan();
+  if (!plan) {
+    swg::set_error("swg_plan_create_device: out of host memory");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  plan->dev.device = device;
+  plan->dev.sm_count = sm_count;
+  int32_t why = SWG_OFFSETS_OK;
+  int64_t where = -1;
+  cudaError_t e = swg::device_plan(device_offsets, segment_count, value_count,
+                                   op, (cudaStream_t)stream, &plan->dev,
+                                   &plan->host, &why, &where);
+  if (reason) *reason = why;
+  if (index) *index = where;
+  if (e != cudaSuccess || why != SWG_OFFSETS_OK) {
+    release(plan->dev);
+    delete plan;
+    if (e != cudaSuccess) return cuda_failure("device planner", e);
+    swg::set_error("offsets rejected: reason %d at index %lld", (int)why,
+                   (long long)where);
+    return SWG_ERR_INVALID_OFFSETS;
+  }
+  plan->description = swg::describe_host_plan(plan->host);
+  *plan_out = plan;
+  return SWG_OK;
+}
+
 int swg_plan_host_tasks(const int32_t *host_offsets, int32_t segment_count,
                         int op, int32_t *tasks, int64_t task_capacity,
                         int64_t *task_count, char *json, size_t json_capacity) {

@@ -66,6 +66,25 @@ cudaError_t launch_segreduce_persistent(int kind, const float *values,
 cudaError_t configure_segreduce_kernels();
 cudaError_t configure_softmax_kernels();
 
+// Validation and planning on the device (swg_device_plan.cu).
+struct DeviceDigest {
+  unsigned long long hash;  // of the offsets' content
+  int32_t last_offset;
+  int32_t max_length;
+};
+// Checks device-resident offsets[0 .. segment_count] against the rules of
+// validate_offsets; synchronises `stream` to read the verdict.
+cudaError_t device_validate(const int32_t *offsets, int32_t segment_count,
+                            int32_t value_count, int device, int sm_count,
+                            cudaStream_t stream, int32_t *reason,
+                            int64_t *index, DeviceDigest *digest);
+// Validates, then fills `dev` (device, sm_count preset by the caller) and the
+// summary fields of `host`.  *reason != SWG_OFFSETS_OK: nothing was planned.
+cudaError_t device_plan(const int32_t *offsets, int32_t segment_count,
+                        int32_t value_count, int op, cudaStream_t stream,
+                        DevicePlan *dev, HostPlan *host, int32_t *reason,
+                        int64_t *index);
+
 // Allocation-free variant: the split schedule run out of a fixed-size
 // file-scope device array.  Limits of that array:
 constexpr int kStaticMaxSegments = 1 << 18;

@@ -15,7 +15,7 @@ namespace swg {
 constexpr int kTileValues = 2048;      // values per tile task (8 KiB of fp32)
 constexpr int kTileItems = 2032;       // values + segments of a packed task:
                                        // its offsets share the tile's stage
-constexpr int kTileMaxSegments = 1024; // segments per packed tile task
+constexpr int kTileMaxSegments = kTileItems;  // segments per packed tile task
 constexpr int kSplitMinimum = 128;     // segments up to here are never cut
 constexpr int kSplitMinimumPiece = 32; // smallest piece left in an open tile
 constexpr int kBigSplit = 256;         // partials from which a merge gets a whole CTA
@@ -85,6 +85,8 @@ struct HostPlan {
   int32_t big_split_count = 0;
   int32_t medium_split_count = 0;
   int64_t pack_tasks = 0, chunk_tasks = 0;
+  // plans built on the device keep no host copy of their lists
+  int64_t task_total = -1, split_total = -1;
 };
 
 // Builds the histogram, the task list and the schedule choice.

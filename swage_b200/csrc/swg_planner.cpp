@@ -319,9 +319,11 @@ std::string describe_host_plan(const HostPlan &plan) {
            "\"tile_max_segments\": %d, "
            "\"split_minimum\": %d, \"softmax_buckets\": [%d, %d, %d, %d, %d, %d, %d, %d], ",
            plan.segment_count, plan.value_count, plan.op, plan.schedule,
-           plan.mean_length, (long long)plan.max_length, plan.tasks.size(),
+           plan.mean_length, (long long)plan.max_length,
+           plan.task_total >= 0 ? (size_t)plan.task_total : plan.tasks.size(),
            (long long)plan.pack_tasks, (long long)plan.chunk_tasks,
-           plan.splits.size(), plan.partial_slots, kTileValues, kTileItems,
+           plan.split_total >= 0 ? (size_t)plan.split_total : plan.splits.size(),
+           plan.partial_slots, kTileValues, kTileItems,
            kTileMaxSegments,
            kSplitMinimum, plan.softmax_count[0], plan.softmax_count[1],
            plan.softmax_count[2], plan.softmax_count[3], plan.softmax_count[4],
