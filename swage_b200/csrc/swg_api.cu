@@ -107,8 +107,10 @@ int upload(T **dst, const T *src, size_t count, size_t padded_count,
 void release(swg::DevicePlan &dev) {
   cudaFree(dev.tasks);
   cudaFree(dev.offsets);
-  cudaFree(dev.splits);
-  cudaFree(dev.partials);
+  if (!dev.shared_block) {
+    cudaFree(dev.splits);
+    cudaFree(dev.partials);
+  }
   cudaFree(dev.softmax_segments);
   cudaFree(dev.control);
   dev = swg::DevicePlan();

@@ -230,6 +230,8 @@ boundary_at(const uint32_t *__restrict__ start,
 }
 
 // One CTA: inclusive counts, per boundary, of first cuts (all / big / medium).
+// The CTA walks the boundaries kScanThreads at a time (coalesced), scans the
+// three flags of a batch with warp shuffles and carries the running totals.
 constexpr int kScanThreads = 1024;
 
 __global__ void __launch_bounds__(kScanThreads)
@@ -237,56 +239,63 @@ boundary_scan_kernel(const uint32_t *__restrict__ start,
                      const int32_t *__restrict__ offsets, int32_t tile_count,
                      int32_t *__restrict__ cuts, int32_t *__restrict__ bigs,
                      int32_t *__restrict__ mediums, Summary *summary) {
-  __shared__ int totals[3][kScanThreads];
-  const int tid = threadIdx.x;
-  const int64_t per = ((int64_t)tile_count + kScanThreads - 1) / kScanThreads;
-  const int64_t begin = tid * per;
-  const int64_t end =
-      begin + per < tile_count ? begin + per : (int64_t)tile_count;
-  int all = 0, big = 0, medium = 0;
-  for (int64_t t = begin; t < end; ++t) {
-    const Boundary b = boundary_at(start, offsets, t);
-    if (!b.first_cut) continue;
-    ++all;
-    big += b.pieces >= kBigSplit;
-    medium += b.pieces < kBigSplit && b.pieces > kTinySplit;
-  }
-  totals[0][tid] = all;
-  totals[1][tid] = big;
-  totals[2][tid] = medium;
+  __shared__ int warp_totals[3][kScanThreads / 32];
+  __shared__ int carry[3];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < 3) carry[tid] = 0;
   __syncthreads();
-  // Hillis-Steele inclusive scan of the three rows
-  for (int delta = 1; delta < kScanThreads; delta <<= 1) {
-    int a = 0, b = 0, c = 0;
-    if (tid >= delta) {
-      a = totals[0][tid - delta];
-      b = totals[1][tid - delta];
-      c = totals[2][tid - delta];
+  for (int64_t base = 0; base < tile_count; base += kScanThreads) {
+    const int64_t t = base + tid;
+    int v[3] = {0, 0, 0};
+    if (t < tile_count) {
+      const Boundary b = boundary_at(start, offsets, t);
+      if (b.first_cut) {
+        v[0] = 1;
+        v[1] = b.pieces >= kBigSplit;
+        v[2] = b.pieces < kBigSplit && b.pieces > kTinySplit;
+      }
+    }
+    // inclusive scan inside the warp
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+#pragma unroll
+      for (int delta = 1; delta < 32; delta <<= 1) {
+        const int up = __shfl_up_sync(kFullMask, v[k], delta);
+        if (lane >= delta) v[k] += up;
+      }
+      if (lane == 31) warp_totals[k][warp] = v[k];
     }
     __syncthreads();
-    totals[0][tid] += a;
-    totals[1][tid] += b;
-    totals[2][tid] += c;
+    if (warp == 0) {
+#pragma unroll
+      for (int k = 0; k < 3; ++k) {
+        int w = warp_totals[k][lane];
+#pragma unroll
+        for (int delta = 1; delta < 32; delta <<= 1) {
+          const int up = __shfl_up_sync(kFullMask, w, delta);
+          if (lane >= delta) w += up;
+        }
+        warp_totals[k][lane] = w;  // inclusive over the warps
+      }
+    }
+    __syncthreads();
+    int before[3];
+#pragma unroll
+    for (int k = 0; k < 3; ++k)
+      before[k] = carry[k] + (warp > 0 ? warp_totals[k][warp - 1] : 0);
+    if (t < tile_count) {
+      cuts[t] = before[0] + v[0];
+      bigs[t] = before[1] + v[1];
+      mediums[t] = before[2] + v[2];
+    }
+    __syncthreads();
+    if (tid < 3) carry[tid] += warp_totals[tid][kScanThreads / 32 - 1];
     __syncthreads();
   }
-  all = totals[0][tid] - all;  // exclusive bases of this thread's range
-  big = totals[1][tid] - big;
-  medium = totals[2][tid] - medium;
-  for (int64_t t = begin; t < end; ++t) {
-    const Boundary b = boundary_at(start, offsets, t);
-    if (b.first_cut) {
-      ++all;
-      big += b.pieces >= kBigSplit;
-      medium += b.pieces < kBigSplit && b.pieces > kTinySplit;
-    }
-    cuts[t] = all;
-    bigs[t] = big;
-    mediums[t] = medium;
-  }
-  if (tid == kScanThreads - 1) {
-    summary->split_count = totals[0][tid];
-    summary->big_count = totals[1][tid];
-    summary->medium_count = totals[2][tid];
+  if (tid == 0) {
+    summary->split_count = carry[0];
+    summary->big_count = carry[1];
+    summary->medium_count = carry[2];
   }
 }
 
@@ -618,18 +627,22 @@ cudaError_t device_plan(const int32_t *offsets, int32_t segment_count,
   const int64_t tiles = (items + kDeviceTile - 1) / kDeviceTile;
   dev->task_count = (int32_t)tiles;
   if (tiles == 0) return cudaStreamSynchronize(stream);
-  uint32_t *start = nullptr;
-  int32_t *scans = nullptr;  // cuts, bigs, mediums
-  e = cudaMalloc((void **)&dev->tasks, (size_t)tiles * sizeof(Task));
-  if (e == cudaSuccess)
-    e = cudaMalloc((void **)&dev->splits, (size_t)tiles * sizeof(SplitSegment));
-  if (e == cudaSuccess)
-    e = cudaMalloc((void **)&dev->partials, (size_t)tiles * 2 * sizeof(float));
-  if (e == cudaSuccess)
-    e = cudaMalloc((void **)&start, (size_t)tiles * sizeof(uint32_t));
-  if (e == cudaSuccess)
-    e = cudaMalloc((void **)&scans, (size_t)tiles * 3 * sizeof(int32_t));
+  // one allocation for what the plan keeps (tasks, merge list, partials), one
+  // for what only the planner needs (tile starts and the three scans)
+  const size_t task_bytes = (size_t)tiles * sizeof(Task);
+  const size_t split_bytes = (size_t)tiles * sizeof(SplitSegment);
+  const size_t partial_bytes = (size_t)tiles * 2 * sizeof(float);
+  unsigned char *kept = nullptr, *scratch_block = nullptr;
+  e = cudaMalloc((void **)&kept, task_bytes + split_bytes + partial_bytes);
+  if (e != cudaSuccess) return e;
+  dev->tasks = reinterpret_cast<Task *>(kept);  // owns the block
+  dev->splits = reinterpret_cast<SplitSegment *>(kept + task_bytes);
+  dev->partials = reinterpret_cast<float *>(kept + task_bytes + split_bytes);
+  dev->shared_block = true;
+  e = cudaMalloc((void **)&scratch_block, (size_t)tiles * 4 * sizeof(int32_t));
   if (e == cudaSuccess) {
+    uint32_t *start = reinterpret_cast<uint32_t *>(scratch_block);
+    int32_t *scans = reinterpret_cast<int32_t *>(scratch_block) + tiles;
     const unsigned grid = (unsigned)((tiles + 255) / 256);
     tile_start_kernel<<<grid, 256, 0, stream>>>(offsets, segment_count,
                                                 (int32_t)tiles, start);
@@ -645,8 +658,7 @@ cudaError_t device_plan(const int32_t *offsets, int32_t segment_count,
     e = cudaMemcpyAsync(scratch->host, scratch->device, sizeof(Summary),
                         cudaMemcpyDeviceToHost, stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
-  cudaFree(start);
-  cudaFree(scans);
+  cudaFree(scratch_block);
   if (e != cudaSuccess) return e;
   dev->split_count = s.split_count;
   dev->big_split_count = s.big_count;

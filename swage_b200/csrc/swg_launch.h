@@ -26,6 +26,7 @@ struct DevicePlan {
   int32_t softmax_begin[kSoftmaxBuckets] = {0};
   int32_t softmax_count[kSoftmaxBuckets] = {0};
   uint32_t *control = nullptr;     // [0] ticket, [1] finished, [2] error, [3] detail
+  bool shared_block = false;       // tasks, splits and partials are one allocation
 };
 
 // Optional pair of events recorded around the dominant kernel of a call.
