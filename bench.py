@@ -16,7 +16,11 @@ resident in HBM; ``e2e`` is the same metric through the public
 ``launch_gpu`` / ``kernel.launch`` call with the inputs copied from pinned host
 memory and the result read back inside the timed region; ``roofline`` is the
 dominant kernel against the measured HBM copy bandwidth; ``cpu_baseline`` is
-the CPU oracle timed on this host.
+the CPU oracle timed on this host; ``plan`` gives the one-off cost of building
+the schedule (on the GPU from device-resident offsets, and by the host
+planner from a host copy) and of validating the offsets on the GPU, none of
+which is inside ``value``'s timed region (``e2e`` pays validation every step
+and finds the plan by the offsets' content digest).
 
 ``--impl reference`` times the reference's CPU path -- the sequential lowering
 restated in ``oracle/`` (the reference's own executable path needs an LLVM
@@ -63,6 +67,10 @@ def parse_arguments():
     parser.add_argument("--schedule", default="auto")
     parser.add_argument("--block", type=int, default=128)
     parser.add_argument("--allgather", action="store_true")
+    parser.add_argument("--planner", default="device",
+                        choices=["device", "host"],
+                        help="where the plan of the timed region is built "
+                             "(both are built once and timed)")
     parser.add_argument("--e2e-steps", type=int, default=None)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-probe", action="store_true",
@@ -323,6 +331,7 @@ def run_ours(args):
     operation, kind, offsets, text = describe_workload(args.workload,
                                                        args.shrink)
     peak, peak_source = measured_peak()
+    plan_info = {}
 
     @sw.jit
     def add_kernel(x_ptr, y_ptr, output_ptr, n, BLOCK: sl.constexpr):
@@ -366,12 +375,36 @@ def run_ours(args):
         if operation == "reduce":
             out = torch.empty(segments, device=device)
             bytes_per_step = workloads.reduce_bytes(count, segments)
-            plan = plan_segments(torch.from_numpy(local_offsets), count)
+            plan_op = "reduce"
         else:
             out = torch.empty(count, device=device)
             bytes_per_step = workloads.softmax_bytes(count, segments)
-            plan = plan_segments(torch.from_numpy(local_offsets), count,
-                                 op="softmax")
+            plan_op = "softmax"
+        # both planners once, outside the timed region: the host walk over a
+        # host copy of the offsets, and the GPU planner over the device copy
+        # (each twice; the second build is reported: the first one also pays
+        # for loading the planner's kernels)
+        plans = {}
+        for where, source in (("host", torch.from_numpy(local_offsets)),
+                              ("device", device_offsets)):
+            for attempt in range(2):
+                if attempt:
+                    plans[where].close()
+                torch.cuda.synchronize()
+                began = time.perf_counter()
+                plans[where] = plan_segments(source, count, op=plan_op)
+                torch.cuda.synchronize()
+                plan_info[where + "_build_ms"] = (
+                    1e3 * (time.perf_counter() - began))
+        plan = plans.pop(args.planner)
+        for other in plans.values():
+            other.close()
+        plan_info["planner"] = args.planner
+        began = time.perf_counter()
+        _native.validate_offsets_device(
+            device_offsets.data_ptr(), segments, count, segments,
+            torch.cuda.current_stream().cuda_stream)
+        plan_info["validate_on_device_us"] = 1e6 * (time.perf_counter() - began)
     gather = args.allgather and world > 1 and operation == "reduce"
 
     launches_per_step = [0]
@@ -574,6 +607,7 @@ def run_ours(args):
                 if achieved else None,
             },
             "cpu_baseline": cpu,
+            "plan": plan_info or None,
         }
         print(json.dumps(line))
     if plan is not None:
