@@ -24,7 +24,7 @@ def install_as(name="swage"):
     package = sys.modules[__name__]
     sys.modules[name] = package
     for submodule in ("language", "_frontend", "_runtime",
-                      "_segmented_qualification"):
+                      "_segmented_qualification", "env"):
         module = importlib.import_module(f"{__name__}.{submodule}")
         sys.modules[f"{name}.{submodule}"] = module
     return package

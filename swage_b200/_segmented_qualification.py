@@ -25,6 +25,8 @@ Differences that do not change results:
 
 import collections
 import json
+import os
+import sys
 import threading
 
 from . import _runtime
@@ -278,6 +280,7 @@ class SegmentPlan:
         self._handle = _native.plan_create(
             host_offsets.data_ptr(), self.segment_count, self.value_count, code
         )
+        self._dump()
 
     def _from_device(self, offsets, value_count, op, _native, torch):
         if (
@@ -310,6 +313,14 @@ class SegmentPlan:
                 self.segment_count, lambda: int(offsets[-1]),
             )
         self._handle = handle
+        self._dump()
+
+    def _dump(self):
+        """With SWAGE_DUMP_PLAN set, every new plan is described on stderr."""
+        if os.environ.get("SWAGE_DUMP_PLAN"):
+            sys.stderr.write(
+                "swage plan: " + self._native.plan_describe(self._handle) + "\n"
+            )
 
     @property
     def handle(self):

@@ -302,3 +302,18 @@ def test_device_planned_softmax():
         softmax_check(values, small, plan)
     finally:
         plan.close()
+
+
+def test_dump_plan_variable(monkeypatch, capfd):
+    """SWAGE_DUMP_PLAN: every new plan is described on stderr."""
+    monkeypatch.setenv("SWAGE_DUMP_PLAN", "1")
+    offsets = offsets_from_lengths([5, 0, 4000, 17])
+    for plan in (device_plan(offsets),
+                 plan_segments(torch.as_tensor(offsets))):
+        plan.close()
+    lines = [line for line in capfd.readouterr().err.splitlines()
+             if line.startswith("swage plan: ")]
+    assert len(lines) == 2
+    for line in lines:
+        described = json.loads(line[len("swage plan: "):])
+        assert described["segments"] == 4 and described["values"] == 4022
