@@ -47,6 +47,9 @@ typedef enum swg_status {
  * (lib/Conversion/SegmentedReduction/SegmentedReduction.cpp:106-108 rejects the rest). */
 #define SWG_KIND_SUM 0 /* identity +0.0f, fp32 add */
 #define SWG_KIND_MAX 1 /* identity -inf, NaN-propagating maximum, -0 < +0 */
+#define SWG_KIND_MIN 2 /* identity +inf, NaN-propagating minimum, -0 < +0: the
+                          dialect's kind<min> (ADR-0008), which the reference's
+                          lowering rejects (SegmentedReduction.cpp:106-108) */
 
 /* Operation a plan is built for. */
 #define SWG_OP_REDUCE 0

@@ -33,7 +33,8 @@ _lib = None
 
 SUM = 0
 MAX = 1
-_KINDS = {"sum": SUM, "max": MAX}
+MIN = 2  # the dialect's kind<min>; the reference has no lowering for it
+_KINDS = {"sum": SUM, "max": MAX, "min": MIN}
 
 
 def build(force=False):
@@ -227,6 +228,10 @@ def py_segreduce(values, offsets, kind):
             acc = -math.inf
             for i in range(offsets[sid], offsets[sid + 1]):
                 acc = _py_maximumf(acc, values[i])
+        elif kind == "min":
+            acc = math.inf
+            for i in range(offsets[sid], offsets[sid + 1]):
+                acc = -_py_maximumf(-acc, -values[i])
         else:
             raise ValueError("reduction kind must be 'sum' or 'max'")
         out.append(acc)
@@ -237,7 +242,7 @@ def cpu_oracle(values, offsets, kind):
     """Reference-shaped entry: torch CPU tensors in, torch CPU tensor out."""
     import torch
 
-    if kind not in _KINDS:
+    if kind not in ("sum", "max"):
         raise ValueError("reduction kind must be 'sum' or 'max'")
     result = segreduce_f32(
         values.detach().cpu().numpy(), offsets.detach().cpu().numpy(), kind)

@@ -39,6 +39,11 @@
 
 #define SWG_ORACLE_SUM 0
 #define SWG_ORACLE_MAX 1
+/* kind<min> exists in the reference's dialect only (ADR-0008; its lowering
+ * rejects it, SegmentedReduction.cpp:106-108): the mirror image of max --
+ * arith.minimumf from +inf -- is restated here by symmetry; no reference test
+ * pins it. */
+#define SWG_ORACLE_MIN 2
 
 /* arith.maximumf: NaN-propagating, -0.0 < +0.0.
  * SegmentedReduction.cpp:173-175 creates arith::MaximumFOp for kind == Max. */
@@ -50,11 +55,24 @@ static inline float oracle_maximumf(float a, float b) {
   return signbit(a) ? b : a;
 }
 
+/* arith.minimumf: NaN-propagating, -0.0 < +0.0. */
+static inline float oracle_minimumf(float a, float b) {
+  if (isnan(a) || isnan(b)) return NAN;
+  if (a < b) return a;
+  if (b < a) return b;
+  return signbit(a) ? a : b;
+}
+
 static inline float oracle_segment_f32(int kind, const float *values,
                                        int64_t start, int64_t end) {
   if (kind == SWG_ORACLE_SUM) {
     float acc = 0.0f; /* identity, SegmentedReduction.cpp:157-158 */
     for (int64_t i = start; i < end; ++i) acc = acc + values[i];
+    return acc;
+  }
+  if (kind == SWG_ORACLE_MIN) {
+    float acc = INFINITY;
+    for (int64_t i = start; i < end; ++i) acc = oracle_minimumf(acc, values[i]);
     return acc;
   }
   float acc = -INFINITY; /* identity, SegmentedReduction.cpp:159 */
@@ -69,7 +87,9 @@ static inline float oracle_segment_f32(int kind, const float *values,
 int swg_oracle_segreduce_f32(int kind, const float *values,
                              const int32_t *offsets, float *out,
                              int64_t segment_count, int threads) {
-  if (kind != SWG_ORACLE_SUM && kind != SWG_ORACLE_MAX) return -1;
+  if (kind != SWG_ORACLE_SUM && kind != SWG_ORACLE_MAX &&
+      kind != SWG_ORACLE_MIN)
+    return -1;
   int used = 1;
 #ifdef _OPENMP
   if (threads > 1) {

@@ -33,9 +33,9 @@ class CompilationError(Exception):
 class _Program(NamedTuple):
     """What a kernel body was recognised as.
 
-    ``kind`` is one of ``vector_add``, ``segmented_sum``, ``segmented_max``
-    or ``segmented_softmax``; ``roles`` maps the role of each runtime
-    parameter (``x``, ``y``, ``out``, ``n`` or ``values``, ``offsets``,
+    ``kind`` is one of ``vector_add``, ``segmented_sum``, ``segmented_max``,
+    ``segmented_min`` or ``segmented_softmax``; ``roles`` maps the role of each
+    runtime parameter (``x``, ``y``, ``out``, ``n`` or ``values``, ``offsets``,
     ``out``) to its name in the kernel signature.
     """
 
@@ -337,14 +337,14 @@ class _Kernel:
 #   ("param", name) | ("static", name) | ("int", v) | ("pid",) | ("lanes",)
 #   ("add", a, b) | ("mul", a, b) | ("sub", a, b) | ("div", a, b) | ("lt", a, b)
 #   ("load", address, mask) | ("sid",) | ("segment", values, offsets, index)
-#   ("elements", segment) | ("max", x) | ("sum", x) | ("exp", x)
+#   ("elements", segment) | ("max", x) | ("min", x) | ("sum", x) | ("exp", x)
 # and a list of effects ("store", address, value, mask) or
 # ("store_segment", pointer, segment, value).  Matching is then plain tuple
 # comparison against the canonical forms below.
 
 _SEGMENT_CALLS = {
-    "segment_id", "segment", "load_segment", "store_segment", "max", "sum",
-    "exp",
+    "segment_id", "segment", "load_segment", "store_segment", "max", "min",
+    "sum", "exp",
 }
 
 
@@ -572,7 +572,7 @@ class _Recognizer:
         segment = ("segment", values, offsets, ("sid",))
         x = ("elements", segment)
         roles = dict(zip(("values", "offsets", "out"), self.runtime))
-        for kind in ("sum", "max"):
+        for kind in ("sum", "max", "min"):
             if effect == ("store", ("add", out, ("sid",)), (kind, x), None):
                 return _Program(f"segmented_{kind}", roles)
         # softmax in the reference's semantic form

@@ -214,5 +214,5 @@ def _launch_segmented(kernel, arguments, constexprs, grid, torch):
         )
     return runner.launch_gpu(
         values, offsets, output, program.kind[len("segmented_"):],
-        _validated=(value_count, segment_count),
+        extensions=True, _validated=(value_count, segment_count),
     )

@@ -33,6 +33,9 @@ from . import _runtime
 
 _I32_LIMIT = 1 << 31
 _KINDS = {"sum": 0, "max": 1}
+# kinds the reference's dialect names but its runner rejects; accepted only
+# when the caller asks for extensions
+_EXTENDED_KINDS = {"min": 2}
 # Below this many values + segments a launch is latency-bound whatever the
 # mapping, and the plan-free schedules are used.
 _PLAN_THRESHOLD = 1 << 16
@@ -472,7 +475,7 @@ def _check_block(block_size, torch):
 
 
 def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
-               schedule="auto", _validated=None):
+               schedule="auto", extensions=False, _validated=None):
     """Queue one segmented ``sum`` or ``max`` on the current PyTorch stream.
 
     ``output[s] = reduce(values[offsets[s]:offsets[s + 1]])`` for every
@@ -482,6 +485,10 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
 
     ``plan`` (a ``SegmentPlan`` for these offsets) skips validation's planner
     step; ``schedule`` forces ``warp``, ``cta``, ``split`` or ``persistent``.
+    With ``extensions=True`` ``kind`` may also be ``"min"`` (NaN-propagating
+    minimum from ``+inf``: the dialect's ``kind<min>``, which the reference's
+    lowering rejects, ``SegmentedReduction.cpp:106-108``); without it the
+    reference's error is kept.
     """
     torch = _runtime._import_torch()
     if _validated is None:
@@ -489,7 +496,11 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
     else:
         value_count, segment_count = _validated
     _check_block(block_size, torch)
-    if kind not in _KINDS:
+    if kind in _KINDS:
+        kind_code = _KINDS[kind]
+    elif extensions and kind in _EXTENDED_KINDS:
+        kind_code = _EXTENDED_KINDS[kind]
+    else:
         raise ValueError("reduction kind must be 'sum' or 'max'")
     code = _schedule_code(schedule)
     if segment_count == 0:
@@ -508,7 +519,7 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
     _last_digest.value = None
     stream = torch.cuda.current_stream()
     _native.segreduce(
-        _KINDS[kind], values.data_ptr(), offsets.data_ptr(), output.data_ptr(),
+        kind_code, values.data_ptr(), offsets.data_ptr(), output.data_ptr(),
         value_count, segment_count,
         plan.handle if plan is not None else None,
         code, block_size, stream.cuda_stream,

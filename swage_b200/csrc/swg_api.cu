@@ -418,8 +418,9 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
                       const swg_plan *plan, int schedule, int32_t block_hint,
                       void *stream) {
   swg::clear_error();
-  if (kind != SWG_KIND_SUM && kind != SWG_KIND_MAX) {
-    swg::set_error("reduction kind must be SWG_KIND_SUM or SWG_KIND_MAX");
+  if (kind != SWG_KIND_SUM && kind != SWG_KIND_MAX && kind != SWG_KIND_MIN) {
+    swg::set_error(
+        "reduction kind must be SWG_KIND_SUM, SWG_KIND_MAX or SWG_KIND_MIN");
     return SWG_ERR_INVALID_ARGUMENT;
   }
   if (value_count < 0 || segment_count < 0 || block_hint < 0 ||
@@ -487,8 +488,9 @@ int swg_segreduce_f32_noalloc(int kind, const float *values,
                               int32_t value_count, int32_t segment_count,
                               void *stream) {
   swg::clear_error();
-  if (kind != SWG_KIND_SUM && kind != SWG_KIND_MAX) {
-    swg::set_error("reduction kind must be SWG_KIND_SUM or SWG_KIND_MAX");
+  if (kind != SWG_KIND_SUM && kind != SWG_KIND_MAX && kind != SWG_KIND_MIN) {
+    swg::set_error(
+        "reduction kind must be SWG_KIND_SUM, SWG_KIND_MAX or SWG_KIND_MIN");
     return SWG_ERR_INVALID_ARGUMENT;
   }
   if (value_count < 0 || segment_count < 0 || !host_offsets) {

@@ -38,6 +38,18 @@ struct MaxOp {
   }
 };
 
+// Min: arith.minimumf, the mirror image (NaN-propagating, -0 below +0,
+// identity +inf).  The reference's dialect admits kind<min> (ADR-0008) but its
+// lowering rejects it (SegmentedReduction.cpp:106-108).
+struct MinOp {
+  static __device__ __forceinline__ float identity() { return CUDART_INF_F; }
+  static __device__ __forceinline__ float apply(float a, float b) {
+    float r;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+  }
+};
+
 template <class Op>
 __device__ __forceinline__ float fold4(float acc, float4 q) {
   return Op::apply(Op::apply(acc, Op::apply(q.x, q.y)), Op::apply(q.z, q.w));

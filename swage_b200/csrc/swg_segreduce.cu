@@ -623,20 +623,31 @@ static cudaError_t persistent_dispatch(const float *values, float *out,
                                      configure);
 }
 
+// Calls f with the operator type of `kind` (f is a generic lambda).
+template <class F>
+static cudaError_t with_op(int kind, F &&f) {
+  switch (kind) {
+    case SWG_KIND_SUM: return f(SumOp{});
+    case SWG_KIND_MAX: return f(MaxOp{});
+    default: return f(MinOp{});
+  }
+}
+
 cudaError_t configure_segreduce_kernels() {
-  cudaError_t e;
   DevicePlan none;
-  e = persistent_dispatch<SumOp>(nullptr, nullptr, 0, none, nullptr, true);
-  if (e != cudaSuccess) return e;
-  e = persistent_dispatch<MaxOp>(nullptr, nullptr, 0, none, nullptr, true);
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(segreduce_split_kernel<SumOp>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           kSplitBytes);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(segreduce_split_kernel<MaxOp>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              kSplitBytes);
+  for (int kind : {SWG_KIND_SUM, SWG_KIND_MAX, SWG_KIND_MIN}) {
+    cudaError_t e = with_op(kind, [&](auto op) {
+      using Op = decltype(op);
+      cudaError_t inner =
+          persistent_dispatch<Op>(nullptr, nullptr, 0, none, nullptr, true);
+      if (inner != cudaSuccess) return inner;
+      return cudaFuncSetAttribute(segreduce_split_kernel<Op>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kSplitBytes);
+    });
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
 }
 
 cudaError_t launch_segreduce_warp(int kind, const float *values,
@@ -648,16 +659,14 @@ cudaError_t launch_segreduce_warp(int kind, const float *values,
   const int64_t cap = (int64_t)sm_count * 8 * 4;
   if (grid > cap) grid = cap;
   probe_begin(probe, stream);
-  if (kind == SWG_KIND_SUM)
-    segreduce_warp_kernel<SumOp><<<(unsigned)grid, kWarpKernelThreads, 0,
-                                   stream>>>(values, offsets, out,
-                                             segment_count);
-  else
-    segreduce_warp_kernel<MaxOp><<<(unsigned)grid, kWarpKernelThreads, 0,
-                                   stream>>>(values, offsets, out,
-                                             segment_count);
+  const cudaError_t e = with_op(kind, [&](auto op) {
+    segreduce_warp_kernel<decltype(op)>
+        <<<(unsigned)grid, kWarpKernelThreads, 0, stream>>>(
+            values, offsets, out, segment_count);
+    return cudaGetLastError();
+  });
   probe_end(probe, stream);
-  return cudaGetLastError();
+  return e;
 }
 
 cudaError_t launch_segreduce_cta(int kind, const float *values,
@@ -672,14 +681,13 @@ cudaError_t launch_segreduce_cta(int kind, const float *values,
   const int64_t cap = (int64_t)sm_count * (2048 / block) * 4;
   if (grid > cap) grid = cap;
   probe_begin(probe, stream);
-  if (kind == SWG_KIND_SUM)
-    segreduce_cta_kernel<SumOp><<<(unsigned)grid, block, 0, stream>>>(
+  const cudaError_t e = with_op(kind, [&](auto op) {
+    segreduce_cta_kernel<decltype(op)><<<(unsigned)grid, block, 0, stream>>>(
         values, offsets, out, segment_count);
-  else
-    segreduce_cta_kernel<MaxOp><<<(unsigned)grid, block, 0, stream>>>(
-        values, offsets, out, segment_count);
+    return cudaGetLastError();
+  });
   probe_end(probe, stream);
-  return cudaGetLastError();
+  return e;
 }
 
 template <class Op>
@@ -710,8 +718,9 @@ static cudaError_t launch_combine_as(const DevicePlan &plan, float *out,
 static cudaError_t launch_combine(int kind, const DevicePlan &plan, float *out,
                                   cudaStream_t stream) {
   if (plan.split_count == 0) return cudaSuccess;
-  return kind == SWG_KIND_SUM ? launch_combine_as<SumOp>(plan, out, stream)
-                              : launch_combine_as<MaxOp>(plan, out, stream);
+  return with_op(kind, [&](auto op) {
+    return launch_combine_as<decltype(op)>(plan, out, stream);
+  });
 }
 
 cudaError_t launch_segreduce_split(int kind, const float *values, float *out,
@@ -722,18 +731,14 @@ cudaError_t launch_segreduce_split(int kind, const float *values, float *out,
       (unsigned)((plan.task_count + kSplitWarps - 1) / kSplitWarps);
   const Limits limits{value_count, plan.segment_count, plan.partial_slots};
   probe_begin(probe, stream);
-  if (kind == SWG_KIND_SUM)
-    segreduce_split_kernel<SumOp>
+  cudaError_t e = with_op(kind, [&](auto op) {
+    segreduce_split_kernel<decltype(op)>
         <<<grid, kSplitWarps * 32, kSplitBytes, stream>>>(
             values, out, value_count, plan.tasks, plan.task_count,
             plan.offsets, plan.partials, plan.control, limits);
-  else
-    segreduce_split_kernel<MaxOp>
-        <<<grid, kSplitWarps * 32, kSplitBytes, stream>>>(
-            values, out, value_count, plan.tasks, plan.task_count,
-            plan.offsets, plan.partials, plan.control, limits);
+    return cudaGetLastError();
+  });
   probe_end(probe, stream);
-  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   return launch_combine(kind, plan, out, stream);
 }
@@ -745,12 +750,10 @@ cudaError_t launch_segreduce_persistent(int kind, const float *values,
                                         const Probe *probe) {
   if (plan.task_count == 0) return cudaSuccess;
   probe_begin(probe, stream);
-  cudaError_t e =
-      kind == SWG_KIND_SUM
-          ? persistent_dispatch<SumOp>(values, out, value_count, plan, stream,
-                                       false)
-          : persistent_dispatch<MaxOp>(values, out, value_count, plan, stream,
-                                       false);
+  cudaError_t e = with_op(kind, [&](auto op) {
+    return persistent_dispatch<decltype(op)>(values, out, value_count, plan,
+                                             stream, false);
+  });
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;
   return launch_combine(kind, plan, out, stream);

@@ -119,6 +119,12 @@ def max(value):  # noqa: A001 - name fixed by the kernel language
     _outside_kernel("max")
 
 
+def min(value):  # noqa: A001 - name fixed by the kernel language
+    """NaN-propagating minimum over a segment (symbolic).  An extension: the
+    reference's dialect has ``kind<min>``, its frontend and lowering do not."""
+    _outside_kernel("min")
+
+
 def sum(value):  # noqa: A001 - name fixed by the kernel language
     """Sum over a segment (symbolic)."""
     _outside_kernel("sum")
@@ -138,6 +144,7 @@ __all__ = [
     "load",
     "load_segment",
     "max",
+    "min",
     "pointer",
     "program_id",
     "segment",

@@ -29,6 +29,13 @@ def segmented_max(values_ptr, offsets_ptr, output_ptr):  # noqa: D103
 
 
 @sw.jit
+def segmented_min(values_ptr, offsets_ptr, output_ptr):  # noqa: D103
+    sid = sl.segment_id(0)
+    x = sl.load_segment(sl.segment(values_ptr, offsets_ptr, sid))
+    sl.store(output_ptr + sid, sl.min(x))
+
+
+@sw.jit
 def segmented_softmax(values_ptr, offsets_ptr, output_ptr):  # noqa: D103
     sid = sl.segment_id(0)
     segment = sl.segment(values_ptr, offsets_ptr, sid)
@@ -68,6 +75,51 @@ def test_sum_and_max_through_kernel_launch():
         else:
             error = np.abs(got - oracle.segsum_f64(host, offsets))
             assert np.all(error <= oracle.sum_tolerance(host, offsets))
+
+
+def test_min_kind_every_schedule():
+    """kind<min> (an extension: the reference's lowering rejects it): bit-exact
+    against the oracle's mirror image of max, through kernel.launch and
+    through every schedule of launch_gpu; the plain launch_gpu call keeps the
+    reference's error."""
+    from swage_b200._segmented_qualification import launch_gpu, plan_segments
+
+    offsets, values, device_offsets = inputs()
+    segments = len(offsets) - 1
+    host = values.cpu().numpy().copy()
+    host[12345] = np.nan
+    values = torch.as_tensor(host).cuda()
+    expected = oracle.segreduce_f32(host, offsets, "min")
+    output = torch.full((segments,), float("nan"), device="cuda")
+    segmented_min.launch(
+        arguments={"values_ptr": values, "offsets_ptr": device_offsets,
+                   "output_ptr": output},
+        constexprs={}, grid=(segments,))
+    torch.cuda.synchronize()
+    got = output.cpu().numpy()
+    both_nan = np.isnan(got) & np.isnan(expected)
+    assert np.all(both_nan | (got.view(np.uint32) == expected.view(np.uint32)))
+    assert np.isnan(expected).sum() == 1
+    plans = (plan_segments(torch.as_tensor(offsets)),
+             plan_segments(device_offsets, int(offsets[-1])))
+    for plan in plans:
+        for schedule in ("warp", "cta", "split", "persistent"):
+            output.fill_(float("nan"))
+            launch_gpu(values, device_offsets, output, "min", plan=plan,
+                       schedule=schedule, extensions=True)
+            torch.cuda.synchronize()
+            got = output.cpu().numpy()
+            both_nan = np.isnan(got) & np.isnan(expected)
+            assert np.all(both_nan | (got.view(np.uint32) ==
+                                      expected.view(np.uint32))), schedule
+        plan.close()
+    empty = torch.full((3,), float("nan"), device="cuda")
+    launch_gpu(values, torch.zeros(4, dtype=torch.int32, device="cuda"),
+               empty, "min", extensions=True)
+    torch.cuda.synchronize()
+    assert torch.isinf(empty).all() and (empty > 0).all()
+    with pytest.raises(ValueError, match="must be 'sum' or 'max'"):
+        launch_gpu(values, device_offsets, output, "min")
 
 
 def test_softmax_through_kernel_launch():

@@ -57,7 +57,7 @@ def test_c_oracle_matches_reference_literal_cases(name):
         oracle.py_segreduce(values, case["offsets"], case["kind"]), expected)
 
 
-@pytest.mark.parametrize("kind", ["sum", "max"])
+@pytest.mark.parametrize("kind", ["sum", "max", "min"])
 def test_c_and_python_restatements_agree_on_random_small_inputs(kind):
     rng = np.random.default_rng(11)
     for _ in range(20):
@@ -75,6 +75,25 @@ def test_max_orders_negative_zero_below_positive_zero():
     assert [struct.pack("<f", v) for v in result] == [
         struct.pack("<f", 0.0), struct.pack("<f", 0.0),
         struct.pack("<f", -0.0)]
+
+
+def test_min_is_the_mirror_image_of_max():
+    """kind<min> has no reference lowering; it is restated by symmetry:
+    min(x) == -max(-x) bit for bit, NaN propagates, -0 below +0, +inf when
+    empty."""
+    rng = np.random.default_rng(12)
+    lengths = rng.integers(0, 50, size=40)
+    offsets = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    values = rng.standard_normal(offsets[-1]).astype(np.float32)
+    values[rng.integers(0, values.size, size=5)] = np.nan
+    low = oracle.segreduce_f32(values, offsets, "min")
+    high = oracle.segreduce_f32(-values, offsets, "max")
+    assert same_bits_or_both_nan(low, -high)
+    zeros = np.array([-0.0, 0.0, 0.0, -0.0, 0.0], dtype=np.float32)
+    result = oracle.segreduce_f32(zeros, [0, 2, 4, 5, 5], "min")
+    assert [struct.pack("<f", v) for v in result] == [
+        struct.pack("<f", -0.0), struct.pack("<f", -0.0),
+        struct.pack("<f", 0.0), struct.pack("<f", np.inf)]
 
 
 def test_sequential_sum_is_strictly_left_to_right():
