@@ -63,6 +63,7 @@ typedef enum swg_status {
 #define SWG_SCHED_CTA 2        /* one CTA per segment: the reference's own mapping */
 #define SWG_SCHED_SPLIT 3      /* one tile task per CTA, long segments chunked, second-pass combine */
 #define SWG_SCHED_PERSISTENT 4 /* one CTA per SM slot, bulk-copy ring, tasks drawn from a ticket counter */
+#define SWG_SCHED_RESIDENT 5   /* one CTA per SM, one stage per warp, tile tasks at a fixed stride */
 
 /* Why swg_validate_offsets_i32 rejected an array (order = order of the checks
  * in python/swage/_segmented_qualification.py:30-55). */

@@ -20,13 +20,15 @@ LIBRARY_PATH = pathlib.Path(__file__).resolve().parent / "libswage_b200.so"
 # mirrors of the header's constants
 KIND_SUM, KIND_MAX = 0, 1
 OP_REDUCE, OP_SOFTMAX = 0, 1
-SCHED_AUTO, SCHED_WARP, SCHED_CTA, SCHED_SPLIT, SCHED_PERSISTENT = range(5)
+(SCHED_AUTO, SCHED_WARP, SCHED_CTA, SCHED_SPLIT, SCHED_PERSISTENT,
+ SCHED_RESIDENT) = range(6)
 SCHEDULES = {
     "auto": SCHED_AUTO,
     "warp": SCHED_WARP,
     "cta": SCHED_CTA,
     "split": SCHED_SPLIT,
     "persistent": SCHED_PERSISTENT,
+    "resident": SCHED_RESIDENT,
 }
 OFFSETS_REASONS = (
     "ok", "empty", "count_range", "output_small", "nonzero_start",

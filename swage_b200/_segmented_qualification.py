@@ -484,7 +484,8 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
     (``_segmented_qualification.py:120-172``).
 
     ``plan`` (a ``SegmentPlan`` for these offsets) skips validation's planner
-    step; ``schedule`` forces ``warp``, ``cta``, ``split`` or ``persistent``.
+    step; ``schedule`` forces ``warp``, ``cta``, ``split``, ``persistent`` or
+    ``resident``.
     With ``extensions=True`` ``kind`` may also be ``"min"`` (NaN-propagating
     minimum from ``+inf``: the dialect's ``kind<min>``, which the reference's
     lowering rejects, ``SegmentedReduction.cpp:106-108``); without it the
@@ -509,7 +510,8 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
     from . import _native
 
     if plan is None and (
-        code in (_native.SCHED_SPLIT, _native.SCHED_PERSISTENT)
+        code in (_native.SCHED_SPLIT, _native.SCHED_PERSISTENT,
+                 _native.SCHED_RESIDENT)
         or (code == _native.SCHED_AUTO
             and value_count + segment_count >= _PLAN_THRESHOLD)
     ):
@@ -555,7 +557,8 @@ def launch_softmax_gpu(values, offsets, output, *, plan=None, schedule="auto",
     from . import _native
 
     if plan is None and (
-        code in (_native.SCHED_SPLIT, _native.SCHED_PERSISTENT)
+        code in (_native.SCHED_SPLIT, _native.SCHED_PERSISTENT,
+                 _native.SCHED_RESIDENT)
         or (code == _native.SCHED_AUTO
             and value_count + segment_count >= _PLAN_THRESHOLD)
     ):

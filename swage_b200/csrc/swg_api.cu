@@ -424,7 +424,7 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
     return SWG_ERR_INVALID_ARGUMENT;
   }
   if (value_count < 0 || segment_count < 0 || block_hint < 0 ||
-      schedule < SWG_SCHED_AUTO || schedule > SWG_SCHED_PERSISTENT) {
+      schedule < SWG_SCHED_AUTO || schedule > SWG_SCHED_RESIDENT) {
     swg::set_error("swg_segreduce_f32: bad count, block or schedule");
     return SWG_ERR_INVALID_ARGUMENT;
   }
@@ -449,8 +449,10 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
     }
     if (schedule == SWG_SCHED_AUTO) schedule = plan->host.schedule;
   } else {
-    if (schedule == SWG_SCHED_SPLIT || schedule == SWG_SCHED_PERSISTENT) {
-      swg::set_error("the split and persistent schedules need a plan");
+    if (schedule == SWG_SCHED_SPLIT || schedule == SWG_SCHED_PERSISTENT ||
+        schedule == SWG_SCHED_RESIDENT) {
+      swg::set_error(
+          "the split, persistent and resident schedules need a plan");
       return SWG_ERR_UNSUPPORTED;
     }
     if (schedule == SWG_SCHED_AUTO)
@@ -473,6 +475,10 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
     case SWG_SCHED_SPLIT:
       e = swg::launch_segreduce_split(kind, values, out, value_count,
                                       plan->dev, s, probe);
+      break;
+    case SWG_SCHED_RESIDENT:
+      e = swg::launch_segreduce_resident(kind, values, out, value_count,
+                                         plan->dev, s, probe);
       break;
     default:
       e = swg::launch_segreduce_persistent(kind, values, out, value_count,
@@ -541,7 +547,7 @@ int swg_segsoftmax_f32(const float *values, const int32_t *offsets, float *out,
                        const swg_plan *plan, int schedule, void *stream) {
   swg::clear_error();
   if (value_count < 0 || segment_count < 0 || schedule < SWG_SCHED_AUTO ||
-      schedule > SWG_SCHED_PERSISTENT) {
+      schedule > SWG_SCHED_RESIDENT) {
     swg::set_error("swg_segsoftmax_f32: bad count or schedule");
     return SWG_ERR_INVALID_ARGUMENT;
   }
@@ -564,7 +570,7 @@ int swg_segsoftmax_f32(const float *values, const int32_t *offsets, float *out,
       swg::set_error("plan was not built for this softmax launch");
       return SWG_ERR_PLAN_MISMATCH;
     }
-  } else if (schedule == SWG_SCHED_SPLIT || schedule == SWG_SCHED_PERSISTENT) {
+  } else if (schedule >= SWG_SCHED_SPLIT) {
     swg::set_error("the planned softmax schedule needs a plan");
     return SWG_ERR_UNSUPPORTED;
   }
@@ -576,7 +582,7 @@ int swg_segsoftmax_f32(const float *values, const int32_t *offsets, float *out,
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t e;
   const swg::Probe *probe = next_probe();
-  if (plan && (schedule == SWG_SCHED_SPLIT || schedule == SWG_SCHED_PERSISTENT))
+  if (plan && schedule >= SWG_SCHED_SPLIT)
     e = swg::launch_segsoftmax_planned(values, offsets, out, value_count,
                                        plan->dev, s, probe);
   else if (schedule == SWG_SCHED_WARP)

@@ -619,10 +619,8 @@ cudaError_t device_plan(const int32_t *offsets, int32_t segment_count,
     return e;
   }
 
-  // the same schedule rule as the host planner
-  host->schedule = (s.max_length <= 4096 && host->mean_length >= 256.0)
-                       ? SWG_SCHED_WARP
-                       : SWG_SCHED_SPLIT;
+  host->schedule = choose_schedule(host->elements_in_bin, host->value_count,
+                                   host->max_length, host->mean_length);
   const int64_t items = (int64_t)s.last_offset + segment_count;
   const int64_t tiles = (items + kDeviceTile - 1) / kDeviceTile;
   dev->task_count = (int32_t)tiles;

@@ -64,6 +64,12 @@ cudaError_t launch_segreduce_persistent(int kind, const float *values,
                                         const DevicePlan &plan,
                                         cudaStream_t stream,
                                         const Probe *probe);
+// One resident CTA per SM, one stage per warp, tasks at a fixed stride +
+// combine pass.
+cudaError_t launch_segreduce_resident(int kind, const float *values,
+                                      float *out, int32_t value_count,
+                                      const DevicePlan &plan,
+                                      cudaStream_t stream, const Probe *probe);
 cudaError_t configure_segreduce_kernels();
 cudaError_t configure_softmax_kernels();
 

@@ -89,6 +89,27 @@ struct HostPlan {
   int64_t task_total = -1, split_total = -1;
 };
 
+// Schedule choice from the length statistics (measured on B200):
+//  - small inputs whose segments are all of moderate length: one warp per
+//    segment streams straight from global memory, no staging;
+//  - most values in long segments (nearly every tile a chunk): tile tasks, a
+//    CTA per pair (split) -- the hardware CTA scheduler then keeps the most
+//    copies in flight;
+//  - otherwise, large inputs: the same tile tasks on resident CTAs, which
+//    hide the time a warp spends reducing a tile of many segments;
+//  - small skewed inputs: split.
+// The persistent (ticketed ring) schedule runs the same tasks and is
+// selectable, but is never the fastest.
+inline int choose_schedule(const int64_t *elements_in_bin, int64_t value_count,
+                           int64_t max_length, double mean_length) {
+  int64_t in_long = 0;  // values in segments of at least 4096
+  for (int bin = 13; bin < kHistogramBins; ++bin) in_long += elements_in_bin[bin];
+  if (2 * in_long >= value_count && value_count > 0) return SWG_SCHED_SPLIT;
+  if (value_count >= (int64_t(1) << 24)) return SWG_SCHED_RESIDENT;
+  return max_length <= 4096 && mean_length >= 256.0 ? SWG_SCHED_WARP
+                                                    : SWG_SCHED_SPLIT;
+}
+
 // Builds the histogram, the task list and the schedule choice.
 void build_host_plan(const int32_t *offsets, int32_t segment_count, int op,
                      HostPlan *plan);

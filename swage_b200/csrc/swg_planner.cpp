@@ -295,16 +295,8 @@ void build_host_plan(const int32_t *offsets, int32_t segment_count, int op,
     return;
   }
   plan_reduce(offsets, segment_count, plan);
-  // Schedule choice from the histogram (measured on B200):
-  //  - every segment of moderate length and none long: one warp per segment
-  //    streams straight from global memory and needs no staging;
-  //  - anything skewed, or dominated by short segments: tile tasks, one per
-  //    warp (split), which balance long segments and pack short ones.
-  // The persistent schedule runs the same tasks and is selectable, but the
-  // hardware CTA scheduler keeps more tiles in flight than its private rings.
-  const bool moderate =
-      plan->max_length <= 4096 && plan->mean_length >= 256.0;
-  plan->schedule = moderate ? SWG_SCHED_WARP : SWG_SCHED_SPLIT;
+  plan->schedule = choose_schedule(plan->elements_in_bin, plan->value_count,
+                                   plan->max_length, plan->mean_length);
 }
 
 std::string describe_host_plan(const HostPlan &plan) {

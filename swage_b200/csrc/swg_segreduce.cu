@@ -535,6 +535,71 @@ segreduce_persistent_kernel(const float *__restrict__ values,
   }
 }
 
+// resident schedule: one CTA per SM, every warp owns one stage for the whole
+// launch and walks the task list with a fixed stride (task = warp * CTAs +
+// CTA, then + warps * CTAs ...), so that neighbouring tasks run on
+// neighbouring SMs at the same time, as in the split schedule.  What it
+// removes is the part of a tile's life in which its stage holds nothing: no
+// CTA is launched per pair of tiles, and the next task's descriptor is fetched
+// while the current tile's copy is in flight.  Measured: 2 - 3 % faster than
+// split where tiles hold many segments (their reduction keeps a stage busy
+// longest), 10 % slower where nearly every tile is a chunk of a long segment
+// -- the planner picks by the share of values in long segments.
+template <class Op, int kWarps>
+__global__ void __launch_bounds__(kWarps * 32, 1)
+segreduce_resident_kernel(const float *__restrict__ values,
+                          float *__restrict__ out, int32_t value_count,
+                          const Task *__restrict__ tasks, int32_t task_count,
+                          const int32_t *__restrict__ d_off,
+                          float *__restrict__ partials,
+                          uint32_t *__restrict__ control, Limits limits) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ uint64_t full[kWarps];
+  __shared__ WarpScratch scratch[kWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int mis = (int)(((uintptr_t)values >> 2) & 3);
+  asm volatile("griddepcontrol.launch_dependents;");
+  if (lane == 0) {
+    mbar_init(&full[warp], 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  const Stage stage = stage_at(smem, warp);
+  const int64_t stride = (int64_t)gridDim.x * kWarps;
+  int64_t index = (int64_t)warp * gridDim.x + blockIdx.x;
+  if (index >= task_count) return;
+  Task task = tasks[index];
+  uint32_t parity = 0;
+  auto start = [&](const Task &t, int64_t at) {
+    if (lane == 0) {
+      if (task_ok(t, limits))
+        issue_task(t, values, mis, value_count, d_off, stage, &full[warp]);
+      else
+        mbar_arrive(&full[warp]);  // reported by process_task
+    }
+    (void)at;
+  };
+  start(task, index);
+  while (true) {
+    const int64_t next_index = index + stride;
+    const bool more = next_index < task_count;
+    Task next = task;
+    if (more) next = tasks[next_index];  // in flight during the wait below
+    if (!mbar_wait(&full[warp], parity)) {
+      if (lane == 0) report(control, kErrTimeout, (uint32_t)index);
+      return;
+    }
+    parity ^= 1u;
+    process_task<Op>(task, stage, mis, out, partials, &scratch[warp], limits,
+                     control, lane);
+    if (!more) return;
+    __syncwarp();  // every lane is done with the stage before it is refilled
+    task = next;
+    index = next_index;
+    start(task, index);
+  }
+}
+
 // Second pass of the split / persistent schedules: merge the partials of each
 // cut segment in slot order.  The plan lists the segments with at least
 // kBigSplit partials first (a CTA each: CTAs 0..big-1), then the middle (a
@@ -636,6 +701,14 @@ static cudaError_t persistent_dispatch(const float *values, float *out,
                                      configure);
 }
 
+#ifndef SWG_RESIDENT_WARPS
+#define SWG_RESIDENT_WARPS 26
+#endif
+constexpr int kResidentWarps = SWG_RESIDENT_WARPS;
+static_assert(kResidentWarps * (kStageBytes + (int)sizeof(WarpScratch) + 8) <=
+                  227 * 1024,
+              "stages of the resident kernel exceed shared memory");
+
 // Calls f with the operator type of `kind` (f is a generic lambda).
 template <class F>
 static cudaError_t with_op(int kind, F &&f) {
@@ -653,6 +726,11 @@ cudaError_t configure_segreduce_kernels() {
       using Op = decltype(op);
       cudaError_t inner =
           persistent_dispatch<Op>(nullptr, nullptr, 0, none, nullptr, true);
+      if (inner != cudaSuccess) return inner;
+      inner = cudaFuncSetAttribute(
+          segreduce_resident_kernel<Op, kResidentWarps>,
+          cudaFuncAttributeMaxDynamicSharedMemorySize,
+          kResidentWarps * kStageBytes);
       if (inner != cudaSuccess) return inner;
       return cudaFuncSetAttribute(segreduce_split_kernel<Op>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -766,6 +844,29 @@ cudaError_t launch_segreduce_persistent(int kind, const float *values,
   cudaError_t e = with_op(kind, [&](auto op) {
     return persistent_dispatch<decltype(op)>(values, out, value_count, plan,
                                              stream, false);
+  });
+  probe_end(probe, stream);
+  if (e != cudaSuccess) return e;
+  return launch_combine(kind, plan, out, stream);
+}
+
+cudaError_t launch_segreduce_resident(int kind, const float *values,
+                                      float *out, int32_t value_count,
+                                      const DevicePlan &plan,
+                                      cudaStream_t stream,
+                                      const Probe *probe) {
+  if (plan.task_count == 0) return cudaSuccess;
+  int grid = plan.sm_count;
+  const int needed = (plan.task_count + kResidentWarps - 1) / kResidentWarps;
+  if (grid > needed) grid = needed;
+  probe_begin(probe, stream);
+  cudaError_t e = with_op(kind, [&](auto op) {
+    segreduce_resident_kernel<decltype(op), kResidentWarps>
+        <<<grid, kResidentWarps * 32, kResidentWarps * kStageBytes, stream>>>(
+            values, out, value_count, plan.tasks, plan.task_count,
+            plan.offsets, plan.partials, plan.control,
+            Limits{value_count, plan.segment_count, plan.partial_slots});
+    return cudaGetLastError();
   });
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;

@@ -162,7 +162,7 @@ def test_device_planned_reduce_matches_the_oracle(name, kind):
     values = rng.standard_normal(int(offsets[-1]) + 3).astype(np.float32)
     plan = device_plan(offsets)
     try:
-        for schedule in ("split", "persistent"):
+        for schedule in ("split", "persistent", "resident"):
             check_reduce(values, offsets, kind, schedule, plan=plan)
         plan.check()
     finally:

@@ -103,7 +103,7 @@ def test_min_kind_every_schedule():
     plans = (plan_segments(torch.as_tensor(offsets)),
              plan_segments(device_offsets, int(offsets[-1])))
     for plan in plans:
-        for schedule in ("warp", "cta", "split", "persistent"):
+        for schedule in ("warp", "cta", "split", "persistent", "resident"):
             output.fill_(float("nan"))
             launch_gpu(values, device_offsets, output, "min", plan=plan,
                        schedule=schedule, extensions=True)

@@ -24,7 +24,7 @@ pytestmark = pytest.mark.gpu
 KNOWN = json.loads(
     (pathlib.Path(__file__).parent / "golden" /
      "segmented_known_answers.json").read_text())
-SCHEDULES = ["auto", "warp", "cta", "split", "persistent"]
+SCHEDULES = ["auto", "warp", "cta", "split", "persistent", "resident"]
 
 
 def from_bits(words):
@@ -214,7 +214,8 @@ def test_config_canonical(kind, schedule):
     check_reduce(values, offsets, kind, schedule)
 
 
-@pytest.mark.parametrize("schedule", ["auto", "warp", "split", "persistent"])
+@pytest.mark.parametrize(
+    "schedule", ["auto", "warp", "split", "persistent", "resident"])
 def test_config_lognormal_max_reduced(schedule):
     offsets = workloads.c3_offsets(segments=1 << 15, cap=1 << 30)
     values = workloads.c3_values(offsets, "cuda").cpu().numpy()
@@ -225,7 +226,8 @@ def test_config_lognormal_max_reduced(schedule):
     assert (piece == result[first]).sum() >= 2
 
 
-@pytest.mark.parametrize("schedule", ["auto", "split", "persistent"])
+@pytest.mark.parametrize(
+    "schedule", ["auto", "split", "persistent", "resident"])
 @pytest.mark.parametrize("kind", ["sum", "max"])
 def test_config_extreme_skew_reduced(kind, schedule):
     offsets = workloads.c5_offsets(segments=1 << 17, total=1 << 24, giants=8,
