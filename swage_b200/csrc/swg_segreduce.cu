@@ -411,6 +411,11 @@ segreduce_split_kernel(const float *__restrict__ values,
   __syncwarp();
   const Task task = tasks[index];
   const Stage stage = stage_at(smem, warp);
+  // Launched with programmatic stream serialisation: everything up to here
+  // (CTA placement, barrier set-up, the descriptor round trip) touches only
+  // memory the plan owns and may overlap the tail of the kernel before; the
+  // caller's arrays are read and written only after that kernel has finished.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (!task_ok(task, limits)) {
     if (lane == 0) report(control, kErrBadTask, (uint32_t)index);
     return;
@@ -618,6 +623,9 @@ segreduce_combine_kernel(const SplitSegment *__restrict__ splits,
                          const float *__restrict__ partials,
                          float *__restrict__ out) {
   __shared__ float scratch[32];
+  // the next launch in the stream, if it is one of the tile kernels, may
+  // place its CTAs and fetch its descriptors while this grid runs
+  asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int32_t medium_ctas = (medium_count + 7) / 8;
@@ -823,11 +831,20 @@ cudaError_t launch_segreduce_split(int kind, const float *values, float *out,
   const Limits limits{value_count, plan.segment_count, plan.partial_slots};
   probe_begin(probe, stream);
   cudaError_t e = with_op(kind, [&](auto op) {
-    segreduce_split_kernel<decltype(op)>
-        <<<grid, kSplitWarps * 32, kSplitBytes, stream>>>(
-            values, out, value_count, plan.tasks, plan.task_count,
-            plan.offsets, plan.partials, plan.control, limits);
-    return cudaGetLastError();
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid);
+    config.blockDim = dim3(kSplitWarps * 32);
+    config.dynamicSmemBytes = kSplitBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(
+        &config, segreduce_split_kernel<decltype(op)>, values, out,
+        value_count, (const Task *)plan.tasks, plan.task_count,
+        (const int32_t *)plan.offsets, plan.partials, plan.control, limits);
   });
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;
