@@ -346,20 +346,70 @@ int shard_offsets(const int32_t *offsets, int32_t segment_count, int32_t shards,
     set_error("shard_offsets: bad arguments");
     return SWG_ERR_INVALID_ARGUMENT;
   }
-  const int64_t total = offsets[segment_count];
+  // A shard costs its values plus its segments (what the tile tasks count):
+  // cost of segments [a, b) = items(b) - items(a), items(i) = offsets[i] + i.
+  // The cuts minimise the largest shard: binary search on the bound, each
+  // probe packing shards greedily from the left with binary searches.
+  auto items = [&](int64_t i) { return (int64_t)offsets[i] + i; };
+  // last boundary b >= from with items(b) - items(from) <= bound
+  auto reach = [&](int64_t from, int64_t bound) {
+    int64_t lo = from, hi = segment_count;
+    const int64_t limit = items(from) + bound;
+    while (lo < hi) {
+      const int64_t mid = (lo + hi + 1) >> 1;
+      if (items(mid) <= limit) lo = mid;
+      else hi = mid - 1;
+    }
+    return lo;
+  };
+  auto fits = [&](int64_t bound) {
+    int64_t at = 0;
+    for (int32_t g = 0; g < shards && at < segment_count; ++g)
+      at = reach(at, bound);
+    return at >= segment_count;
+  };
+  const int64_t total = items(segment_count);
+  int64_t low = (total + shards - 1) / shards, high = total;
+  while (low < high) {
+    const int64_t mid = low + (high - low) / 2;
+    if (fits(mid)) high = mid;
+    else low = mid + 1;
+  }
+  // With the best bound known, every cut goes as near its ideal position as
+  // the bound allows: not before the point the shards to its left can reach
+  // back from (so they stay within the bound) ... walking from the right
+  // gives each cut's earliest position, from the left its latest.
+  std::vector<int64_t> latest((size_t)shards + 1, segment_count);
+  latest[0] = 0;
+  for (int32_t g = 1; g < shards; ++g) latest[g] = reach(latest[g - 1], low);
   seg_begin[0] = 0;
   for (int32_t g = 1; g < shards; ++g) {
-    const int64_t ideal = total * g / shards;
-    // first boundary index b in [0, segment_count] with offsets[b] >= ideal
-    const int32_t *at =
-        std::lower_bound(offsets, offsets + segment_count + 1, (int32_t)ideal);
-    int32_t boundary = (int32_t)(at - offsets);
-    if (boundary > segment_count) boundary = segment_count;
-    if (boundary > 0 &&
-        ideal - offsets[boundary - 1] < (int64_t)offsets[boundary] - ideal)
-      boundary -= 1;
-    if (boundary < seg_begin[g - 1]) boundary = seg_begin[g - 1];
-    seg_begin[g] = boundary;
+    const int64_t ideal = total / shards * g;
+    // first boundary whose items reach the ideal position
+    int64_t lo = seg_begin[g - 1], hi = latest[g];
+    while (lo < hi) {
+      const int64_t mid = (lo + hi) >> 1;
+      if (items(mid) >= ideal) hi = mid;
+      else lo = mid + 1;
+    }
+    int64_t boundary = lo;
+    // the rest must still fit behind this cut: move right while it does not
+    auto rest_fits = [&](int64_t from) {
+      int64_t at = from;
+      for (int32_t r = g; r < shards && at < segment_count; ++r)
+        at = reach(at, low);
+      return at >= segment_count;
+    };
+    if (!rest_fits(boundary)) {
+      int64_t a = boundary, z = latest[g];  // rest_fits(z) holds
+      while (a < z) {
+        const int64_t mid = (a + z) >> 1;
+        if (rest_fits(mid)) z = mid;
+        else a = mid + 1;
+      }
+      boundary = a;
+    }
+    seg_begin[g] = (int32_t)boundary;
   }
   seg_begin[shards] = segment_count;
   return SWG_OK;
