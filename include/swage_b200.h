@@ -106,8 +106,8 @@ int swg_validate_offsets_i32(const int32_t *host_offsets, int64_t count,
  * device copies of the task list, of the offsets (16-byte aligned and padded,
  * so they can be bulk-copied) and the scratch for split-segment partials, all
  * on the current device.  It is the planned scheduling layer of the reference
- * (DESIGN.md:143-151 there: warp, packed_warp, cta, split_cta, merge,
- * persistent) made concrete.  A plan is valid only for launches whose device
+ * (its design document, lines 143-151: warp, packed_warp, cta, split_cta,
+ * merge, persistent) made concrete.  A plan is valid only for launches whose device
  * offsets hold the same numbers. */
 int swg_plan_create(const int32_t *host_offsets, int32_t segment_count,
                     int32_t value_count, int op, swg_plan **plan);
@@ -128,7 +128,8 @@ int swg_plan_status(swg_plan *plan);
  * 64-bit digest of the offsets' content, *last_offset offsets[segment_count].
  * No reference counterpart: the reference copies the offsets to the host and
  * walks them in Python (python/swage/_segmented_qualification.py:30-55,78) and
- * lists device-only offset validation as future work (DESIGN.md:100-102). */
+ * lists device-only offset validation as future work (its design document,
+ * lines 100-102). */
 int swg_validate_offsets_device(const int32_t *device_offsets,
                                 int32_t segment_count, int32_t value_count,
                                 int64_t output_count, void *stream,

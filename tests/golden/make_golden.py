@@ -1,8 +1,8 @@
 """Regenerates the golden fixtures in this directory.
 
-Run where the reference checkout is mounted:
+Run where a checkout of the reference is at hand:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py PATH_TO_REFERENCE_CHECKOUT
 
 Three fixtures are written:
 
@@ -183,8 +183,9 @@ def known_answers():
 
 
 def main():
-    reference = pathlib.Path(sys.argv[1] if len(sys.argv) > 1
-                             else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py PATH_TO_REFERENCE_CHECKOUT")
+    reference = pathlib.Path(sys.argv[1])
     sys.path.insert(0, str(reference / "python"))
     written = {
         "offset_validation.json": offset_validation(reference),
