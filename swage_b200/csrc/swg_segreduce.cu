@@ -76,6 +76,9 @@ __global__ void segreduce_cta_kernel(const float *__restrict__ values,
 // pipeline on its own shared-memory stages and its own mbarriers, and the SM
 // overlaps the phases of its resident warps.
 // ---------------------------------------------------------------------------
+#ifndef SWG_WIDE_VECTOR
+#define SWG_WIDE_VECTOR 0  // 1: whole-warp segments of a packed tile by 128-bit loads
+#endif
 constexpr int kLaneSegment = 16;    // reduced by a single lane inside a tile
 constexpr int kGroupSegment = 256;  // up to here by a group of eight lanes
 // One stage holds the task's values and, for a packed task, its offsets right
@@ -363,6 +366,10 @@ __device__ __forceinline__ void process_task(const Task &task,
     for (int e = medium_count; e < listed; ++e) {
       // (the 128-bit range reduce of the chunk path was tried here: same
       // speed on the lognormal workload, eight more registers everywhere)
+#if SWG_WIDE_VECTOR
+      const float r =
+          warp_range<Op>(tile, scratch->begin[e], scratch->end[e], lane);
+#else
       const int ea = scratch->begin[e], eb = scratch->end[e];
       float p0 = Op::identity(), p1 = Op::identity(), p2 = Op::identity(),
             p3 = Op::identity();
@@ -376,6 +383,7 @@ __device__ __forceinline__ void process_task(const Task &task,
       for (; i < eb; i += 32) p0 = Op::apply(p0, tile[i]);
       const float r =
           warp_reduce<Op>(Op::apply(Op::apply(p0, p1), Op::apply(p2, p3)));
+#endif
       if (lane == 0) scratch->result[e] = r;
     }
     __syncwarp();
