@@ -58,9 +58,13 @@ struct SplitSegment {
 // through shared-memory rings whose size doubles from class to class, so that
 // a segment -- in the last class, one of up to 57344 values -- stays on the SM
 // between its two sweeps.
+#ifndef SWG_SOFTMAX_LIMIT6
+#define SWG_SOFTMAX_LIMIT6 24576  // a multiple of 2048: the ring of that class has LIMIT6 / 2048 warps
+#endif
 constexpr int kSoftmaxBuckets = 8;
 constexpr int kSoftmaxLimit[kSoftmaxBuckets - 1] = {64,   512,  2048, 4096,
-                                                    8192, 16384, 28672};
+                                                    8192, 16384,
+                                                    SWG_SOFTMAX_LIMIT6};
 
 struct HostPlan {
   int32_t segment_count = 0;

@@ -582,7 +582,7 @@ segsoftmax_ring_kernel(const float *__restrict__ values,
 //   bucket 3  (2048, 4096]    2 warps x 4 stages, 12 CTAs/SM  16 KB each
 //   bucket 4  (4096, 8192]    4 warps x 4 stages,  6 CTAs/SM  32 KB each
 //   bucket 5  (8192, 16384]   8 warps x 4 stages,  3 CTAs/SM  64 KB each
-//   bucket 6  (16384, 28672] 14 warps x 4 stages,  2 CTAs/SM 112 KB each
+//   bucket 6  (16384, 24576] 12 warps x 4 stages,  2 CTAs/SM  96 KB each
 //   bucket 7  longer         16 warps x 7 stages,  1 CTA/SM  224 KB: whole
 //             up to 57344 values, above that all but the last 57344 values of
 //             a segment are read a second time (from L2 when they are still
@@ -662,8 +662,9 @@ static cudaError_t ring_bucket(int bucket, const float *values,
       return ring_launch<8, 4, 3>(values, offsets, out, segments, count,
                                   value_count, plan, stream, kConfigure);
     case 6:
-      return ring_launch<14, 4, 2>(values, offsets, out, segments, count,
-                                   value_count, plan, stream, kConfigure);
+      return ring_launch<SWG_SOFTMAX_LIMIT6 / 2048, 4, 2>(
+          values, offsets, out, segments, count, value_count, plan, stream,
+          kConfigure);
     default:
       return ring_launch<16, 7, 1>(values, offsets, out, segments, count,
                                    value_count, plan, stream, kConfigure);
