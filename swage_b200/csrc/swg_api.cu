@@ -225,7 +225,7 @@ int swg_plan_create(const int32_t *host_offsets, int32_t segment_count,
                     plan->host.softmax_segments.size(),
                     "cudaMalloc(softmax buckets)");
   if (status == SWG_OK)
-    status = upload<uint32_t>(&dev.control, nullptr, 0, 4,
+    status = upload<uint32_t>(&dev.control, nullptr, 0, swg::kControlWords,
                               "cudaMalloc(control)");
   if (status != SWG_OK) {
     release(dev);

@@ -583,9 +583,10 @@ cudaError_t device_plan(const int32_t *offsets, int32_t segment_count,
   e = cudaMemcpyAsync(dev->offsets, offsets, noffsets * sizeof(int32_t),
                       cudaMemcpyDeviceToDevice, stream);
   if (e != cudaSuccess) return e;
-  e = cudaMalloc((void **)&dev->control, 4 * sizeof(uint32_t));
+  e = cudaMalloc((void **)&dev->control, kControlWords * sizeof(uint32_t));
   if (e != cudaSuccess) return e;
-  e = cudaMemsetAsync(dev->control, 0, 4 * sizeof(uint32_t), stream);
+  e = cudaMemsetAsync(dev->control, 0, kControlWords * sizeof(uint32_t),
+                      stream);
   if (e != cudaSuccess) return e;
 
   if (op == SWG_OP_SOFTMAX) {

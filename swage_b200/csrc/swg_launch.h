@@ -8,6 +8,9 @@
 
 namespace swg {
 
+constexpr int kTicketBase = 4;
+constexpr int kControlWords = kTicketBase + kSoftmaxBuckets + 4;  // 16
+
 // Device-resident part of a plan; every pointer is owned by the plan.
 struct DevicePlan {
   int device = -1;
@@ -25,7 +28,8 @@ struct DevicePlan {
   int32_t *softmax_segments = nullptr;  // bucketed segment ids
   int32_t softmax_begin[kSoftmaxBuckets] = {0};
   int32_t softmax_count[kSoftmaxBuckets] = {0};
-  uint32_t *control = nullptr;     // [0] ticket, [1] finished, [2] error, [3] detail
+  uint32_t *control = nullptr;     // [0] ticket, [1] finished, [2] error, [3] detail,
+                                   // [kTicketBase + class] softmax ticket counters
   bool shared_block = false;       // tasks, splits and partials are one allocation
 };
 

@@ -397,7 +397,8 @@ segsoftmax_ring_kernel(const float *__restrict__ values,
                        const int32_t *__restrict__ offsets,
                        float *__restrict__ out,
                        const int32_t *__restrict__ segments, int32_t count,
-                       int32_t value_count, uint32_t *__restrict__ control) {
+                       int32_t value_count, uint32_t *__restrict__ control,
+                       uint32_t *__restrict__ ticket) {
   static_assert(kWarps <= 32 && kStages >= 1 && kStages <= 16, "ring shape");
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full_all[kWarps * kStages];
@@ -424,8 +425,25 @@ segsoftmax_ring_kernel(const float *__restrict__ values,
     return r.chunks > warp ? (r.chunks - warp + kWarps - 1) / kWarps : 0;
   };
 
-  RingSegment g =
-      ring_segment(ring_bounds(offsets, segments, blockIdx.x, count), mis);
+  // Segments are handed out in list order to whichever CTA asks next (a
+  // ticket counter per length class, zeroed by the launcher): the CTAs of a
+  // class then work side by side on neighbouring segments whatever their
+  // pace, and none is left with a long tail.  Tickets are drawn two segments
+  // ahead of use -- thread 0 starts the atomic at the top of a segment and
+  // publishes it through shared memory across the barriers of that segment's
+  // reduction -- so neither the atomic nor the bounds of the next segment,
+  // fetched one segment ahead, are ever waited for.
+  __shared__ int ticket_box;
+  auto draw = [&]() -> int64_t {
+    if (tid == 0) ticket_box = (int)atomicAdd(ticket, 1u);
+    __syncthreads();
+    const int64_t drawn = ticket_box;
+    __syncthreads();
+    return drawn;
+  };
+  int64_t j = draw();
+  int64_t j_next = draw();
+  RingSegment g = ring_segment(ring_bounds(offsets, segments, j, count), mis);
   int mine = share(g);
   if (lane == 0)
     for (int k = 0; k < mine && k < kStages; ++k)
@@ -433,10 +451,11 @@ segsoftmax_ring_kernel(const float *__restrict__ values,
                  k * kWarps + warp, k + kStages < mine ? keep : once);
 
   bool down = false;  // direction of the chunk -> stage map
-  for (int64_t j = blockIdx.x; j < count; j += gridDim.x, down = !down) {
+  for (; j < count; down = !down) {
     // the next segment's bounds are fetched now and used after sweep A
-    const int2 next_bounds =
-        ring_bounds(offsets, segments, j + gridDim.x, count);
+    unsigned drawn = 0;
+    if (tid == 0) drawn = atomicAdd(ticket, 1u);  // consumed after sweep A
+    const int2 next_bounds = ring_bounds(offsets, segments, j_next, count);
     const int resident_from = mine > kStages ? mine - kStages : 0;
     auto stage_of = [&](int k, bool reversed) {
       return reversed ? kStages - 1 - k % kStages : k % kStages;
@@ -494,8 +513,10 @@ segsoftmax_ring_kernel(const float *__restrict__ values,
       }
     }
     if (failed) atomicCAS(control + 2, 0u, 1u);
+    if (tid == 0) ticket_box = (int)drawn;
     // the segment maximum first (NaN-propagating), then the sums rescaled to it
     const float m = cta_reduce<MaxOp>(any, scratch);
+    const int64_t j_after = ticket_box;  // written before the barriers above
     const float part = s.d == 0.0f ? 0.0f : s.d * exp_neg(s.m - m);
     const float d = cta_reduce<SumOp>(part, scratch);
     const float inv = 1.0f / d;
@@ -573,6 +594,8 @@ segsoftmax_ring_kernel(const float *__restrict__ values,
     if (failed) atomicCAS(control + 2, 0u, 1u);
     g = next;
     mine = next_mine;
+    j = j_next;
+    j_next = j_after;
   }
 }
 
@@ -596,7 +619,7 @@ static cudaError_t ring_launch(const float *values, const int32_t *offsets,
                                float *out, const int32_t *segments,
                                int32_t count, int32_t value_count,
                                const DevicePlan &plan, cudaStream_t stream,
-                               bool configure) {
+                               uint32_t *ticket, bool configure) {
   constexpr int kBytes = kWarps * kStages * kRingChunk * 4;
   static_assert((kBytes + 1024 + 8 * kWarps * kStages + 128) * kCtasPerSm <=
                     228 * 1024,
@@ -609,7 +632,8 @@ static cudaError_t ring_launch(const float *values, const int32_t *offsets,
   if (grid > count) grid = count;
   segsoftmax_ring_kernel<kWarps, kStages, kCtasPerSm>
       <<<grid, kWarps * 32, kBytes, stream>>>(values, offsets, out, segments,
-                                              count, value_count, plan.control);
+                                              count, value_count, plan.control,
+                                              ticket);
   return cudaGetLastError();
 }
 
@@ -651,23 +675,29 @@ static cudaError_t ring_bucket(int bucket, const float *values,
                                const int32_t *segments, int32_t count,
                                int32_t value_count, const DevicePlan &plan,
                                cudaStream_t stream) {
+  // one ticket counter per class, behind the plan's four control words
+  uint32_t *ticket = plan.control ? plan.control + kTicketBase + bucket : nullptr;
   switch (bucket) {
     case 3:
       return ring_launch<2, 4, 12>(values, offsets, out, segments, count,
-                                   value_count, plan, stream, kConfigure);
+                                   value_count, plan, stream, ticket,
+                                   kConfigure);
     case 4:
       return ring_launch<4, 4, 6>(values, offsets, out, segments, count,
-                                  value_count, plan, stream, kConfigure);
+                                  value_count, plan, stream, ticket,
+                                   kConfigure);
     case 5:
       return ring_launch<8, 4, 3>(values, offsets, out, segments, count,
-                                  value_count, plan, stream, kConfigure);
+                                  value_count, plan, stream, ticket,
+                                   kConfigure);
     case 6:
       return ring_launch<SWG_SOFTMAX_LIMIT6 / 2048, 4, 2>(
           values, offsets, out, segments, count, value_count, plan, stream,
-          kConfigure);
+          ticket, kConfigure);
     default:
       return ring_launch<16, 7, 1>(values, offsets, out, segments, count,
-                                   value_count, plan, stream, kConfigure);
+                                   value_count, plan, stream, ticket,
+                                   kConfigure);
   }
 }
 
@@ -694,6 +724,9 @@ cudaError_t launch_segsoftmax_planned(const float *values,
   cudaError_t e = fork_for(plan.device, &fork);
   if (e != cudaSuccess) return e;
   probe_begin(probe, stream);
+  e = cudaMemsetAsync(plan.control + kTicketBase, 0,
+                      kSoftmaxBuckets * sizeof(uint32_t), stream);
+  if (e != cudaSuccess) return e;
   e = cudaEventRecord(fork->begin, stream);
   if (e != cudaSuccess) return e;
   const int32_t *list = plan.softmax_segments;
