@@ -391,8 +391,12 @@ __device__ __forceinline__ void ring_loads_landed(
   asm volatile("" ::"r"(seen) : "memory");
 }
 
+// (The shape with one CTA per SM is compiled for 640 threads per block though
+// it runs 512: that caps it at 96 registers, at no cost in speed, and leaves
+// room on every SM for CTAs of the short classes' kernels to run beside it.)
 template <int kWarps, int kStages, int kCtasPerSm>
-__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
+__global__ void __launch_bounds__(kCtasPerSm == 1 ? kWarps * 40 : kWarps * 32,
+                                  kCtasPerSm)
 segsoftmax_ring_kernel(const float *__restrict__ values,
                        const int32_t *__restrict__ offsets,
                        float *__restrict__ out,
@@ -730,8 +734,9 @@ cudaError_t launch_segsoftmax_planned(const float *values,
   e = cudaEventRecord(fork->begin, stream);
   if (e != cudaSuccess) return e;
   const int32_t *list = plan.softmax_segments;
-  // the longest class on the caller's stream, the others beside it, longest
-  // first
+  // the longest class on the caller's stream; beside it first the three
+  // register kernels of the short classes (their CTAs fit next to the long
+  // class's and fill its bubbles), then the other rings, longest first
   constexpr int kLast = kSoftmaxBuckets - 1;
   if (plan.softmax_count[kLast] > 0) {
     e = ring_bucket<false>(kLast, values, offsets, out,
@@ -740,7 +745,9 @@ cudaError_t launch_segsoftmax_planned(const float *values,
                            stream);
     if (e != cudaSuccess) return e;
   }
-  for (int b = kLast - 1; b >= 0; --b) {
+  static const int kOrder[kLast] = {2, 1, 0, 6, 5, 4, 3};
+  for (int at = 0; at < kLast; ++at) {
+    const int b = kOrder[at];
     const int32_t n = plan.softmax_count[b];
     if (n == 0) continue;
     cudaStream_t side = fork->side[b];
