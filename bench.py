@@ -50,10 +50,10 @@ FALLBACK_HBM_GBS = 6650.0
 # bytes, from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum).
 # c5: capture of the workload shrunk 4x, 1.090 GB for 1.082 GB (traffic grows
 # in proportion to the units processed); c4: the kernels of a full-size call,
-# 8.76 GB for 9.055 GB (reads 4.543 GB for 4.528 GB of input; the writes
+# 8.75 GB for 9.055 GB (reads 4.562 GB for 4.528 GB of input; the writes
 # counted are short of the output because the last lines of each kernel are
 # still in L2 when it ends).  Workloads without a capture report null.
-TRAFFIC_RATIO = {"c5": 1.0074, "c4": 0.968}
+TRAFFIC_RATIO = {"c5": 1.0074, "c4": 0.966}
 
 
 def parse_arguments():
