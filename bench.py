@@ -206,11 +206,11 @@ class ClockSampler:
 # reference arm: the CPU path on all host threads
 # ---------------------------------------------------------------------------
 
-def cpu_sample(name, offsets, budget_elements):
-    """A prefix of whole segments holding at most ``budget_elements``."""
+def cpu_sample(name, offsets, limit_elements):
+    """A prefix of whole segments holding at most ``limit_elements``."""
     if offsets is None:
         return None
-    last = int(np.searchsorted(offsets, budget_elements, side="right")) - 1
+    last = int(np.searchsorted(offsets, limit_elements, side="right")) - 1
     last = max(1, min(last, len(offsets) - 1))
     return offsets[:last + 1]
 
@@ -263,8 +263,8 @@ def run_reference(args):
     cpu_pass(operation, kind, probe_values, probe_offsets, threads, args.block)
     rate = probe_count / cpu_pass(operation, kind, probe_values,
                                   probe_offsets, threads, args.block)
-    budget = 120.0 / max(1, args.steps + args.warmup)
-    sample_count = int(min(full_count, max(1 << 22, rate * budget)))
+    seconds_per_step = 120.0 / max(1, args.steps + args.warmup)
+    sample_count = int(min(full_count, max(1 << 22, rate * seconds_per_step)))
     sample_offsets = cpu_sample(args.workload, offsets, sample_count)
     if offsets is not None:
         sample_count = int(sample_offsets[-1])
