@@ -11,20 +11,27 @@ values are cut into N element-balanced contiguous segment ranges -- strong
 scaling, no data-path collective (``--allgather`` adds the optional NCCL
 all-gather of the per-segment results to every step).
 
-Rank 0 prints ONE JSON line.  ``value`` is whole-job throughput with inputs
-resident in HBM; ``e2e`` is the same metric through the public
-``launch_gpu`` / ``kernel.launch`` call with the inputs copied from pinned host
-memory and the result read back inside the timed region; ``roofline`` is the
-dominant kernel against the measured HBM copy bandwidth; ``cpu_baseline`` is
-the CPU oracle timed on this host; ``plan`` gives the one-off cost of building
-the schedule (on the GPU from device-resident offsets, and by the host
-planner from a host copy) and of validating the offsets on the GPU, none of
-which is inside ``value``'s timed region (``e2e`` pays validation every step
-and finds the plan by the offsets' content digest).
+Rank 0 prints ONE JSON line.
 
-``--impl reference`` times the reference's CPU path -- the sequential lowering
-restated in ``oracle/`` (the reference's own executable path needs an LLVM
-toolchain that is not in its tree) -- on all host threads, same workload.
+``value``      whole-job throughput with inputs resident in HBM and the plan
+               built: K steps between two CUDA events, nothing else recorded
+               on the stream inside that region.
+``roofline``   the dominant kernel against the measured HBM copy bandwidth;
+               its duration comes from a SEPARATE short loop in which the
+               library records a pair of events around that kernel.
+``cold``       the drop-in call on offsets the plan cache has not seen:
+               validation + planning + launch, device-resident inputs.
+``e2e``        the drop-in call with the inputs copied from pinned host
+               memory and the result read back, every step.
+``workloads``  (1 GPU) the other configurations measured the same way in the
+               same process, each with its parity status against the CPU
+               oracle at full size.
+``cpu_baseline`` the CPU restatement of the reference's sequential lowering
+               timed on this host's cores.
+
+``--impl reference`` times that CPU restatement (the reference's own
+executable path needs an LLVM toolchain that is not in its tree) on all host
+cores, on the same seeded inputs as the GPU arm.
 """
 
 import argparse
@@ -47,13 +54,12 @@ import workloads  # noqa: E402
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch of the dominant kernel divided by its algorithmic
-# bytes, from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum).
-# c5: capture of the workload shrunk 4x, 1.090 GB for 1.082 GB (traffic grows
-# in proportion to the units processed); c4: the kernels of a full-size call,
-# 8.75 GB for 9.055 GB (reads 4.562 GB for 4.528 GB of input; the writes
-# counted are short of the output because the last lines of each kernel are
-# still in L2 when it ends).  Workloads without a capture report null.
+# bytes, from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum) of
+# shrunk cases; traffic grows in proportion to the units processed.
+# Workloads without a capture report null.
 TRAFFIC_RATIO = {"c5": 1.0074, "c4": 0.966}
+ALL_WORKLOADS = ("c1", "c1x256", "c2", "c3", "c4", "c5")
+VADD_COUNT = (1 << 28) - 37
 
 
 def parse_arguments():
@@ -62,8 +68,7 @@ def parse_arguments():
     parser.add_argument("--steps", type=int, default=400)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="c5",
-                        choices=["c1", "c1x256", "c2", "c3", "c4", "c5"])
+    parser.add_argument("--workload", default="c5", choices=ALL_WORKLOADS)
     parser.add_argument("--schedule", default="auto")
     parser.add_argument("--block", type=int, default=128)
     parser.add_argument("--allgather", action="store_true")
@@ -73,12 +78,16 @@ def parse_arguments():
                              "(both are built once and timed)")
     parser.add_argument("--e2e-steps", type=int, default=None)
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--no-probe", action="store_true",
-                        help="do not record per-kernel events in the timed "
-                             "region (roofline.achieved is then null)")
+    parser.add_argument("--no-others", action="store_true",
+                        help="skip the `workloads` entry (the other "
+                             "configurations)")
+    parser.add_argument("--no-parity", action="store_true",
+                        help="skip the oracle comparison of the measured "
+                             "workloads")
     parser.add_argument("--shrink", type=int, default=1,
-                        help="divide the c5 workload by this power of two "
-                             "(profiling captures only; not a bench value)")
+                        help="divide the c5 / c4 workload by this power of "
+                             "two (profiling captures only; not a bench "
+                             "value)")
     return parser.parse_args()
 
 
@@ -110,7 +119,8 @@ def describe_workload(name, shrink=1):
             f"softmax shrunk {shrink}x (profiling only)"
     if name == "c1":
         offsets = workloads.c1_offsets()
-        return "reduce", "sum", offsets, "canonical 4096 segments U{0..2048}"
+        return "reduce", "sum+max", offsets, \
+            "canonical 4096 segments U{0..2048}, sum and max"
     if name == "c1x256":
         offsets = workloads.c1_offsets(segments=1 << 20)
         return "reduce", "sum", offsets, "canonical x256: 2^20 segments U{0..2048}"
@@ -127,11 +137,32 @@ def describe_workload(name, shrink=1):
 
 
 def make_values(name, offsets, device):
+    """The workload's seeded values, drawn on ``device``."""
     if name == "c3":
         return workloads.c3_values(offsets, device)
     scale = 2.0 if name == "c4" else 1.0
     return workloads.normal_values(int(offsets[-1]), device,
                                    workloads.SEEDS[name[:2]], scale=scale)
+
+
+def vadd_inputs(count, device, rank=0):
+    import torch
+
+    generator = torch.Generator(device=device).manual_seed(
+        workloads.SEEDS["c2"] + rank)
+    x = torch.randn(count, generator=generator, device=device)
+    y = torch.randn(count, generator=generator, device=device)
+    return x, y
+
+
+def algorithmic_bytes(operation, kind, count, segments):
+    if operation == "vadd":
+        return workloads.vadd_bytes(count)
+    if operation == "softmax":
+        return workloads.softmax_bytes(count, segments)
+    if kind == "sum+max":
+        return workloads.reduce_bytes(count, segments) + 4 * segments
+    return workloads.reduce_bytes(count, segments)
 
 
 # ---------------------------------------------------------------------------
@@ -203,10 +234,10 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------
-# reference arm: the CPU path on all host threads
+# the CPU path (reference arm and cpu_baseline)
 # ---------------------------------------------------------------------------
 
-def cpu_sample(name, offsets, limit_elements):
+def cpu_sample(offsets, limit_elements):
     """A prefix of whole segments holding at most ``limit_elements``."""
     if offsets is None:
         return None
@@ -220,7 +251,8 @@ def cpu_pass(operation, kind, values, offsets, threads, block):
 
     start = time.perf_counter()
     if operation == "reduce":
-        oracle.segreduce_f32(values, offsets, kind, threads=threads)
+        for one in kind.split("+"):
+            oracle.segreduce_f32(values, offsets, one, threads=threads)
     elif operation == "softmax":
         oracle.segsoftmax_f32(values, offsets, threads=threads)
     else:
@@ -230,7 +262,25 @@ def cpu_pass(operation, kind, values, offsets, threads, block):
 
 
 def host_inputs(name, operation, offsets, count):
-    """Host arrays with the workload's distribution (numpy, seeded)."""
+    """Host arrays holding the first ``count`` values of the workload.
+
+    The same seeded values as the GPU arm: drawn by the same device generator
+    and copied to the host when a CUDA device is there; a numpy draw with the
+    workload's distribution otherwise (no GPU arm can run then either).
+    """
+    try:
+        import torch
+
+        on_device = torch.cuda.is_available()
+    except Exception:
+        on_device = False
+    if on_device:
+        device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        if operation == "vadd":
+            x, y = vadd_inputs(VADD_COUNT, device)
+            return x[:count].cpu().numpy(), y[:count].cpu().numpy()
+        full = make_values(name, offsets, device)
+        return full[:count].cpu().numpy()
     rng = np.random.default_rng(workloads.SEEDS[name[:2]])
     if operation == "vadd":
         return (rng.standard_normal(count, dtype=np.float32),
@@ -252,24 +302,31 @@ def run_reference(args):
     oracle.build()
     operation, kind, offsets, text = describe_workload(args.workload,
                                                        args.shrink)
-    threads = oracle.max_threads()
-    full_count = int(offsets[-1]) if offsets is not None else (1 << 28) - 37
+    # every core this process may use, whatever OMP_NUM_THREADS a launcher
+    # exported for its ranks
+    threads = oracle.host_threads()
+    full_count = int(offsets[-1]) if offsets is not None else VADD_COUNT
+    everything = host_inputs(args.workload, operation, offsets, full_count)
+
+    def prefix(sample_offsets, count):
+        if operation == "vadd":
+            return everything[0][:count], everything[1][:count]
+        return everything[:count]
+
     # probe the throughput on a small sample, then size the timed sample so
     # that steps + warm-up stay within about two minutes
-    probe_offsets = cpu_sample(args.workload, offsets, 1 << 24)
+    probe_offsets = cpu_sample(offsets, 1 << 24)
     probe_count = int(probe_offsets[-1]) if offsets is not None else 1 << 24
-    probe_values = host_inputs(args.workload, operation, probe_offsets,
-                               probe_count)
+    probe_values = prefix(probe_offsets, probe_count)
     cpu_pass(operation, kind, probe_values, probe_offsets, threads, args.block)
     rate = probe_count / cpu_pass(operation, kind, probe_values,
                                   probe_offsets, threads, args.block)
     seconds_per_step = 120.0 / max(1, args.steps + args.warmup)
     sample_count = int(min(full_count, max(1 << 22, rate * seconds_per_step)))
-    sample_offsets = cpu_sample(args.workload, offsets, sample_count)
+    sample_offsets = cpu_sample(offsets, sample_count)
     if offsets is not None:
         sample_count = int(sample_offsets[-1])
-    values = host_inputs(args.workload, operation, sample_offsets,
-                         sample_count)
+    values = prefix(sample_offsets, sample_count)
     for _ in range(args.warmup):
         cpu_pass(operation, kind, values, sample_offsets, threads, args.block)
     elapsed = 0.0
@@ -286,8 +343,8 @@ def run_reference(args):
         "ms_per_step": 1e3 * elapsed / args.steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {text}",
-                   "device": "host CPU", "sample": sample},
+        "config": workload_config(args, text, operation, kind, offsets),
+        "run": {"device": "host CPU", "sample": sample, "threads": threads},
         "cpu_baseline": {"value": value, "unit": "Gelem/s", "cores": threads,
                          "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "Gelem/s", "h2d_bytes_per_step": 0,
@@ -303,22 +360,433 @@ def metric_name(operation):
             "vadd": "vector_add_throughput"}[operation]
 
 
+def workload_config(args, text, operation, kind, offsets):
+    """The ``config`` object: identical on both arms for one workload."""
+    if offsets is None:
+        elements, segments = VADD_COUNT, 0
+    else:
+        elements, segments = int(offsets[-1]), len(offsets) - 1
+    fits = algorithmic_bytes(operation, kind, elements, segments) < 3e8
+    return {
+        "workload": f"{args.workload}: {text}",
+        "elements_total": elements, "segments_total": segments,
+        "l2": ("inputs fit in L2: the kernel is timed after a 256 MiB write "
+               "(cold); back-to-back steps are L2-warm") if fits
+        else "inputs larger than L2",
+    }
+
+
 # ---------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------
+
+class Problem:
+    """One workload's share on this rank, resident on the device."""
+
+    def __init__(self, name, args, world, rank, device, shrink=1):
+        import torch
+
+        from swage_b200 import multi_gpu
+
+        self.name = name
+        self.args = args
+        self.device = device
+        (self.operation, self.kind, offsets,
+         self.text) = describe_workload(name, shrink)
+        self.full_offsets = offsets
+        self.plan = None
+        self.plan_info = {}
+        self.cuts = None
+        if self.operation == "vadd":
+            total = VADD_COUNT
+            per = -(-total // world)
+            per += (-per) % 32  # 128-byte boundaries between ranks
+            begin = min(total, rank * per)
+            self.count = min(total, begin + per) - begin
+            if world == 1:
+                self.x, self.y = vadd_inputs(self.count, device)
+            else:
+                self.x, self.y = vadd_inputs(self.count, device, rank)
+            self.out = torch.empty(self.count, device=device)
+            self.segments = 0
+            self.total_elements = total
+            self.local_offsets = None
+        else:
+            self.total_elements = int(offsets[-1])
+            host_offsets = torch.from_numpy(offsets)
+            self.cuts = multi_gpu.shard_cuts(host_offsets, world)
+            local, begin, end = multi_gpu.local_shard(host_offsets, self.cuts,
+                                                      rank)
+            self.local_offsets = local.numpy()
+            full = make_values(name, offsets, device)
+            self.values = full[begin:end].clone() if world > 1 else full
+            del full
+            torch.cuda.empty_cache()
+            self.count = end - begin
+            self.segments = len(self.local_offsets) - 1
+            self.device_offsets = torch.from_numpy(
+                self.local_offsets).to(device)
+            if self.operation == "softmax":
+                self.out = torch.empty(self.count, device=device)
+            else:
+                self.out = torch.empty(self.segments, device=device)
+                if self.kind == "sum+max":
+                    self.out2 = torch.empty(self.segments, device=device)
+        self.bytes_per_step = algorithmic_bytes(self.operation, self.kind,
+                                                self.count, self.segments)
+
+    def build_plans(self):
+        """Both planners once, outside every timed region (each twice; the
+        second build is reported: the first also loads the planner's
+        kernels)."""
+        import torch
+
+        from swage_b200 import _native
+        from swage_b200._segmented_qualification import plan_segments
+
+        if self.operation == "vadd" or self.kind == "sum+max":
+            return
+        plan_op = "softmax" if self.operation == "softmax" else "reduce"
+        plans = {}
+        for where, source in (("host", torch.from_numpy(self.local_offsets)),
+                              ("device", self.device_offsets)):
+            for attempt in range(2):
+                if attempt:
+                    plans[where].close()
+                torch.cuda.synchronize()
+                began = time.perf_counter()
+                plans[where] = plan_segments(source, self.count, op=plan_op)
+                torch.cuda.synchronize()
+                self.plan_info[where + "_build_ms"] = (
+                    1e3 * (time.perf_counter() - began))
+        self.plan = plans.pop(self.args.planner)
+        for other in plans.values():
+            other.close()
+        self.plan_info["planner"] = self.args.planner
+        began = time.perf_counter()
+        _native.validate_offsets_device(
+            self.device_offsets.data_ptr(), self.segments, self.count,
+            self.segments, torch.cuda.current_stream().cuda_stream)
+        self.plan_info["validate_on_device_us"] = (
+            1e6 * (time.perf_counter() - began))
+
+    def step(self):
+        """One pass with the inputs where they are and the plan built."""
+        from swage_b200._segmented_qualification import (
+            launch_gpu,
+            launch_softmax_gpu,
+            launch_sum_max_gpu,
+        )
+
+        args = self.args
+        if self.operation == "vadd":
+            add_kernel().launch(
+                arguments={"x_ptr": self.x, "y_ptr": self.y,
+                           "output_ptr": self.out, "n": self.count},
+                constexprs={"BLOCK": args.block},
+                grid=(-(-self.count // args.block),))
+        elif self.kind == "sum+max":
+            launch_sum_max_gpu(self.values, self.device_offsets, self.out,
+                               self.out2,
+                               _validated=(self.count, self.segments))
+        elif self.operation == "reduce":
+            launch_gpu(self.values, self.device_offsets, self.out, self.kind,
+                       args.block, plan=self.plan, schedule=args.schedule,
+                       _validated=(self.count, self.segments))
+        else:
+            launch_softmax_gpu(self.values, self.device_offsets, self.out,
+                               plan=self.plan, schedule=args.schedule,
+                               _validated=(self.count, self.segments))
+
+    def drop_in_call(self):
+        """The call a user makes: validates, finds or builds the plan."""
+        from swage_b200._segmented_qualification import (
+            launch_gpu,
+            launch_softmax_gpu,
+            launch_sum_max_gpu,
+        )
+
+        args = self.args
+        if self.operation == "vadd":
+            self.step()
+        elif self.kind == "sum+max":
+            launch_sum_max_gpu(self.values, self.device_offsets, self.out,
+                               self.out2)
+        elif self.operation == "reduce":
+            launch_gpu(self.values, self.device_offsets, self.out, self.kind,
+                       args.block, schedule=args.schedule)
+        else:
+            launch_softmax_gpu(self.values, self.device_offsets, self.out,
+                               schedule=args.schedule)
+
+    def launches_per_step(self):
+        """Kernels of this library launched by one step."""
+        if self.plan is None:
+            return 1
+        info = self.plan.describe()
+        if self.operation == "softmax":
+            return sum(1 for n in info["softmax_buckets"] if n > 0)
+        schedule = self.args.schedule
+        tiles = (schedule in ("split", "persistent", "resident")
+                 or (schedule == "auto" and info["schedule"] >= 3))
+        return 2 if tiles and info["split_segments"] > 0 else 1
+
+    def parity(self):
+        """The device result of one step against the CPU oracle, full size."""
+        import torch
+
+        import oracle
+
+        self.step()
+        torch.cuda.synchronize()
+        if self.plan is not None:
+            self.plan.check()
+        threads = oracle.host_threads()
+        if self.operation == "vadd":
+            expected = oracle.vadd_f32(self.x.cpu().numpy(),
+                                       self.y.cpu().numpy(), self.count,
+                                       threads=threads)
+            same = np.array_equal(self.out.cpu().numpy().view(np.uint32),
+                                  expected.view(np.uint32))
+            return "bit-exact vs x + y" if same else "MISMATCH"
+        host_values = self.values.cpu().numpy()
+        offsets = self.local_offsets
+        if self.operation == "softmax":
+            got = self.out.cpu().numpy()
+            worst = 0.0
+            first = 0
+            while first < self.segments:
+                last = int(np.searchsorted(
+                    offsets, int(offsets[first]) + (1 << 26),
+                    side="right")) - 1
+                last = min(self.segments, max(last, first + 1))
+                a, b = int(offsets[first]), int(offsets[last])
+                local = (offsets[first:last + 1] - a).astype(np.int32)
+                exact = oracle.segsoftmax_f64(host_values[a:b], local,
+                                              threads=threads)
+                error = np.abs(got[a:b] - exact)
+                if not np.all(error <= 1e-10 + 4e-6 * exact):
+                    return f"MISMATCH in segments {first}..{last}"
+                seen = exact > 1e-30
+                worst = max(worst, float(np.max(error[seen] / exact[seen])))
+                first = last
+            return (f"every segment within 4e-6 relative of fp64 "
+                    f"(worst {worst:.2e})")
+        notes = []
+        if self.kind == "sum+max":
+            outputs = (("sum", self.out), ("max", self.out2))
+        else:
+            outputs = ((self.kind, self.out),)
+        for kind, tensor in outputs:
+            result = tensor.cpu().numpy()
+            if kind == "max":
+                expected = oracle.segreduce_f32(host_values, offsets, "max",
+                                                threads=threads)
+                same = np.array_equal(result.view(np.uint32),
+                                      expected.view(np.uint32))
+                if not same:
+                    return "MISMATCH (max)"
+                notes.append("max bit-exact")
+            else:
+                exact = oracle.segsum_f64(host_values, offsets,
+                                          threads=threads)
+                bound = oracle.sum_tolerance(host_values, offsets)
+                error = np.abs(result - exact)
+                if not np.all(error <= bound):
+                    return "MISMATCH (sum)"
+                nonempty = bound > 0
+                ratio = float(np.max(error[nonempty] / bound[nonempty]))
+                notes.append(f"sum within {ratio:.2g} x bound of fp64")
+        return ", ".join(notes)
+
+    def close(self):
+        if self.plan is not None:
+            self.plan.close()
+            self.plan = None
+
+
+_ADD_KERNEL = []
+
+
+def add_kernel():
+    """The reference's example kernel through the public decorator."""
+    if not _ADD_KERNEL:
+        import swage_b200 as sw
+        import swage_b200.language as sl
+
+        @sw.jit
+        def kernel(x_ptr, y_ptr, output_ptr, n, BLOCK: sl.constexpr):
+            pid = sl.program_id(0)
+            offsets = pid * BLOCK + sl.arange(0, BLOCK)
+            mask = offsets < n
+            x = sl.load(x_ptr + offsets, mask=mask, other=0.0)
+            y = sl.load(y_ptr + offsets, mask=mask, other=0.0)
+            sl.store(output_ptr + offsets, x + y, mask=mask)
+
+        _ADD_KERNEL.append(kernel)
+    return _ADD_KERNEL[0]
+
+
+def timed_steps(step, steps, barrier):
+    """Device time of ``steps`` calls, nothing else on the stream between."""
+    import torch
+
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for _ in range(steps):
+        step()
+    stop.record()
+    barrier()
+    return start.elapsed_time(stop)
+
+
+def dominant_kernel_ms(step, launches):
+    """Mean duration of the dominant kernel over a separate loop in which the
+    library records one pair of events around it per call."""
+    import torch
+
+    from swage_b200 import _native
+
+    torch.cuda.synchronize()
+    _native.profile_start(launches, 1)
+    for _ in range(launches):
+        step()
+    torch.cuda.synchronize()
+    return [float(ms) for ms in _native.profile_stop(launches)]
+
+
+def l2_flusher(device):
+    """Writes a buffer larger than L2 (for workloads that fit in it)."""
+    import torch
+
+    scratch = torch.empty(1 << 28, dtype=torch.uint8, device=device)
+
+    def flush():
+        scratch.fill_(1)
+    return flush
+
+
+def measure(problem, steps, warmup, barrier, peak):
+    """value-style and roofline-style numbers of one resident problem."""
+    import torch
+
+    for _ in range(max(3, warmup)):
+        problem.step()
+    elapsed_ms = timed_steps(problem.step, steps, barrier)
+    fits_l2 = problem.bytes_per_step < 3e8
+    flush = l2_flusher(problem.device) if fits_l2 else None
+    probes = max(5, min(steps, 40))
+    if fits_l2:
+        # cold: a write larger than L2 before every timed launch
+        kernel_ms = []
+        for _ in range(probes):
+            flush()
+            kernel_ms += dominant_kernel_ms(problem.step, 1)
+        warm_ms = dominant_kernel_ms(problem.step, probes)
+    else:
+        kernel_ms = dominant_kernel_ms(problem.step, probes)
+        warm_ms = None
+    del flush
+    torch.cuda.empty_cache()
+    mean_ms = float(np.mean(kernel_ms))
+    achieved = problem.bytes_per_step / (mean_ms * 1e-3) / 1e9
+    result = {
+        "elapsed_ms": elapsed_ms,
+        "ms_per_step": elapsed_ms / steps,
+        "kernel_ms": mean_ms,
+        "kernel_launches_timed": len(kernel_ms),
+        "achieved_gbs": achieved,
+        "frac": achieved / peak,
+        "l2": ("fits in L2: kernel timed after a 256 MiB write (cold); "
+               "back-to-back steps and kernel_warm_ms are L2-warm")
+        if fits_l2 else "inputs larger than L2",
+    }
+    if warm_ms is not None:
+        result["kernel_warm_ms"] = float(np.mean(warm_ms))
+    return result
+
+
+def measure_cold(problem, barrier):
+    """The drop-in call on offsets no cache has seen: validation, planning
+    and launch, inputs resident on the device.  Three different offsets
+    arrays (one boundary moved by one each), wall clock around call + stream
+    synchronisation."""
+    import torch
+
+    if problem.operation == "vadd" or problem.kind == "sum+max":
+        return None
+    keep = problem.device_offsets
+    offsets = problem.local_offsets
+    movable = np.nonzero(offsets[1:-1] > offsets[:-2])[0] + 1
+    if movable.size < 3:
+        return None
+    times = []
+    for pick in (movable[movable.size // 4], movable[movable.size // 2],
+                 movable[3 * movable.size // 4]):
+        changed = offsets.copy()
+        changed[pick] -= 1
+        problem.device_offsets = torch.from_numpy(changed).to(problem.device)
+        barrier()
+        began = time.perf_counter()
+        problem.drop_in_call()
+        torch.cuda.current_stream().synchronize()
+        times.append(1e3 * (time.perf_counter() - began))
+    problem.device_offsets = keep
+    return {"ms": float(np.median(times)), "all_ms": times,
+            "what": "validate + plan + launch through the drop-in call on "
+                    "offsets not seen before, device-resident inputs, wall "
+                    "clock to stream completion"}
+
+
+def measure_e2e(problem, steps, barrier):
+    """The drop-in call with host buffers: H2D of the inputs from pinned
+    memory, the call, D2H of the result, every step."""
+    import torch
+
+    if problem.operation == "vadd":
+        sources = [problem.x.cpu().pin_memory(), problem.y.cpu().pin_memory()]
+        targets = [problem.x, problem.y]
+    else:
+        sources = [problem.values.cpu().pin_memory(),
+                   torch.from_numpy(problem.local_offsets).pin_memory()]
+        targets = [problem.values, problem.device_offsets]
+    results = [problem.out]
+    if problem.kind == "sum+max":
+        results.append(problem.out2)
+    host_results = [torch.empty(r.numel(), dtype=torch.float32).pin_memory()
+                    for r in results]
+    h2d = sum(4 * s.numel() for s in sources)
+    d2h = sum(4 * r.numel() for r in results)
+
+    def step():
+        for target, source in zip(targets, sources):
+            target.copy_(source, non_blocking=True)
+        problem.drop_in_call()
+        for host, result in zip(host_results, results):
+            host.copy_(result, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    step()
+    barrier()
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    start.record()
+    wall = time.perf_counter()
+    for _ in range(steps):
+        step()
+    stop.record()
+    barrier()
+    ms = max(start.elapsed_time(stop), 1e3 * (time.perf_counter() - wall))
+    return ms, h2d, d2h, sources
+
 
 def run_ours(args):
     import torch
     import torch.distributed as dist
 
-    import swage_b200 as sw
-    import swage_b200.language as sl
-    from swage_b200 import _native, multi_gpu
-    from swage_b200._segmented_qualification import (
-        launch_gpu,
-        launch_softmax_gpu,
-        plan_segments,
-    )
+    from swage_b200 import multi_gpu
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -341,204 +809,46 @@ def run_ours(args):
             os.dup2(saved, 1)
             os.close(saved)
 
-    operation, kind, offsets, text = describe_workload(args.workload,
-                                                       args.shrink)
-    peak, peak_source = measured_peak()
-    plan_info = {}
-
-    @sw.jit
-    def add_kernel(x_ptr, y_ptr, output_ptr, n, BLOCK: sl.constexpr):
-        pid = sl.program_id(0)
-        offsets = pid * BLOCK + sl.arange(0, BLOCK)
-        mask = offsets < n
-        x = sl.load(x_ptr + offsets, mask=mask, other=0.0)
-        y = sl.load(y_ptr + offsets, mask=mask, other=0.0)
-        sl.store(output_ptr + offsets, x + y, mask=mask)
-
-    # ---- this rank's share ----
-    if operation == "vadd":
-        total = (1 << 28) - 37
-        per = -(-total // world)
-        per += (-per) % 32  # 128-byte boundaries between ranks
-        begin = min(total, rank * per)
-        count = min(total, begin + per) - begin
-        generator = torch.Generator(device=device).manual_seed(
-            workloads.SEEDS["c2"] + rank)
-        x = torch.randn(count, generator=generator, device=device)
-        y = torch.randn(count, generator=generator, device=device)
-        out = torch.empty(count, device=device)
-        segments = 0
-        bytes_per_step = workloads.vadd_bytes(count)
-        total_elements = total
-        plan = None
-        local_offsets = None
-    else:
-        total_elements = int(offsets[-1])
-        host_offsets = torch.from_numpy(offsets)
-        cuts = multi_gpu.shard_cuts(host_offsets, world)
-        local, begin, end = multi_gpu.local_shard(host_offsets, cuts, rank)
-        local_offsets = local.numpy()
-        full = make_values(args.workload, offsets, device)
-        values = full[begin:end].clone() if world > 1 else full
-        del full
-        torch.cuda.empty_cache()
-        count = end - begin
-        segments = len(local_offsets) - 1
-        device_offsets = torch.from_numpy(local_offsets).to(device)
-        if operation == "reduce":
-            out = torch.empty(segments, device=device)
-            bytes_per_step = workloads.reduce_bytes(count, segments)
-            plan_op = "reduce"
-        else:
-            out = torch.empty(count, device=device)
-            bytes_per_step = workloads.softmax_bytes(count, segments)
-            plan_op = "softmax"
-        # both planners once, outside the timed region: the host walk over a
-        # host copy of the offsets, and the GPU planner over the device copy
-        # (each twice; the second build is reported: the first one also pays
-        # for loading the planner's kernels)
-        plans = {}
-        for where, source in (("host", torch.from_numpy(local_offsets)),
-                              ("device", device_offsets)):
-            for attempt in range(2):
-                if attempt:
-                    plans[where].close()
-                torch.cuda.synchronize()
-                began = time.perf_counter()
-                plans[where] = plan_segments(source, count, op=plan_op)
-                torch.cuda.synchronize()
-                plan_info[where + "_build_ms"] = (
-                    1e3 * (time.perf_counter() - began))
-        plan = plans.pop(args.planner)
-        for other in plans.values():
-            other.close()
-        plan_info["planner"] = args.planner
-        began = time.perf_counter()
-        _native.validate_offsets_device(
-            device_offsets.data_ptr(), segments, count, segments,
-            torch.cuda.current_stream().cuda_stream)
-        plan_info["validate_on_device_us"] = 1e6 * (time.perf_counter() - began)
-    gather = args.allgather and world > 1 and operation == "reduce"
-
-    launches_per_step = [0]
-
-    def step():
-        if operation == "vadd":
-            add_kernel.launch(
-                arguments={"x_ptr": x, "y_ptr": y, "output_ptr": out,
-                           "n": count},
-                constexprs={"BLOCK": args.block},
-                grid=(-(-count // args.block),))
-        elif operation == "reduce":
-            launch_gpu(values, device_offsets, out, kind, args.block,
-                       plan=plan, schedule=args.schedule,
-                       _validated=(count, segments))
-            if gather:
-                multi_gpu.gather_results(out, cuts)
-        else:
-            launch_softmax_gpu(values, device_offsets, out, plan=plan,
-                               schedule=args.schedule,
-                               _validated=(count, segments))
-
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(value):
+        if world == 1:
+            return float(value)
+        cell = torch.tensor([value], device=device, dtype=torch.float64)
+        dist.all_reduce(cell, op=dist.ReduceOp.MAX)
+        return float(cell.item())
+
+    peak, peak_source = measured_peak()
+    problem = Problem(args.workload, args, world, rank, device, args.shrink)
+    problem.build_plans()
+    gather = (args.allgather and world > 1 and problem.operation == "reduce"
+              and problem.kind != "sum+max")
+    if gather:
+        plain_step = problem.step
+
+        def step_with_gather():
+            plain_step()
+            multi_gpu.gather_results(problem.out, problem.cuts)
+        problem.step = step_with_gather
+
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    # the dominant kernel of every probe_stride-th step is timed with its own
-    # pair of events; a sparse sample keeps the event records (about 5 us of
-    # stream time per pair) from inflating the step time
-    probe_stride = 8 if args.steps >= 64 else 1
-    if not args.no_probe:
-        _native.profile_start(args.steps, probe_stride)
-    start = torch.cuda.Event(enable_timing=True)
-    stop = torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(args.steps):
-        step()
-    stop.record()
-    barrier()
-    elapsed_ms = start.elapsed_time(stop)
-    kernel_ms = [] if args.no_probe else _native.profile_stop(args.steps)
-    if plan is not None:
-        plan.check()
-    times = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms = float(times.item())
-
-    # kernels per step: planned reduce = tile kernel + combine pass (when any
-    # segment is split); everything else = one kernel
-    per_step = 1
-    if plan is not None and operation == "reduce":
-        info = plan.describe()
-        uses_tiles = (args.schedule in ("split", "persistent")
-                      or (args.schedule == "auto" and info["schedule"] >= 3))
-        if uses_tiles and info["split_segments"] > 0:
-            per_step = 2
-    if plan is not None and operation == "softmax":
-        info = plan.describe()
-        per_step = sum(1 for n in info["softmax_buckets"] if n > 0)
-    launches_per_step[0] = per_step
-
-    # ---- end to end through the public call, host buffers ----
+    numbers = measure(problem, args.steps, args.warmup, barrier, peak)
+    elapsed_ms = max_over_ranks(numbers["elapsed_ms"])
+    if problem.plan is not None:
+        problem.plan.check()
+    cold = measure_cold(problem, barrier)
     e2e_steps = args.e2e_steps or max(1, min(args.steps, 5))
-    if operation == "vadd":
-        host_inputs_ = [x.cpu().pin_memory(), y.cpu().pin_memory()]
-        host_out = torch.empty(count, dtype=torch.float32).pin_memory()
-        h2d = 8 * count
-        d2h = 4 * count
-    else:
-        host_inputs_ = [values.cpu().pin_memory(),
-                        torch.from_numpy(local_offsets).pin_memory()]
-        host_out = torch.empty(out.numel(), dtype=torch.float32).pin_memory()
-        h2d = 4 * count + 4 * (segments + 1)
-        d2h = 4 * out.numel()
-
-    def e2e_step():
-        if operation == "vadd":
-            x.copy_(host_inputs_[0], non_blocking=True)
-            y.copy_(host_inputs_[1], non_blocking=True)
-            add_kernel.launch(
-                arguments={"x_ptr": x, "y_ptr": y, "output_ptr": out,
-                           "n": count},
-                constexprs={"BLOCK": args.block},
-                grid=(-(-count // args.block),))
-        else:
-            values.copy_(host_inputs_[0], non_blocking=True)
-            device_offsets.copy_(host_inputs_[1], non_blocking=True)
-            if operation == "reduce":
-                # the drop-in call: validates the offsets, finds the plan
-                launch_gpu(values, device_offsets, out, kind, args.block,
-                           schedule=args.schedule)
-            else:
-                launch_softmax_gpu(values, device_offsets, out,
-                                   schedule=args.schedule)
-        host_out.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    e2e_step()
-    barrier()
-    e2e_start = torch.cuda.Event(enable_timing=True)
-    e2e_stop = torch.cuda.Event(enable_timing=True)
-    e2e_start.record()
-    wall = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e2e_stop.record()
-    barrier()
-    e2e_ms = max(e2e_start.elapsed_time(e2e_stop),
-                 1e3 * (time.perf_counter() - wall))
-    times = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    e2e_ms = float(times.item())
+    e2e_ms, h2d, d2h, host_sources = measure_e2e(problem, e2e_steps, barrier)
+    h2d_rank_gbs = h2d * e2e_steps / (e2e_ms * 1e-3) / 1e9
+    e2e_ms = max_over_ranks(e2e_ms)
     clocks = sampler.stop() if sampler is not None else None
+    parity = None
+    if world == 1 and not args.no_parity and args.shrink == 1:
+        parity = problem.parity()
 
     # ---- CPU baseline on this host (rank 0, single GPU runs only) ----
     cpu = None
@@ -546,85 +856,137 @@ def run_ours(args):
         import oracle
 
         oracle.build()
-        threads = oracle.max_threads()
-        if operation == "vadd":
+        threads = oracle.host_threads()
+        if problem.operation == "vadd":
             sample_offsets = None
-            sample_values = (host_inputs_[0].numpy(), host_inputs_[1].numpy())
-            sample_count = count
+            sample_values = (host_sources[0].numpy(), host_sources[1].numpy())
+            sample_count = problem.count
         else:
             # bounded sample: a prefix of whole segments, at most 2**29 values
-            sample_offsets = cpu_sample(args.workload, local_offsets, 1 << 29)
+            sample_offsets = cpu_sample(problem.local_offsets, 1 << 29)
             sample_count = int(sample_offsets[-1])
-            sample_values = host_inputs_[0].numpy()[:sample_count]
-        single = cpu_pass(operation, kind, sample_values, sample_offsets, 1,
-                          args.block)
-        cpu_pass(operation, kind, sample_values, sample_offsets, threads,
-                 args.block)
+            sample_values = host_sources[0].numpy()[:sample_count]
+        single = cpu_pass(problem.operation, problem.kind, sample_values,
+                          sample_offsets, 1, args.block)
+        cpu_pass(problem.operation, problem.kind, sample_values,
+                 sample_offsets, threads, args.block)
         parallel = min(
-            cpu_pass(operation, kind, sample_values, sample_offsets, threads,
-                     args.block) for _ in range(3))
+            cpu_pass(problem.operation, problem.kind, sample_values,
+                     sample_offsets, threads, args.block) for _ in range(3))
         cpu = {
             "value": sample_count / parallel / 1e9, "unit": "Gelem/s",
             "cores": threads, "kind": "port",
-            "sample": f"{sample_count} of {count} elements, best of 3",
+            "sample": f"{sample_count} of {problem.count} elements, "
+                      "best of 3",
             "single_thread_value": sample_count / single / 1e9,
         }
+    del host_sources
+    launches = problem.launches_per_step()
+    summary = {
+        "operation": problem.operation, "kind": problem.kind,
+        "count": problem.count, "segments": problem.segments,
+        "bytes_per_step": problem.bytes_per_step,
+        "total_elements": problem.total_elements, "text": problem.text,
+        "plan_info": problem.plan_info,
+        "config": workload_config(args, problem.text, problem.operation,
+                                  problem.kind, problem.full_offsets),
+    }
+    problem.close()
+    del problem
+    torch.cuda.empty_cache()
+
+    # ---- the other configurations, same process, 1 GPU only ----
+    others = None
+    if world == 1 and not args.no_others and args.shrink == 1:
+        others = {}
+        for name in ALL_WORKLOADS:
+            if name == args.workload:
+                continue
+            other = Problem(name, args, 1, 0, device)
+            other.build_plans()
+            got = measure(other, min(args.steps, 50), 3, barrier, peak)
+            entry = {
+                "what": other.text,
+                "kernel_us": 1e3 * got["kernel_ms"],
+                "kernel_gbs": got["achieved_gbs"],
+                "frac_of_measured_copy": got["frac"],
+                "pct_of_8tbs": 100.0 * got["achieved_gbs"] / NOMINAL_HBM_GBS,
+                "step_us": 1e3 * got["ms_per_step"],
+                "step_gelems": other.total_elements
+                / (got["ms_per_step"] * 1e-3) / 1e9,
+                "l2": got["l2"],
+                "schedule": (other.plan.describe()["schedule"]
+                             if other.plan is not None else None),
+            }
+            if "kernel_warm_ms" in got:
+                entry["kernel_warm_us"] = 1e3 * got["kernel_warm_ms"]
+            if not args.no_parity:
+                entry["parity"] = other.parity()
+            others[name] = entry
+            other.close()
+            del other
+            torch.cuda.empty_cache()
 
     if rank == 0:
         ms_per_step = elapsed_ms / args.steps
-        gelems = total_elements / (ms_per_step * 1e-3) / 1e9
-        kernel_avg_ms = float(np.mean(kernel_ms)) if kernel_ms else None
-        achieved = (bytes_per_step / (kernel_avg_ms * 1e-3) / 1e9
-                    if kernel_avg_ms else None)
+        total = summary["total_elements"]
+        bytes_per_step = summary["bytes_per_step"]
+        gelems = total / (ms_per_step * 1e-3) / 1e9
+        achieved = numbers["achieved_gbs"]
         step_gbs = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+        name = args.workload
         line = {
-            "metric": metric_name(operation), "value": gelems,
+            "metric": metric_name(summary["operation"]), "value": gelems,
             "unit": "Gelem/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {
-                "workload": f"{args.workload}: {text}",
-                "elements_total": total_elements,
-                "elements_rank0": count, "segments_rank0": segments,
+            "config": summary["config"],
+            "run": {
+                "device": "B200", "sample": "whole workload",
+                "elements_rank0": summary["count"],
+                "segments_rank0": summary["segments"],
                 "schedule": args.schedule,
                 "sharding": f"{world} element-balanced contiguous segment "
                             "ranges, no collective"
                             + (" + NCCL all-gather of results"
                                if gather else ""),
-                "l2": "inputs larger than L2" if bytes_per_step > 3e8
-                      else "inputs fit in L2 (warm)",
-            },
+                "l2": numbers["l2"]},
             "hbm_gbs_per_gpu": step_gbs,
             "pct_of_8tbs_per_gpu": 100.0 * step_gbs / NOMINAL_HBM_GBS,
             "clocks": clocks,
-            "e2e": {"value": total_elements / (e2e_ms / e2e_steps * 1e-3) / 1e9,
+            "e2e": {"value": total / (e2e_ms / e2e_steps * 1e-3) / 1e9,
                     "unit": "Gelem/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                    "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": args.steps * launches_per_step[0],
+                    "ms_per_step": e2e_ms / e2e_steps,
+                    "h2d_gbs_rank0": h2d_rank_gbs},
+            "gpu_launches": args.steps * launches,
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak,
-                "unit": "GB/s",
-                "frac": achieved / peak if achieved else None,
-                "traffic": (TRAFFIC_RATIO[args.workload] * bytes_per_step
-                            if args.workload in TRAFFIC_RATIO
-                            and args.shrink == 1 else None),
-                "traffic_source": "ncu capture, scaled by algorithmic bytes"
-                if args.workload in TRAFFIC_RATIO else None,
+                "unit": "GB/s", "frac": achieved / peak,
+                "traffic": (TRAFFIC_RATIO[name] * bytes_per_step
+                            if name in TRAFFIC_RATIO and args.shrink == 1
+                            else None),
+                "traffic_source": "ncu capture of a shrunk case, scaled by "
+                                  "algorithmic bytes"
+                if name in TRAFFIC_RATIO else None,
                 "peak_source": peak_source,
-                "kernel_ms": kernel_avg_ms,
-                "kernel_launches_timed": len(kernel_ms),
+                "kernel_ms": numbers["kernel_ms"],
+                "kernel_launches_timed": numbers["kernel_launches_timed"],
+                "timed_in": "a separate loop after the value region",
                 "algorithmic_bytes_per_launch": bytes_per_step,
-                "pct_of_8tbs": 100.0 * achieved / NOMINAL_HBM_GBS
-                if achieved else None,
+                "pct_of_8tbs": 100.0 * achieved / NOMINAL_HBM_GBS,
             },
+            "cold": cold,
+            "parity": parity,
             "cpu_baseline": cpu,
-            "plan": plan_info or None,
+            "plan": summary["plan_info"] or None,
+            "workloads": others,
         }
+        if cold is not None:
+            cold["warm_ms"] = ms_per_step
+            cold["cold_over_warm"] = cold["ms"] / ms_per_step
         print(json.dumps(line))
-    if plan is not None:
-        plan.close()
     if world > 1:
         dist.destroy_process_group()
 

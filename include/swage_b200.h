@@ -177,6 +177,21 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
                       const swg_plan *plan, int schedule, int32_t block_hint,
                       void *stream);
 
+/* Sum AND max of every segment in one pass over the values:
+ * out_sum[s] = swg_segreduce_f32(SWG_KIND_SUM)[s] to the documented tolerance,
+ * out_max[s] = swg_segreduce_f32(SWG_KIND_MAX)[s] bit for bit, for
+ * 0 <= s < segment_count; each value is read once and the call is one kernel
+ * launch.  Plan-free (a warp or a CTA per segment, chosen by the mean length):
+ * meant for inputs of moderate size such as the canonical 4096-segment
+ * configuration, where two separate launches cost more than the data.  This
+ * entry point has no counterpart in the reference, which runs the two kinds
+ * as two kernels; identities and combiners are those of
+ * lib/Conversion/SegmentedReduction/SegmentedReduction.cpp:156-161, 236-267. */
+int swg_segreduce_sum_max_f32(const float *values, const int32_t *offsets,
+                              float *out_sum, float *out_max,
+                              int32_t value_count, int32_t segment_count,
+                              void *stream);
+
 /* Same result as swg_segreduce_f32 with a plan and SWG_SCHED_SPLIT, for
  * callers that must not allocate device memory: code running inside a
  * framework whose memory pool already owns the GPU's memory, a serving loop

@@ -91,6 +91,21 @@ def max_threads():
     return int(_load().swg_oracle_max_threads())
 
 
+def host_threads():
+    """Host cores this process may run on.
+
+    Unlike ``max_threads`` this ignores ``OMP_NUM_THREADS``, which launchers
+    such as ``torch.distributed.run`` set to 1 for every rank: the timed CPU
+    baseline asks for the cores the machine really offers.
+    """
+    import os
+
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        return max(1, os.cpu_count() or 1)
+
+
 def _f32(array):
     array = np.ascontiguousarray(array, dtype=np.float32)
     return array, array.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
@@ -250,7 +265,7 @@ def cpu_oracle(values, offsets, kind):
 
 
 __all__ = [
-    "build", "cpu_oracle", "max_threads", "py_segreduce", "segabsmax_f64",
+    "build", "cpu_oracle", "host_threads", "max_threads", "py_segreduce", "segabsmax_f64",
     "segreduce_f32", "segsoftmax_f32", "segsoftmax_f64", "segsum_f64",
     "sum_tolerance", "vadd_f32",
 ]

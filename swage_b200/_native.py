@@ -43,6 +43,7 @@ EXPORTS = (
     "swg_segsoftmax_f32", "swg_shard_offsets", "swg_profile_start",
     "swg_profile_stop", "swg_segreduce_f32_noalloc",
     "swg_validate_offsets_device", "swg_plan_create_device",
+    "swg_segreduce_sum_max_f32",
 )
 
 _lock = threading.Lock()
@@ -85,6 +86,9 @@ def _declare(lib):
         ptr, ptr, ptr, c_i32, c_i32, ptr, c_int, ptr]
     lib.swg_shard_offsets.restype = c_int
     lib.swg_shard_offsets.argtypes = [ptr, c_i32, c_i32, ptr]
+    lib.swg_segreduce_sum_max_f32.restype = c_int
+    lib.swg_segreduce_sum_max_f32.argtypes = [
+        ptr, ptr, ptr, ptr, c_i32, c_i32, ptr]
     lib.swg_segreduce_f32_noalloc.restype = c_int
     lib.swg_segreduce_f32_noalloc.argtypes = [
         c_int, ptr, ptr, ptr, c_i32, c_i32, ptr]
@@ -141,6 +145,17 @@ def segreduce(kind, values_ptr, offsets_ptr, out_ptr, value_count,
             kind, values_ptr, offsets_ptr, out_ptr, value_count,
             segment_count, plan_handle, schedule, block, stream),
         "swg_segreduce_f32",
+    )
+
+
+def segreduce_sum_max(values_ptr, offsets_ptr, sum_ptr, max_ptr, value_count,
+                      segment_count, stream):
+    """Sum and max of every segment in one pass (one launch, no plan)."""
+    check(
+        library().swg_segreduce_sum_max_f32(
+            values_ptr, offsets_ptr, sum_ptr, max_ptr, value_count,
+            segment_count, stream),
+        "swg_segreduce_sum_max_f32",
     )
 
 

@@ -531,6 +531,55 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
     return None
 
 
+def launch_sum_max_gpu(values, offsets, sum_output, max_output, *,
+                       _validated=None):
+    """Queue the segmented sum AND max of one input as a single kernel.
+
+    ``sum_output[s]`` and ``max_output[s]`` are what two ``launch_gpu`` calls
+    with ``"sum"`` and ``"max"`` give (max bit for bit, sum to the documented
+    tolerance), but every value is read once.  Plan-free: meant for inputs of
+    moderate size such as the canonical 4096-segment configuration.  The
+    reference runs the two kinds as two launches
+    (``_segmented_qualification.py:120-172``); the validation is its own,
+    applied to both outputs.
+    """
+    torch = _runtime._import_torch()
+    if _validated is None:
+        value_count, segment_count = _validate_tensors(values, offsets,
+                                                       sum_output)
+        _last_host_offsets.value = None
+        _last_digest.value = None
+        if (not isinstance(max_output, torch.Tensor)
+                or max_output.dtype != torch.float32):
+            raise TypeError("output must have dtype torch.float32")
+        if max_output.dim() != 1:
+            raise TypeError("output must have rank one")
+        if not max_output.is_contiguous():
+            raise ValueError("output must be contiguous")
+        if max_output.numel() < segment_count:
+            raise ValueError(
+                f"output has {max_output.numel()} elements for "
+                f"{segment_count} segments")
+        if max_output.device != sum_output.device:
+            raise ValueError("output must be on the current CUDA device")
+    else:
+        value_count, segment_count = _validated
+    if segment_count == 0:
+        return None
+    if sum_output.data_ptr() == max_output.data_ptr():
+        raise ValueError("the two outputs must not alias")
+
+    from . import _native
+
+    stream = torch.cuda.current_stream()
+    _native.segreduce_sum_max(
+        values.data_ptr(), offsets.data_ptr(), sum_output.data_ptr(),
+        max_output.data_ptr(), value_count, segment_count, stream.cuda_stream)
+    for tensor in (values, offsets, sum_output, max_output):
+        tensor.record_stream(stream)
+    return None
+
+
 def launch_softmax_gpu(values, offsets, output, *, plan=None, schedule="auto",
                        _validated=None):
     """Queue one segmented softmax on the current PyTorch stream.
@@ -579,5 +628,5 @@ def launch_softmax_gpu(values, offsets, output, *, plan=None, schedule="auto",
 
 __all__ = [
     "SegmentPlan", "clear_plan_cache", "launch_gpu", "launch_softmax_gpu",
-    "plan_segments",
+    "launch_sum_max_gpu", "plan_segments",
 ]

@@ -394,14 +394,27 @@ int swg_plan_status(swg_plan *plan) {
     swg::set_error("swg_plan_status: plan is null");
     return SWG_ERR_INVALID_ARGUMENT;
   }
-  cudaError_t e = cudaDeviceSynchronize();
-  if (e != cudaSuccess) return cuda_failure("cudaDeviceSynchronize", e);
+  // the plan's own device, whichever one is current on this thread
+  int previous = -1;
+  const int owner = plan->dev.device;
+  cudaGetDevice(&previous);
+  const bool switched = owner >= 0 && previous != owner;
+  if (switched) cudaSetDevice(owner);
   uint32_t control[4] = {0, 0, 0, 0};
-  e = cudaMemcpy(control, plan->dev.control, sizeof(control),
-                 cudaMemcpyDeviceToHost);
-  if (e != cudaSuccess) return cuda_failure("cudaMemcpy", e);
-  if (control[2] != 0) {
+  cudaError_t e = cudaDeviceSynchronize();
+  const char *failed = "cudaDeviceSynchronize";
+  if (e == cudaSuccess) {
+    e = cudaMemcpy(control, plan->dev.control, sizeof(control),
+                   cudaMemcpyDeviceToHost);
+    failed = "cudaMemcpy";
+  }
+  // an error leaves the ticket and finished counters of the persistent
+  // schedule wherever the kernel stopped: start the next launch from zero
+  if (e == cudaSuccess && control[2] != 0)
     cudaMemset(plan->dev.control, 0, sizeof(control));
+  if (switched && previous >= 0) cudaSetDevice(previous);
+  if (e != cudaSuccess) return cuda_failure(failed, e);
+  if (control[2] != 0) {
     const char *what = control[2] == 1 ? "a bounded device-side wait gave up"
                        : control[2] == 2
                            ? "a task of the plan does not fit the launch's "
@@ -486,6 +499,34 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
       break;
   }
   if (e != cudaSuccess) return cuda_failure("segmented reduce launch", e);
+  return SWG_OK;
+}
+
+int swg_segreduce_sum_max_f32(const float *values, const int32_t *offsets,
+                              float *out_sum, float *out_max,
+                              int32_t value_count, int32_t segment_count,
+                              void *stream) {
+  swg::clear_error();
+  if (value_count < 0 || segment_count < 0) {
+    swg::set_error("swg_segreduce_sum_max_f32: negative count");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  if (segment_count == 0) return SWG_OK;
+  if (!offsets || !out_sum || !out_max || (!values && value_count > 0)) {
+    swg::set_error("swg_segreduce_sum_max_f32: null pointer");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  if (out_sum == out_max) {
+    swg::set_error("swg_segreduce_sum_max_f32: the two outputs must differ");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  int device = 0, sm_count = 0;
+  const int status = current_device(&device, &sm_count);
+  if (status != SWG_OK) return status;
+  const cudaError_t e = swg::launch_segreduce_sum_max(
+      values, offsets, out_sum, out_max, value_count, segment_count, sm_count,
+      (cudaStream_t)stream, next_probe());
+  if (e != cudaSuccess) return cuda_failure("fused sum + max launch", e);
   return SWG_OK;
 }
 

@@ -103,38 +103,94 @@ __device__ __forceinline__ int head_elems(const float *p) {
 
 // One thread's share of reduce(v[begin, end)) when `nthreads` threads with
 // ranks 0..nthreads-1 stride over the range: scalar head up to the first
-// 16-byte boundary, float4 body (four independent accumulators), scalar tail.
-template <class Op>
+// 16-byte boundary, float4 body with kInFlight independent 128-bit loads
+// issued before any of them is used (four accumulators), scalar tail.
+template <class Op, int kInFlight = 4>
 __device__ __forceinline__ float strided_partial(const float *__restrict__ v,
                                                  int64_t begin, int64_t end,
                                                  int rank, int nthreads) {
-  float acc = Op::identity();
+  static_assert(kInFlight % 4 == 0, "loads in flight: a multiple of four");
+  float acc[4] = {Op::identity(), Op::identity(), Op::identity(),
+                  Op::identity()};
   const float *p = v + begin;
-  int64_t len = end - begin;
-  if (len <= 0) return acc;
+  const int len = (int)(end - begin);  // one segment: < 2^31
+  if (len <= 0) return acc[0];
   int head = head_elems(p);
-  if (head > len) head = (int)len;
-  if (rank < head) acc = Op::apply(acc, ld_stream(p + rank));
+  if (head > len) head = len;
+  if (rank < head) acc[0] = Op::apply(acc[0], ld_stream(p + rank));
   const float4 *body = reinterpret_cast<const float4 *>(p + head);
-  int64_t nvec = (len - head) >> 2;
-  float a1 = Op::identity(), a2 = Op::identity(), a3 = Op::identity();
-  int64_t i = rank;
-  for (; i + 3 * (int64_t)nthreads < nvec; i += 4 * (int64_t)nthreads) {
-    float4 q0 = ld_stream4(body + i);
-    float4 q1 = ld_stream4(body + i + nthreads);
-    float4 q2 = ld_stream4(body + i + 2 * (int64_t)nthreads);
-    float4 q3 = ld_stream4(body + i + 3 * (int64_t)nthreads);
-    acc = fold4<Op>(acc, q0);
-    a1 = fold4<Op>(a1, q1);
-    a2 = fold4<Op>(a2, q2);
-    a3 = fold4<Op>(a3, q3);
+  const int nvec = (len - head) >> 2;
+  int i = rank;
+  for (; i < nvec; i += kInFlight * nthreads) {
+    // (the loads of a last, partial batch are predicated off)
+    float4 q[kInFlight];
+#pragma unroll
+    for (int k = 0; k < kInFlight; ++k)
+      if (i + k * nthreads < nvec)
+        q[k] = ld_stream4(body + i + k * nthreads);
+#pragma unroll
+    for (int k = 0; k < kInFlight; ++k)
+      if (i + k * nthreads < nvec)
+        acc[k & 3] = fold4<Op>(acc[k & 3], q[k]);
   }
-  for (; i < nvec; i += nthreads) acc = fold4<Op>(acc, ld_stream4(body + i));
-  acc = Op::apply(Op::apply(acc, a1), Op::apply(a2, a3));
-  int64_t tail = head + (nvec << 2);
-  int rem = (int)(len - tail);
-  if (rank < rem) acc = Op::apply(acc, ld_stream(p + tail + rank));
-  return acc;
+  float r = Op::apply(Op::apply(acc[0], acc[1]), Op::apply(acc[2], acc[3]));
+  const int tail = head + (nvec << 2);
+  const int rem = len - tail;
+  if (rank < rem) r = Op::apply(r, ld_stream(p + tail + rank));
+  return r;
+}
+
+// Sum and maximum of the same range in one pass over it: every value is
+// loaded once and folded into both accumulators.
+struct SumMax {
+  float sum, max;
+};
+
+template <int kInFlight>
+__device__ __forceinline__ SumMax strided_sum_max(const float *__restrict__ v,
+                                                  int64_t begin, int64_t end,
+                                                  int rank, int nthreads) {
+  static_assert(kInFlight % 4 == 0, "loads in flight: a multiple of four");
+  float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  float m[4] = {MaxOp::identity(), MaxOp::identity(), MaxOp::identity(),
+                MaxOp::identity()};
+  const float *p = v + begin;
+  const int len = (int)(end - begin);  // one segment: < 2^31
+  if (len <= 0) return SumMax{s[0], m[0]};
+  int head = head_elems(p);
+  if (head > len) head = len;
+  if (rank < head) {
+    const float x = ld_stream(p + rank);
+    s[0] = SumOp::apply(s[0], x);
+    m[0] = MaxOp::apply(m[0], x);
+  }
+  const float4 *body = reinterpret_cast<const float4 *>(p + head);
+  const int nvec = (len - head) >> 2;
+  int i = rank;
+  for (; i < nvec; i += kInFlight * nthreads) {
+    float4 q[kInFlight];
+#pragma unroll
+    for (int k = 0; k < kInFlight; ++k)
+      if (i + k * nthreads < nvec)
+        q[k] = ld_stream4(body + i + k * nthreads);
+#pragma unroll
+    for (int k = 0; k < kInFlight; ++k)
+      if (i + k * nthreads < nvec) {
+        s[k & 3] = fold4<SumOp>(s[k & 3], q[k]);
+        m[k & 3] = fold4<MaxOp>(m[k & 3], q[k]);
+      }
+  }
+  SumMax r;
+  r.sum = SumOp::apply(SumOp::apply(s[0], s[1]), SumOp::apply(s[2], s[3]));
+  r.max = MaxOp::apply(MaxOp::apply(m[0], m[1]), MaxOp::apply(m[2], m[3]));
+  const int tail = head + (nvec << 2);
+  const int rem = len - tail;
+  if (rank < rem) {
+    const float x = ld_stream(p + tail + rank);
+    r.sum = SumOp::apply(r.sum, x);
+    r.max = MaxOp::apply(r.max, x);
+  }
+  return r;
 }
 
 // ---------------------------------------------------------------------------
@@ -201,6 +257,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
       if (mbar_try_wait(bar, parity)) return true;
     if (global_timer_ns() > deadline) return false;
   }
+}
+
+// Orders this thread's earlier generic-proxy accesses to shared memory (and
+// those of other threads it has synchronised with) before the async-proxy
+// writes of the bulk copies it issues next: the architected fence for handing
+// a stage that has just been read back to the copy engine.
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
 // global -> shared bulk copy, completion counted in bytes on `bar`.  Both

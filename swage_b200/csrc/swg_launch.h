@@ -58,6 +58,12 @@ cudaError_t launch_segreduce_cta(int kind, const float *values,
                                  int32_t segment_count, int32_t block,
                                  int sm_count, cudaStream_t stream,
                                  const Probe *probe);
+// Sum and max of every segment in one pass (no plan).
+cudaError_t launch_segreduce_sum_max(const float *values,
+                                     const int32_t *offsets, float *out_sum,
+                                     float *out_max, int32_t value_count,
+                                     int32_t segment_count, int sm_count,
+                                     cudaStream_t stream, const Probe *probe);
 // One tile task per CTA + combine pass.
 cudaError_t launch_segreduce_split(int kind, const float *values, float *out,
                                    int32_t value_count, const DevicePlan &plan,

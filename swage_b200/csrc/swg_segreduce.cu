@@ -31,7 +31,7 @@ namespace swg {
 constexpr int kWarpKernelThreads = 256;
 
 template <class Op>
-__global__ void __launch_bounds__(kWarpKernelThreads)
+__global__ void __launch_bounds__(kWarpKernelThreads, 4)
 segreduce_warp_kernel(const float *__restrict__ values,
                       const int32_t *__restrict__ offsets,
                       float *__restrict__ out, int32_t segment_count) {
@@ -42,9 +42,55 @@ segreduce_warp_kernel(const float *__restrict__ values,
   for (int64_t seg = warp; seg < segment_count; seg += nwarps) {
     const int64_t begin = __ldg(offsets + seg);
     const int64_t end = __ldg(offsets + seg + 1);
-    float acc = strided_partial<Op>(values, begin, end, lane, kWarp);
+    // eight 128-bit loads per lane are issued before the first is used: a
+    // segment of up to 1024 values is one round trip to memory
+    float acc = strided_partial<Op, 8>(values, begin, end, lane, kWarp);
     acc = warp_reduce<Op>(acc);
     if (lane == 0) out[seg] = acc;
+  }
+}
+
+// Sum AND max of every segment in one pass over the values (one launch, each
+// value read once, two outputs per segment): the canonical configuration asks
+// for both reductions of the same input.  Identities and combiners are those
+// of the two single kernels (SegmentedReduction.cpp:156-161, 236-241,
+// 256-258).  kCta = false: one warp per segment; true: one CTA per segment.
+template <bool kCta>
+__global__ void __launch_bounds__(kWarpKernelThreads, 4)
+segreduce_sum_max_kernel(const float *__restrict__ values,
+                         const int32_t *__restrict__ offsets,
+                         float *__restrict__ out_sum,
+                         float *__restrict__ out_max, int32_t segment_count) {
+  __shared__ float scratch[32];
+  const int lane = threadIdx.x & 31;
+  if (kCta) {
+    for (int64_t seg = blockIdx.x; seg < segment_count; seg += gridDim.x) {
+      const int64_t begin = __ldg(offsets + seg);
+      const int64_t end = __ldg(offsets + seg + 1);
+      const SumMax r = strided_sum_max<8>(values, begin, end, threadIdx.x,
+                                          kWarpKernelThreads);
+      const float sum = cta_reduce<SumOp>(r.sum, scratch);
+      const float max = cta_reduce<MaxOp>(r.max, scratch);
+      if (threadIdx.x == 0) {
+        out_sum[seg] = sum;
+        out_max[seg] = max;
+      }
+    }
+    return;
+  }
+  const int64_t warp =
+      ((int64_t)blockIdx.x * kWarpKernelThreads + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * kWarpKernelThreads) >> 5;
+  for (int64_t seg = warp; seg < segment_count; seg += nwarps) {
+    const int64_t begin = __ldg(offsets + seg);
+    const int64_t end = __ldg(offsets + seg + 1);
+    const SumMax r = strided_sum_max<8>(values, begin, end, lane, kWarp);
+    const float sum = warp_reduce<SumOp>(r.sum);
+    const float max = warp_reduce<MaxOp>(r.max);
+    if (lane == 0) {
+      out_sum[seg] = sum;
+      out_max[seg] = max;
+    }
   }
 }
 
@@ -222,6 +268,9 @@ __device__ __forceinline__ void issue_task(const Task &task,
     const int32_t o_hi = (task.seg + task.count + 1 + 3) & ~3;
     bytes_o = (uint32_t)(o_hi - o_lo) * 4u;
   }
+  // the stage may have been read a moment ago (generic proxy); the copies
+  // below write it through the async proxy
+  fence_proxy_async();
   mbar_arrive_expect_tx(full, bytes_v + bytes_o);
   if (bytes_v) bulk_g2s(stage.tile + (lo - origin), values + lo, bytes_v, full);
   if (bytes_o)
@@ -783,6 +832,31 @@ cudaError_t launch_segreduce_warp(int kind, const float *values,
             values, offsets, out, segment_count);
     return cudaGetLastError();
   });
+  probe_end(probe, stream);
+  return e;
+}
+
+cudaError_t launch_segreduce_sum_max(const float *values,
+                                     const int32_t *offsets, float *out_sum,
+                                     float *out_max, int32_t value_count,
+                                     int32_t segment_count, int sm_count,
+                                     cudaStream_t stream, const Probe *probe) {
+  // long segments on average: a CTA each; else a warp each
+  const bool cta = (int64_t)value_count >= (int64_t)segment_count * 2048;
+  const int per_cta = cta ? 1 : kWarpKernelThreads / 32;
+  int64_t grid = ((int64_t)segment_count + per_cta - 1) / per_cta;
+  const int64_t cap = (int64_t)sm_count * 8 * 4;
+  if (grid > cap) grid = cap;
+  probe_begin(probe, stream);
+  if (cta)
+    segreduce_sum_max_kernel<true>
+        <<<(unsigned)grid, kWarpKernelThreads, 0, stream>>>(
+            values, offsets, out_sum, out_max, segment_count);
+  else
+    segreduce_sum_max_kernel<false>
+        <<<(unsigned)grid, kWarpKernelThreads, 0, stream>>>(
+            values, offsets, out_sum, out_max, segment_count);
+  const cudaError_t e = cudaGetLastError();
   probe_end(probe, stream);
   return e;
 }

@@ -357,6 +357,9 @@ __device__ __forceinline__ void ring_issue(const RingSegment &g,
                                            uint64_t *full, int c,
                                            uint64_t policy) {
   const int64_t g0 = g.origin + (int64_t)c * kRingChunk;
+  // the slot has just been read through the generic proxy; the copy writes it
+  // through the async proxy
+  fence_proxy_async();
   if (c > 0 && c < g.chunks - 1) {  // whole lines well inside the array
     mbar_arrive_expect_tx(full, kRingChunk * 4);
     bulk_g2s_hint(slot, values + g0, kRingChunk * 4, full, policy);
@@ -647,6 +650,10 @@ static cudaError_t ring_launch(const float *values, const int32_t *offsets,
 namespace {
 struct Fork {
   bool ready = false;
+  // held over the whole record / wait / launch sequence of one call: the
+  // events are shared by every call on the device, so two host threads must
+  // not interleave their sequences
+  std::mutex sequence;
   cudaStream_t side[kSoftmaxBuckets - 1];
   cudaEvent_t begin;
   cudaEvent_t done[kSoftmaxBuckets - 1];
@@ -715,19 +722,14 @@ cudaError_t configure_softmax_kernels() {
   return cudaSuccess;
 }
 
-cudaError_t launch_segsoftmax_planned(const float *values,
-                                      const int32_t *offsets, float *out,
-                                      int32_t value_count,
-                                      const DevicePlan &plan,
-                                      cudaStream_t stream,
-                                      const Probe *probe) {
-  static_assert(kSoftmaxBuckets == 8 && kSoftmaxLimit[0] == 8 * 8 &&
-                    kSoftmaxLimit[1] == 32 * 16 && kSoftmaxLimit[2] == 128 * 16,
-                "bucket limits are the capacities of the resident kernels");
-  Fork *fork = nullptr;
-  cudaError_t e = fork_for(plan.device, &fork);
-  if (e != cudaSuccess) return e;
-  probe_begin(probe, stream);
+// The launch sequence of one planned call: ticket counters cleared, the
+// longest class on the caller's stream, every other class on its side stream
+// behind `begin`, each joined back through its `done` event.
+static cudaError_t launch_buckets(const float *values, const int32_t *offsets,
+                                  float *out, int32_t value_count,
+                                  const DevicePlan &plan, cudaStream_t stream,
+                                  Fork *fork) {
+  cudaError_t e;
   e = cudaMemsetAsync(plan.control + kTicketBase, 0,
                       kSoftmaxBuckets * sizeof(uint32_t), stream);
   if (e != cudaSuccess) return e;
@@ -775,8 +777,26 @@ cudaError_t launch_segsoftmax_planned(const float *values,
     e = cudaStreamWaitEvent(stream, fork->done[b], 0);
     if (e != cudaSuccess) return e;
   }
+  return cudaSuccess;
+}
+
+cudaError_t launch_segsoftmax_planned(const float *values,
+                                      const int32_t *offsets, float *out,
+                                      int32_t value_count,
+                                      const DevicePlan &plan,
+                                      cudaStream_t stream,
+                                      const Probe *probe) {
+  static_assert(kSoftmaxBuckets == 8 && kSoftmaxLimit[0] == 8 * 8 &&
+                    kSoftmaxLimit[1] == 32 * 16 && kSoftmaxLimit[2] == 128 * 16,
+                "bucket limits are the capacities of the resident kernels");
+  Fork *fork = nullptr;
+  cudaError_t e = fork_for(plan.device, &fork);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> in_sequence(fork->sequence);
+  probe_begin(probe, stream);
+  e = launch_buckets(values, offsets, out, value_count, plan, stream, fork);
   probe_end(probe, stream);
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 cudaError_t launch_segsoftmax_cta(const float *values, const int32_t *offsets,

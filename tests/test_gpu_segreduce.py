@@ -266,9 +266,16 @@ def test_sum_is_bit_reproducible_and_plan_independent_of_launch_order():
 
 # ---- full-size configurations: oracle on all host cores + properties ----
 
-def full_size_check(offsets, values, kind):
+def full_size_check(offsets, values, kind, planner):
+    """``planner`` "host": the plan is built by the host planner from a CPU
+    copy of the offsets; "device": by the GPU planner from the device-resident
+    offsets, with the schedule it picks -- the path a large ``launch_gpu`` call
+    takes by itself, and the one the benchmark times."""
     device_offsets = torch.as_tensor(offsets).cuda()
-    plan = make_plan(offsets)
+    if planner == "host":
+        plan = make_plan(offsets)
+    else:
+        plan = plan_segments(device_offsets, int(values.numel()))
     segments = len(offsets) - 1
     output = torch.empty(segments, device="cuda")
     launch_gpu(values, device_offsets, output, kind, plan=plan)
@@ -319,16 +326,18 @@ def full_size_check(offsets, values, kind):
     plan.close()
 
 
-def test_full_size_lognormal_max():
+@pytest.mark.parametrize("planner", ["host", "device"])
+def test_full_size_lognormal_max(planner):
     """2**20 segments, lognormal lengths, about 4.8e8 values."""
     offsets = workloads.c3_offsets()
     values = workloads.c3_values(offsets, "cuda")
-    full_size_check(offsets, values, "max")
+    full_size_check(offsets, values, "max", planner)
 
 
-def test_full_size_extreme_skew_sum():
+@pytest.mark.parametrize("planner", ["host", "device"])
+def test_full_size_extreme_skew_sum(planner):
     """2**22 segments, 2**30 values, 64 segments of 2**23."""
     offsets = workloads.c5_offsets()
     values = workloads.normal_values(int(offsets[-1]), "cuda",
                                      workloads.SEEDS["c5"])
-    full_size_check(offsets, values, "sum")
+    full_size_check(offsets, values, "sum", planner)

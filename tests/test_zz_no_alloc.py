@@ -7,7 +7,9 @@ of ``cudaMalloc`` is not acceptable in their serving loop.  For them
 the library image.  This file checks, through the C ABI, that it gives the
 same bits as ``swg_segreduce_f32`` with a plan and the split schedule (both run
 the same tile tasks with the same combine tree), on two calls in a row --
-the second call sees the first call's leftovers in the shared array.
+the second call sees the first call's leftovers in the shared array -- and
+that both agree with the CPU oracle (max bit for bit, sum within
+``1e-5 * sqrt(len) * max|x|`` of the fp64 sum).
 
 Collected last on purpose: a run that stops at the first failure has then
 already run every other test.
@@ -17,6 +19,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 import workloads
 from swage_b200 import _native
 
@@ -50,6 +53,18 @@ def same_bits(a, b):
     return torch.equal(a.view(torch.int32), b.view(torch.int32))
 
 
+def agrees_with_oracle(kind, result, values, offsets):
+    host_values = values.cpu().numpy()
+    result = result.cpu().numpy()
+    if kind == _native.KIND_MAX:
+        expected = oracle.segreduce_f32(host_values, offsets, "max")
+        return np.array_equal(result.view(np.uint32),
+                              expected.view(np.uint32))
+    exact = oracle.segsum_f64(host_values, offsets)
+    bound = oracle.sum_tolerance(host_values, offsets)
+    return bool(np.all(np.abs(result - exact) <= bound))
+
+
 def test_two_calls_in_a_row_match_the_planned_entry_point():
     # first a skewed input with split segments, then a different, smaller one
     # that leaves most of the previous call's data behind in the shared array
@@ -66,6 +81,8 @@ def test_two_calls_in_a_row_match_the_planned_entry_point():
             second = no_alloc(kind, values, offsets, segments)
             assert same_bits(first, expected)
             assert same_bits(second, expected)
+            assert agrees_with_oracle(kind, first, values, offsets)
+            assert agrees_with_oracle(kind, second, values, offsets)
 
 
 def test_sizes_beyond_the_fixed_array_are_rejected_clearly():
