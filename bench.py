@@ -523,12 +523,14 @@ class Problem:
         """Kernels of this library launched by one step."""
         if self.plan is None:
             return 1
-        info = self.plan.describe()
         if self.operation == "softmax":
+            info = self.plan.describe()
             return sum(1 for n in info["softmax_buckets"] if n > 0)
+        info = self.plan.describe()
         schedule = self.args.schedule
         tiles = (schedule in ("split", "persistent", "resident")
                  or (schedule == "auto" and info["schedule"] >= 3))
+        # the tile kernel and, when any segment is cut, the merge pass
         return 2 if tiles and info["split_segments"] > 0 else 1
 
     def parity(self):
@@ -710,9 +712,10 @@ def measure(problem, steps, warmup, barrier, peak):
 
 def measure_cold(problem, barrier):
     """The drop-in call on offsets no cache has seen: validation, planning
-    and launch, inputs resident on the device.  Three different offsets
+    and launch, inputs resident on the device.  Eight different offsets
     arrays (one boundary moved by one each), wall clock around call + stream
-    synchronisation."""
+    synchronisation; ``ms`` is the median, ``all_ms`` every call in order (the
+    first ones also grow the library's memory pool to its working size)."""
     import torch
 
     if problem.operation == "vadd" or problem.kind == "sum+max":
@@ -723,8 +726,8 @@ def measure_cold(problem, barrier):
     if movable.size < 3:
         return None
     times = []
-    for pick in (movable[movable.size // 4], movable[movable.size // 2],
-                 movable[3 * movable.size // 4]):
+    picks = [movable[(2 * i + 1) * movable.size // 16] for i in range(8)]
+    for pick in picks:
         changed = offsets.copy()
         changed[pick] -= 1
         problem.device_offsets = torch.from_numpy(changed).to(problem.device)

@@ -56,12 +56,14 @@ typedef enum swg_status {
 #define SWG_OP_SOFTMAX 1
 
 /* Schedules. AUTO lets the plan (or, without one, the mean segment length)
- * decide.  WARP and CTA need no plan; SPLIT and PERSISTENT run the plan's
- * tile tasks and therefore need one. */
+ * decide.  WARP and CTA need no plan; SPLIT, PERSISTENT and RESIDENT run the
+ * plan's tile tasks and therefore need one.  Segments that cross a tile
+ * boundary are cut into pieces whose partials a small merge pass, launched
+ * right behind the tile kernel, combines in a fixed order. */
 #define SWG_SCHED_AUTO 0
 #define SWG_SCHED_WARP 1       /* one warp per segment */
 #define SWG_SCHED_CTA 2        /* one CTA per segment: the reference's own mapping */
-#define SWG_SCHED_SPLIT 3      /* one tile task per CTA, long segments chunked, second-pass combine */
+#define SWG_SCHED_SPLIT 3      /* one tile task per warp, two per CTA */
 #define SWG_SCHED_PERSISTENT 4 /* one CTA per SM slot, bulk-copy ring, tasks drawn from a ticket counter */
 #define SWG_SCHED_RESIDENT 5   /* one CTA per SM, one stage per warp, tile tasks at a fixed stride */
 
@@ -104,8 +106,10 @@ int swg_validate_offsets_i32(const int32_t *host_offsets, int64_t count,
 /* Host planner: segment-length histogram -> buckets -> tile tasks -> schedule.
  * `host_offsets` has segment_count + 1 validated entries.  The plan owns
  * device copies of the task list, of the offsets (16-byte aligned and padded,
- * so they can be bulk-copied) and the scratch for split-segment partials, all
- * on the current device.  It is the planned scheduling layer of the reference
+ * so they can be bulk-copied) and the scratch in which cut segments are
+ * merged, all in one block on the current device (taken from the device's
+ * stream-ordered memory pool, which the library tells to keep freed memory, so
+ * that later plans cost no cudaMalloc).  It is the planned scheduling layer of the reference
  * (its design document, lines 143-151: warp, packed_warp, cta, split_cta,
  * merge, persistent) made concrete.  A plan is valid only for launches whose device
  * offsets hold the same numbers. */
@@ -119,8 +123,16 @@ int swg_plan_describe(const swg_plan *plan, char *json, size_t capacity);
  * launch since the last call: a bounded wait that gave up
  * (SWG_ERR_DEVICE_TIMEOUT) or a task / segment that does not fit the launch's
  * arrays and was skipped instead of dereferenced (SWG_ERR_DEVICE_CHECK);
- * else SWG_OK. */
+ * else SWG_OK.  After an error the plan's counters are cleared, so it can be
+ * launched again. */
 int swg_plan_status(swg_plan *plan);
+/* The same report without any CUDA call or synchronisation: the kernels also
+ * leave their first error in pinned host memory, which this reads.  It
+ * therefore only knows about launches that have finished; each error is
+ * returned once.  Meant to be called before every launch of a cached plan, so
+ * that a launch that went wrong is noticed at the next one.  No reference
+ * counterpart (the reference's kernels have no device-side checks). */
+int swg_plan_peek_status(const swg_plan *plan);
 
 /* The same rules, order and reason codes as swg_validate_offsets_i32, for
  * offsets[0 .. segment_count] that live on the GPU: one pass on the device, one
@@ -137,24 +149,40 @@ int swg_validate_offsets_device(const int32_t *device_offsets,
                                 uint64_t *hash, int32_t *last_offset);
 
 /* swg_plan_create for device-resident offsets: validation (as above), the
- * length histogram, the tile tasks and merge lists (op = SWG_OP_REDUCE) or the
- * length-class lists (SWG_OP_SOFTMAX) are all computed on the GPU; the offsets
- * are never copied to the host.  On SWG_ERR_INVALID_OFFSETS *reason / *index
- * say which rule broke first and no plan is returned.  The tiles are cut at
- * fixed item positions (merge-path), not by the host planner's walk, so the
- * task list differs from swg_plan_create's; results agree to the documented
- * tolerance (max: bit-exact). */
+ * length histogram, the tile tasks (op = SWG_OP_REDUCE) or the length-class
+ * lists (SWG_OP_SOFTMAX) are all computed on the GPU; the offsets are never
+ * copied to the host.  On SWG_ERR_INVALID_OFFSETS *reason / *index say which
+ * rule broke first and no plan is returned.  `stream` is synchronised once, to
+ * read the validation's verdict; the planner's own kernels are only queued on
+ * it, so launch the plan on that stream (or order other streams behind it).
+ * The tiles are cut at fixed item positions (merge-path), not by the host
+ * planner's walk, so the task list differs from swg_plan_create's; results
+ * agree to the documented tolerance (max: bit-exact). */
 int swg_plan_create_device(const int32_t *device_offsets,
                            int32_t segment_count, int32_t value_count,
                            int64_t output_count, int op, void *stream,
                            swg_plan **plan, int32_t *reason, int64_t *index);
+
+/* swg_plan_create_device for offsets that swg_validate_offsets_device has just
+ * accepted on this device, returning `hash`: when that validation is still the
+ * latest one on the device and was of the same array, its summary is reused
+ * and this call neither reads the offsets a second time nor synchronises --
+ * the planner's kernels are queued on `stream` and the call returns.
+ * Otherwise it behaves like swg_plan_create_device.  This is what a launch
+ * on new offsets costs beyond validation.  No reference counterpart. */
+int swg_plan_create_validated(const int32_t *device_offsets,
+                              int32_t segment_count, int32_t value_count,
+                              int op, void *stream, uint64_t hash,
+                              swg_plan **plan);
 
 /* The planner alone, on the host: no device is touched.  Writes up to
  * `task_capacity` tasks as 8 x int32 each {first segment, segment count or
  * partial slot (-1 = whole segment), first value, value count | kind << 28
  * (kind 0 = packed segments, 1 = chunk of one long segment), partial slot of a
  * first segment that began in an earlier task (else -1), partial slot of a
- * last segment that continues in a later task (else -1), 0, 0}, the total
+ * last segment that continues in a later task (else -1), first partial slot of
+ * the segment a chunk or a first segment belongs to, number of pieces of the
+ * segment a chunk or a last segment belongs to}, the total
  * number of tasks to *task_count, and the same JSON as swg_plan_describe.
  * `tasks` and `json` may be NULL.  For inspection and for tests. */
 int swg_plan_host_tasks(const int32_t *host_offsets, int32_t segment_count,
@@ -201,17 +229,24 @@ int swg_segreduce_sum_max_f32(const float *values, const int32_t *offsets,
  *
  * The planner runs on the host from `host_offsets` (segment_count + 1 entries,
  * validated here) and the task list, an aligned copy of the offsets and the
- * partials of split segments are placed in a fixed array that is part of the
- * library image on every GPU (about 2.3 MB, held until the process exits).
- * No cudaMalloc, cudaFree or other allocating call is made.
- * Limits: at most 262144 segments, 32768 tile tasks (about 6.6e7 values),
- * 32768 partials and 8192 split segments; larger inputs are rejected with
+ * list and partials of cut segments are placed in a fixed array that is part of
+ * the library image on every GPU (2,490,880 bytes, about 2.5 MB, held until
+ * the process exits).  No cudaMalloc, cudaFree or other allocating call is
+ * made.
+ * Limits: at most 262144 segments, 32768 tile tasks (about 6.6e7 values) and
+ * 32768 partials of cut segments; larger inputs are rejected with
  * SWG_ERR_UNSUPPORTED and a message naming the limit.
- * The first call on a device looks up the array's device address; make that
- * first call outside any stream capture.  All calls share the array, which
+ * The first call on a device looks up the array's device address; that first
+ * call should come before any stream capture.  Every call copies the offsets
+ * and the task list from host memory on `stream`: `host_offsets` must stay
+ * unchanged until `stream` has passed the call (a pinned buffer is read by the
+ * copy engine after the call has returned).  All calls share the array, which
  * keeps the last call's contents (the parts that must start at zero are
  * cleared on `stream` each time), so two calls that can overlap on the GPU --
- * different streams, or different host threads -- race: serialise them. */
+ * different streams, or different host threads -- race: serialise them.
+ * The kernel's device-side checks write their verdict into the array; it is
+ * not read back (the tasks are built from the very offsets passed in, so only
+ * the two-second wait limit could trip). */
 int swg_segreduce_f32_noalloc(int kind, const float *values,
                               const int32_t *host_offsets, float *out,
                               int32_t value_count, int32_t segment_count,

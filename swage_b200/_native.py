@@ -43,7 +43,8 @@ EXPORTS = (
     "swg_segsoftmax_f32", "swg_shard_offsets", "swg_profile_start",
     "swg_profile_stop", "swg_segreduce_f32_noalloc",
     "swg_validate_offsets_device", "swg_plan_create_device",
-    "swg_segreduce_sum_max_f32",
+    "swg_segreduce_sum_max_f32", "swg_plan_create_validated",
+    "swg_plan_peek_status",
 )
 
 _lock = threading.Lock()
@@ -101,6 +102,11 @@ def _declare(lib):
     lib.swg_plan_create_device.argtypes = [
         ptr, c_i32, c_i32, c_i64, c_int, ptr, ctypes.POINTER(ptr),
         ctypes.POINTER(c_i32), ctypes.POINTER(c_i64)]
+    lib.swg_plan_create_validated.restype = c_int
+    lib.swg_plan_create_validated.argtypes = [
+        ptr, c_i32, c_i32, c_int, ptr, ctypes.c_uint64, ctypes.POINTER(ptr)]
+    lib.swg_plan_peek_status.restype = c_int
+    lib.swg_plan_peek_status.argtypes = [ptr]
     lib.swg_profile_start.restype = c_int
     lib.swg_profile_start.argtypes = [c_i32, c_i32]
     lib.swg_profile_stop.restype = c_int
@@ -236,6 +242,20 @@ def plan_create_device(device_ptr, segment_count, value_count, output_count,
     return handle, "ok", -1
 
 
+def plan_create_validated(device_ptr, segment_count, value_count, op, stream,
+                          digest):
+    """Plan on the GPU from offsets ``validate_offsets_device`` has just
+    accepted (it returned ``digest``): no second pass, no synchronisation."""
+    handle = ctypes.c_void_p()
+    check(
+        library().swg_plan_create_validated(
+            device_ptr, segment_count, value_count, op, stream, digest,
+            ctypes.byref(handle)),
+        "swg_plan_create_validated",
+    )
+    return handle
+
+
 def plan_create(host_ptr, segment_count, value_count, op):
     handle = ctypes.c_void_p()
     check(
@@ -261,7 +281,9 @@ def plan_host_tasks(host_ptr, segment_count, op=OP_REDUCE):
     """Run the planner on the host only; return ``(tasks, description)``.
 
     ``tasks`` is a list of ``(segment, count_or_slot, value_begin,
-    value_count, kind, head_slot, tail_slot)`` tuples.
+    value_count, kind, head_slot, tail_slot, link_first, link_pieces)``
+    tuples (the last two: where the partial slots of the cut segment a piece
+    belongs to begin, and how many pieces it has).
     """
     import json
 
@@ -277,15 +299,24 @@ def plan_host_tasks(host_ptr, segment_count, op=OP_REDUCE):
           "swg_plan_host_tasks")
     tasks = []
     for t in range(total.value):
-        seg, count, vbegin, packed, head, tail = words[8 * t:8 * t + 6]
+        (seg, count, vbegin, packed, head, tail, link_first,
+         link_pieces) = words[8 * t:8 * t + 8]
         packed &= 0xFFFFFFFF
         tasks.append((seg, count, vbegin, packed & ((1 << 28) - 1),
-                      packed >> 28, head, tail))
+                      packed >> 28, head, tail, link_first, link_pieces))
     return tasks, json.loads(text.value.decode())
 
 
 def plan_status(handle):
     check(library().swg_plan_status(handle), "swg_plan_status")
+
+
+def plan_peek_status(handle):
+    """Raise for an error a FINISHED launch of the plan left behind; no CUDA
+    call, no synchronisation."""
+    status = library().swg_plan_peek_status(handle)
+    if status:
+        check(status, "swg_plan_peek_status")
 
 
 def shard_offsets(host_ptr, segment_count, shards):

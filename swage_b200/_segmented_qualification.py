@@ -19,8 +19,9 @@ Differences that do not change results:
   physical schedule (warp / CTA / split / persistent tile tasks) is chosen by
   a plan built from the segment-length histogram;
 * plans are cached per offsets content (a 64-bit digest computed by the
-  validation pass on the device, or exact comparison of the host copy), so
-  repeated launches over the same CSR structure skip the planner.
+  validation pass on the device, or exact comparison of the host copy) and
+  per stream, so repeated launches over the same CSR structure skip the
+  planner and launches on different streams never share scratch.
 """
 
 import collections
@@ -251,17 +252,21 @@ class SegmentPlan:
     The plan owns device copies of its task list, of the offsets and of the
     partial scratch.  It stays valid for as long as the offsets hold the same
     numbers; launches that share a plan must not overlap on the GPU (they
-    share the partial scratch and the ticket counter).
+    share the merge scratch and the ticket counters): keep a plan to one
+    stream, or order the streams yourself.  The plans ``launch_gpu`` and
+    ``launch_softmax_gpu`` find by themselves are cached per stream.
     """
 
-    def __init__(self, host_offsets, value_count, op="reduce"):
+    def __init__(self, host_offsets, value_count, op="reduce", *,
+                 _digest=None):
         from . import _native
 
         torch = _runtime._import_torch()
         if isinstance(host_offsets, torch.Tensor) and (
             host_offsets.device.type == "cuda"
         ):
-            self._from_device(host_offsets, value_count, op, _native, torch)
+            self._from_device(host_offsets, value_count, op, _native, torch,
+                              _digest)
             return
         if (
             not isinstance(host_offsets, torch.Tensor)
@@ -285,7 +290,8 @@ class SegmentPlan:
         )
         self._dump()
 
-    def _from_device(self, offsets, value_count, op, _native, torch):
+    def _from_device(self, offsets, value_count, op, _native, torch,
+                     digest=None):
         if (
             offsets.dtype != torch.int32
             or offsets.dim() != 1
@@ -306,6 +312,14 @@ class SegmentPlan:
         self._handle = None
         _validate_counts(self.value_count, self.segment_count)
         stream = torch.cuda.current_stream()
+        if digest is not None:
+            # validated a moment ago on this stream: its summary is reused
+            self._handle = _native.plan_create_validated(
+                offsets.data_ptr(), self.segment_count, self.value_count,
+                code, stream.cuda_stream, digest,
+            )
+            self._dump()
+            return
         handle, reason, _ = _native.plan_create_device(
             offsets.data_ptr(), self.segment_count, self.value_count,
             self.segment_count, code, stream.cuda_stream,
@@ -338,6 +352,14 @@ class SegmentPlan:
     def check(self):
         """Synchronise and raise if a bounded device-side wait gave up."""
         self._native.plan_status(self.handle)
+
+    def peek(self):
+        """Raise if a launch of this plan that has FINISHED flagged an error
+        (a wait that gave up, a task or segment that does not fit the
+        launch's arrays).  Costs no CUDA call; the launch functions call it
+        before every launch, so a launch that went wrong is reported by the
+        next one instead of passing silently."""
+        self._native.plan_peek_status(self.handle)
 
     def close(self):
         if self._handle is not None:
@@ -377,11 +399,18 @@ def plan_segments(offsets, value_count=None, op="reduce"):
 _plan_cache = collections.OrderedDict()
 _plan_cache_lock = threading.Lock()
 
+# A plan owns scratch that its launches write (partials, arrival counters,
+# ticket counters): two launches of one plan must not overlap on the GPU.
+# Launches on one stream never do, so the caches hand out one plan per
+# (offsets, stream): two streams reducing over the same CSR structure get a
+# plan each.  An evicted plan is only dropped from the cache; it is closed
+# when the last launch that still holds it lets go.
 
-def _cached_plan(host_offsets, value_count, op, device):
+
+def _cached_plan(host_offsets, value_count, op, device, stream):
     """Plan for exactly these offsets; equality is checked on the full array."""
     torch = _runtime._import_torch()
-    key = (device, op, host_offsets.numel(), value_count)
+    key = (device, stream, op, host_offsets.numel(), value_count)
     with _plan_cache_lock:
         bucket = _plan_cache.get(key)
         if bucket is not None:
@@ -395,7 +424,7 @@ def _cached_plan(host_offsets, value_count, op, device):
         while sum(len(b) for b in _plan_cache.values()) > _PLAN_CACHE_ENTRIES:
             oldest = next(iter(_plan_cache))
             entries = _plan_cache[oldest]
-            entries.pop(0)[1].close()
+            entries.pop(0)
             if not entries:
                 del _plan_cache[oldest]
         return plan
@@ -404,35 +433,55 @@ def _cached_plan(host_offsets, value_count, op, device):
 _device_plan_cache = collections.OrderedDict()
 
 
-def _cached_device_plan(offsets, value_count, op, device, digest):
+def _cached_device_plan(offsets, value_count, op, device, stream, digest):
     """Plan built on the GPU for offsets with this content digest."""
-    key = (device, op, offsets.numel(), value_count, digest)
+    key = (device, stream, op, offsets.numel(), value_count, digest)
     with _plan_cache_lock:
         plan = _device_plan_cache.get(key)
         if plan is not None:
             _device_plan_cache.move_to_end(key)
             return plan
-        plan = SegmentPlan(offsets, value_count, op)
+        plan = SegmentPlan(offsets, value_count, op, _digest=digest)
         _device_plan_cache[key] = plan
         while len(_device_plan_cache) > _PLAN_CACHE_ENTRIES:
-            _, oldest = _device_plan_cache.popitem(last=False)
-            oldest.close()
+            _device_plan_cache.popitem(last=False)
         return plan
 
 
 def _plan_for_launch(offsets, value_count, segment_count, op, torch):
     """The cached plan for a launch that was just validated on this thread."""
     device = torch.cuda.current_device()
+    stream = torch.cuda.current_stream().cuda_stream
     digest = getattr(_last_digest, "value", None)
     _last_digest.value = None
     if digest is not None and digest[:2] == (offsets.data_ptr(),
                                              segment_count):
-        return _cached_device_plan(offsets, value_count, op, device,
+        return _cached_device_plan(offsets, value_count, op, device, stream,
                                    digest[2])
     host = getattr(_last_host_offsets, "value", None)
     if host is None or host.numel() != segment_count + 1:
         host = offsets.detach().cpu()
-    return _cached_plan(host, value_count, op, device)
+    return _cached_plan(host, value_count, op, device, stream)
+
+
+def _drop_cached(plan):
+    """Forget a plan whose launch went wrong; the next launch plans afresh."""
+    with _plan_cache_lock:
+        for key, kept in list(_device_plan_cache.items()):
+            if kept is plan:
+                del _device_plan_cache[key]
+        for key, entries in list(_plan_cache.items()):
+            entries[:] = [pair for pair in entries if pair[1] is not plan]
+            if not entries:
+                del _plan_cache[key]
+
+
+def _peek(plan):
+    try:
+        plan.peek()
+    except RuntimeError:
+        _drop_cached(plan)
+        raise
 
 
 def clear_plan_cache():
@@ -519,6 +568,8 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
                                 torch)
     _last_host_offsets.value = None
     _last_digest.value = None
+    if plan is not None:
+        _peek(plan)
     stream = torch.cuda.current_stream()
     _native.segreduce(
         kind_code, values.data_ptr(), offsets.data_ptr(), output.data_ptr(),
@@ -615,6 +666,8 @@ def launch_softmax_gpu(values, offsets, output, *, plan=None, schedule="auto",
                                 "softmax", torch)
     _last_host_offsets.value = None
     _last_digest.value = None
+    if plan is not None:
+        _peek(plan)
     stream = torch.cuda.current_stream()
     _native.segsoftmax(
         values.data_ptr(), offsets.data_ptr(), output.data_ptr(), value_count,

@@ -11,7 +11,12 @@
 struct swg_plan {
   swg::HostPlan host;
   swg::DevicePlan dev;
-  std::string description;
+  // the stream of the launches so far (the plan's memory is freed behind it)
+  mutable cudaStream_t last_stream = nullptr;
+  mutable bool launched = false;
+  mutable bool many_streams = false;
+  // device planner: the task statistics are fetched when first asked for
+  mutable bool counts_known = true;
 };
 
 namespace {
@@ -86,35 +91,93 @@ int current_device(int *device, int *sm_count) {
   return SWG_OK;
 }
 
-template <class T>
-int upload(T **dst, const T *src, size_t count, size_t padded_count,
-           const char *what) {
-  *dst = nullptr;
-  if (padded_count == 0) return SWG_OK;
-  cudaError_t e = cudaMalloc((void **)dst, padded_count * sizeof(T));
-  if (e != cudaSuccess) return cuda_failure(what, e);
-  if (padded_count > count) {
-    e = cudaMemset(*dst + count, 0, (padded_count - count) * sizeof(T));
-    if (e != cudaSuccess) return cuda_failure("cudaMemset", e);
+// Host-visible error words, one pair per plan: a page of pinned, mapped
+// memory per device, handed out in 8-byte slots.
+struct StatusPool {
+  uint32_t *page = nullptr;
+  std::vector<int> free_slots;
+  bool tried = false;
+};
+constexpr int kStatusSlots = 512;
+StatusPool g_status[64];
+
+uint32_t *status_acquire(int device) {
+  std::lock_guard<std::mutex> guard(g_lock);
+  StatusPool &pool = g_status[device];
+  if (!pool.tried) {
+    pool.tried = true;
+    void *page = nullptr;
+    if (cudaHostAlloc(&page, kStatusSlots * 8, cudaHostAllocMapped |
+                                                   cudaHostAllocPortable) ==
+        cudaSuccess) {
+      pool.page = static_cast<uint32_t *>(page);
+      memset(page, 0, kStatusSlots * 8);
+      for (int i = kStatusSlots - 1; i >= 0; --i) pool.free_slots.push_back(i);
+    } else {
+      cudaGetLastError();
+    }
   }
-  if (count) {
-    e = cudaMemcpy(*dst, src, count * sizeof(T), cudaMemcpyHostToDevice);
-    if (e != cudaSuccess) return cuda_failure("cudaMemcpy", e);
-  }
-  return SWG_OK;
+  if (pool.page == nullptr || pool.free_slots.empty()) return nullptr;
+  const int slot = pool.free_slots.back();
+  pool.free_slots.pop_back();
+  uint32_t *words = pool.page + 2 * slot;
+  words[0] = words[1] = 0;
+  return words;
 }
 
-void release(swg::DevicePlan &dev) {
-  cudaFree(dev.tasks);
-  cudaFree(dev.offsets);
-  if (!dev.shared_block) {
-    cudaFree(dev.splits);
-    cudaFree(dev.partials);
-  }
-  cudaFree(dev.softmax_segments);
-  cudaFree(dev.control);
+void status_release(int device, uint32_t *words) {
+  if (words == nullptr) return;
+  std::lock_guard<std::mutex> guard(g_lock);
+  StatusPool &pool = g_status[device];
+  pool.free_slots.push_back((int)((words - pool.page) / 2));
+}
+
+// Tells the plan's kernels where the host-visible error words are.
+cudaError_t status_attach(swg::DevicePlan *dev, cudaStream_t stream) {
+  dev->host_status = status_acquire(dev->device);
+  if (dev->host_status == nullptr || dev->control == nullptr)
+    return cudaSuccess;
+  void *seen_by_device = nullptr;
+  cudaError_t e =
+      cudaHostGetDevicePointer(&seen_by_device, dev->host_status, 0);
+  if (e != cudaSuccess) return e;
+  const unsigned long long address =
+      (unsigned long long)(uintptr_t)seen_by_device;
+  // (a small copy from pageable memory is staged before the call returns)
+  return cudaMemcpyAsync(dev->control + swg::kStatusWord, &address,
+                         sizeof(address), cudaMemcpyHostToDevice, stream);
+}
+
+void release(swg_plan *plan) {
+  swg::DevicePlan &dev = plan->dev;
+  status_release(dev.device, dev.host_status);
+  swg::plan_block_release(&dev, plan->last_stream,
+                          plan->launched && !plan->many_streams);
   dev = swg::DevicePlan();
 }
+
+void note_launch(const swg_plan *plan, cudaStream_t stream) {
+  if (plan->launched && plan->last_stream != stream)
+    plan->many_streams = true;
+  plan->last_stream = stream;
+  plan->launched = true;
+}
+
+std::string describe(const swg_plan *plan) {
+  if (!plan->counts_known) {
+    int64_t chunks = 0, cuts = 0;
+    if (swg::device_plan_counts(plan->dev, &chunks, &cuts) == cudaSuccess) {
+      swg_plan *writable = const_cast<swg_plan *>(plan);
+      writable->host.chunk_tasks = chunks;
+      writable->host.pack_tasks = plan->host.task_total - chunks;
+      writable->host.split_segments = cuts;
+      writable->counts_known = true;
+    }
+  }
+  return swg::describe_host_plan(plan->host);
+}
+
+constexpr size_t aligned256(size_t bytes) { return (bytes + 255) / 256 * 256; }
 
 }  // namespace
 
@@ -191,50 +254,92 @@ int swg_plan_create(const int32_t *host_offsets, int32_t segment_count,
     return SWG_ERR_INVALID_ARGUMENT;
   }
   swg::build_host_plan(host_offsets, segment_count, op, &plan->host);
-  plan->description = swg::describe_host_plan(plan->host);
   swg::DevicePlan &dev = plan->dev;
   dev.device = device;
   dev.sm_count = sm_count;
   dev.task_count = (int32_t)plan->host.tasks.size();
   dev.segment_count = segment_count;
-  dev.split_count = (int32_t)plan->host.splits.size();
-  dev.big_split_count = plan->host.big_split_count;
-  dev.medium_split_count = plan->host.medium_split_count;
   dev.partial_slots = plan->host.partial_slots;
-  const size_t noffsets = (size_t)segment_count + 1;
-  const size_t padded = ((noffsets + 3) / 4) * 4 + 4;
-  status = upload(&dev.tasks, plan->host.tasks.data(), plan->host.tasks.size(),
-                  plan->host.tasks.size(), "cudaMalloc(tasks)");
-  if (status == SWG_OK)
-    status = upload(&dev.offsets, host_offsets, noffsets, padded,
-                    "cudaMalloc(offsets)");
-  if (status == SWG_OK)
-    status = upload(&dev.splits, plan->host.splits.data(),
-                    plan->host.splits.size(), plan->host.splits.size(),
-                    "cudaMalloc(splits)");
-  if (status == SWG_OK)
-    status = upload<float>(&dev.partials, nullptr, 0,
-                           (size_t)dev.partial_slots, "cudaMalloc(partials)");
+  dev.slot_step = plan->host.slot_step;
   for (int b = 0; b < swg::kSoftmaxBuckets; ++b) {
     dev.softmax_begin[b] = plan->host.softmax_begin[b];
     dev.softmax_count[b] = plan->host.softmax_count[b];
   }
-  if (status == SWG_OK)
-    status = upload(&dev.softmax_segments, plan->host.softmax_segments.data(),
-                    plan->host.softmax_segments.size(),
-                    plan->host.softmax_segments.size(),
-                    "cudaMalloc(softmax buckets)");
-  if (status == SWG_OK)
-    status = upload<uint32_t>(&dev.control, nullptr, 0, swg::kControlWords,
-                              "cudaMalloc(control)");
-  if (status != SWG_OK) {
-    release(dev);
+  // one block: padded offsets, control words, tasks, merge records, partials,
+  // softmax class lists
+  const size_t noffsets = (size_t)segment_count + 1;
+  const size_t padded = ((noffsets + 3) / 4) * 4 + 4;
+  const size_t offsets_bytes = aligned256(padded * sizeof(int32_t));
+  const size_t control_bytes =
+      aligned256(swg::kControlWords * sizeof(uint32_t) + sizeof(int32_t));
+  const size_t task_bytes =
+      aligned256(plan->host.tasks.size() * sizeof(swg::Task));
+  const size_t merge_bytes =
+      aligned256(plan->host.merges.size() * sizeof(swg::MergeRecord));
+  const size_t big_bytes =
+      aligned256(plan->host.big_merges.size() * sizeof(swg::MergeRecord));
+  const size_t slot_bytes =
+      aligned256((size_t)dev.partial_slots * sizeof(float));
+  const size_t list_bytes =
+      aligned256(plan->host.softmax_segments.size() * sizeof(int32_t));
+  cudaError_t e = swg::plan_block_allocate(
+      &dev,
+      offsets_bytes + control_bytes + task_bytes + merge_bytes + big_bytes +
+          slot_bytes + list_bytes,
+      nullptr);
+  if (e == cudaSuccess) e = cudaMemset(dev.block, 0, dev.block_bytes);
+  if (e == cudaSuccess) {
+    unsigned char *at = static_cast<unsigned char *>(dev.block);
+    dev.offsets = reinterpret_cast<int32_t *>(at);
+    at += offsets_bytes;
+    dev.control = reinterpret_cast<uint32_t *>(at);
+    dev.big_count = reinterpret_cast<int32_t *>(dev.control + swg::kControlWords);
+    at += control_bytes;
+    dev.tasks = reinterpret_cast<swg::Task *>(at);
+    at += task_bytes;
+    dev.merges = reinterpret_cast<swg::MergeRecord *>(at);
+    dev.merge_count = (int32_t)plan->host.merges.size();
+    at += merge_bytes;
+    dev.bigs = reinterpret_cast<swg::MergeRecord *>(at);
+    dev.big_capacity = (int32_t)plan->host.big_merges.size();
+    at += big_bytes;
+    dev.partials = reinterpret_cast<float *>(at);
+    at += slot_bytes;
+    dev.softmax_segments = reinterpret_cast<int32_t *>(at);
+    e = cudaMemcpy(dev.offsets, host_offsets, noffsets * sizeof(int32_t),
+                   cudaMemcpyHostToDevice);
+  }
+  if (e == cudaSuccess && !plan->host.tasks.empty())
+    e = cudaMemcpy(dev.tasks, plan->host.tasks.data(),
+                   plan->host.tasks.size() * sizeof(swg::Task),
+                   cudaMemcpyHostToDevice);
+  if (e == cudaSuccess && !plan->host.merges.empty())
+    e = cudaMemcpy(dev.merges, plan->host.merges.data(),
+                   plan->host.merges.size() * sizeof(swg::MergeRecord),
+                   cudaMemcpyHostToDevice);
+  if (e == cudaSuccess && !plan->host.big_merges.empty())
+    e = cudaMemcpy(dev.bigs, plan->host.big_merges.data(),
+                   plan->host.big_merges.size() * sizeof(swg::MergeRecord),
+                   cudaMemcpyHostToDevice);
+  if (e == cudaSuccess)
+    e = cudaMemcpy(dev.big_count, &dev.big_capacity, sizeof(int32_t),
+                   cudaMemcpyHostToDevice);
+  if (e == cudaSuccess && !plan->host.softmax_segments.empty())
+    e = cudaMemcpy(dev.softmax_segments, plan->host.softmax_segments.data(),
+                   plan->host.softmax_segments.size() * sizeof(int32_t),
+                   cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = status_attach(&dev, nullptr);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(nullptr);
+  if (e != cudaSuccess) {
+    release(plan);
     delete plan;
-    return status;
+    return cuda_failure("plan upload", e);
   }
   // host vectors are no longer needed once uploaded
+  plan->host.task_total = (int64_t)plan->host.tasks.size();
   std::vector<swg::Task>().swap(plan->host.tasks);
-  std::vector<swg::SplitSegment>().swap(plan->host.splits);
+  std::vector<swg::MergeRecord>().swap(plan->host.merges);
+  std::vector<swg::MergeRecord>().swap(plan->host.big_merges);
   std::vector<int32_t>().swap(plan->host.softmax_segments);
   *plan_out = plan;
   return SWG_OK;
@@ -287,14 +392,15 @@ int swg_validate_offsets_device(const int32_t *device_offsets,
   return SWG_ERR_INVALID_OFFSETS;
 }
 
-int swg_plan_create_device(const int32_t *device_offsets,
-                           int32_t segment_count, int32_t value_count,
-                           int64_t output_count, int op, void *stream,
-                           swg_plan **plan_out, int32_t *reason,
-                           int64_t *index) {
+static int create_on_device(const char *who, const int32_t *device_offsets,
+                            int32_t segment_count, int32_t value_count,
+                            int64_t output_count, int op, void *stream,
+                            const unsigned long long *known_hash,
+                            swg_plan **plan_out, int32_t *reason,
+                            int64_t *index) {
   swg::clear_error();
   if (!plan_out || (op != SWG_OP_REDUCE && op != SWG_OP_SOFTMAX)) {
-    swg::set_error("swg_plan_create_device: bad arguments");
+    swg::set_error("%s: bad arguments", who);
     return SWG_ERR_INVALID_ARGUMENT;
   }
   *plan_out = nullptr;
@@ -306,7 +412,7 @@ int swg_plan_create_device(const int32_t *device_offsets,
   if (status != SWG_OK) return status;
   swg_plan *plan = new (std::nothrow) swg_plan();
   if (!plan) {
-    swg::set_error("swg_plan_create_device: out of host memory");
+    swg::set_error("%s: out of host memory", who);
     return SWG_ERR_INVALID_ARGUMENT;
   }
   plan->dev.device = device;
@@ -314,21 +420,46 @@ int swg_plan_create_device(const int32_t *device_offsets,
   int32_t why = SWG_OFFSETS_OK;
   int64_t where = -1;
   cudaError_t e = swg::device_plan(device_offsets, segment_count, value_count,
-                                   op, (cudaStream_t)stream, &plan->dev,
-                                   &plan->host, &why, &where);
+                                   op, (cudaStream_t)stream, known_hash,
+                                   &plan->dev, &plan->host, &why, &where);
+  if (e == cudaSuccess && why == SWG_OFFSETS_OK)
+    e = status_attach(&plan->dev, (cudaStream_t)stream);
   if (reason) *reason = why;
   if (index) *index = where;
   if (e != cudaSuccess || why != SWG_OFFSETS_OK) {
-    release(plan->dev);
+    release(plan);
     delete plan;
     if (e != cudaSuccess) return cuda_failure("device planner", e);
     swg::set_error("offsets rejected: reason %d at index %lld", (int)why,
                    (long long)where);
     return SWG_ERR_INVALID_OFFSETS;
   }
-  plan->description = swg::describe_host_plan(plan->host);
+  // the planner's kernels are queued on `stream`; launches of the plan on
+  // that stream follow them, and the plan's memory is released behind it
+  note_launch(plan, (cudaStream_t)stream);
+  plan->counts_known = op != SWG_OP_REDUCE;
   *plan_out = plan;
   return SWG_OK;
+}
+
+int swg_plan_create_device(const int32_t *device_offsets,
+                           int32_t segment_count, int32_t value_count,
+                           int64_t output_count, int op, void *stream,
+                           swg_plan **plan_out, int32_t *reason,
+                           int64_t *index) {
+  return create_on_device("swg_plan_create_device", device_offsets,
+                          segment_count, value_count, output_count, op, stream,
+                          nullptr, plan_out, reason, index);
+}
+
+int swg_plan_create_validated(const int32_t *device_offsets,
+                              int32_t segment_count, int32_t value_count,
+                              int op, void *stream, uint64_t hash,
+                              swg_plan **plan_out) {
+  const unsigned long long known = hash;
+  return create_on_device("swg_plan_create_validated", device_offsets,
+                          segment_count, value_count, segment_count, op,
+                          stream, &known, plan_out, nullptr, nullptr);
 }
 
 int swg_plan_host_tasks(const int32_t *host_offsets, int32_t segment_count,
@@ -371,7 +502,7 @@ int swg_plan_destroy(swg_plan *plan) {
   const int owner = plan->dev.device;
   cudaGetDevice(&previous);
   if (owner >= 0 && previous != owner) cudaSetDevice(owner);
-  release(plan->dev);
+  release(plan);
   if (previous >= 0 && previous != owner) cudaSetDevice(previous);
   delete plan;
   return SWG_OK;
@@ -379,13 +510,41 @@ int swg_plan_destroy(swg_plan *plan) {
 
 int swg_plan_describe(const swg_plan *plan, char *json, size_t capacity) {
   swg::clear_error();
-  if (!plan || !json || capacity <= plan->description.size()) {
-    swg::set_error("swg_plan_describe: need %zu bytes",
-                   plan ? plan->description.size() + 1 : (size_t)0);
+  if (!plan || !json) {
+    swg::set_error("swg_plan_describe: null argument");
     return SWG_ERR_INVALID_ARGUMENT;
   }
-  memcpy(json, plan->description.c_str(), plan->description.size() + 1);
+  const std::string text = describe(plan);
+  if (capacity <= text.size()) {
+    swg::set_error("swg_plan_describe: need %zu bytes", text.size() + 1);
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  memcpy(json, text.c_str(), text.size() + 1);
   return SWG_OK;
+}
+
+// The message and status for an error code left by a kernel.
+static int device_error(uint32_t code, uint32_t detail) {
+  const char *what = code == 1 ? "a bounded device-side wait gave up"
+                     : code == 2
+                         ? "a task of the plan does not fit the launch's "
+                           "arrays"
+                         : "the device offsets do not match the plan";
+  swg::set_error("%s (code %u, detail %u)", what, code, detail);
+  return code == 1 ? SWG_ERR_DEVICE_TIMEOUT : SWG_ERR_DEVICE_CHECK;
+}
+
+int swg_plan_peek_status(const swg_plan *plan) {
+  swg::clear_error();
+  if (!plan) {
+    swg::set_error("swg_plan_peek_status: plan is null");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  volatile uint32_t *words = plan->dev.host_status;
+  if (words == nullptr || words[0] == 0) return SWG_OK;
+  const uint32_t code = words[0], detail = words[1];
+  words[0] = 0;  // reported once here; swg_plan_status still sees it
+  return device_error(code, detail);
 }
 
 int swg_plan_status(swg_plan *plan) {
@@ -410,19 +569,13 @@ int swg_plan_status(swg_plan *plan) {
   }
   // an error leaves the ticket and finished counters of the persistent
   // schedule wherever the kernel stopped: start the next launch from zero
-  if (e == cudaSuccess && control[2] != 0)
+  if (e == cudaSuccess && control[2] != 0) {
     cudaMemset(plan->dev.control, 0, sizeof(control));
+    if (plan->dev.host_status != nullptr) plan->dev.host_status[0] = 0;
+  }
   if (switched && previous >= 0) cudaSetDevice(previous);
   if (e != cudaSuccess) return cuda_failure(failed, e);
-  if (control[2] != 0) {
-    const char *what = control[2] == 1 ? "a bounded device-side wait gave up"
-                       : control[2] == 2
-                           ? "a task of the plan does not fit the launch's "
-                             "arrays"
-                           : "the device offsets do not match the plan";
-    swg::set_error("%s (code %u, detail %u)", what, control[2], control[3]);
-    return control[2] == 1 ? SWG_ERR_DEVICE_TIMEOUT : SWG_ERR_DEVICE_CHECK;
-  }
+  if (control[2] != 0) return device_error(control[2], control[3]);
   return SWG_OK;
 }
 
@@ -476,6 +629,7 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t e = cudaSuccess;
   const swg::Probe *probe = next_probe();
+  if (plan) note_launch(plan, s);
   switch (schedule) {
     case SWG_SCHED_WARP:
       e = swg::launch_segreduce_warp(kind, values, offsets, out, segment_count,
@@ -562,15 +716,18 @@ int swg_segreduce_f32_noalloc(int kind, const float *values,
   }
   swg::HostPlan plan;
   swg::build_host_plan(host_offsets, segment_count, SWG_OP_REDUCE, &plan);
+  // (the list of cut segments shares its region with the list of the long
+  // ones, which takes kStaticMaxSlots / kWarpMerge records off its end)
   if ((int64_t)plan.tasks.size() > swg::kStaticMaxTasks ||
       plan.partial_slots > swg::kStaticMaxSlots ||
-      (int64_t)plan.splits.size() > swg::kStaticMaxSplits) {
+      (int64_t)plan.merges.size() >
+          swg::kStaticMaxSlots / 2 - swg::kStaticMaxSlots / swg::kWarpMerge) {
     swg::set_error(
-        "swg_segreduce_f32_noalloc: input needs %zu tile tasks / %d partials "
-        "/ %zu split segments, the fixed scratch holds %d / %d / %d; use "
-        "swg_plan_create + swg_segreduce_f32",
-        plan.tasks.size(), plan.partial_slots, plan.splits.size(),
-        swg::kStaticMaxTasks, swg::kStaticMaxSlots, swg::kStaticMaxSplits);
+        "swg_segreduce_f32_noalloc: input needs %zu tile tasks / %d partials, "
+        "the fixed scratch holds %d / %d; use swg_plan_create + "
+        "swg_segreduce_f32",
+        plan.tasks.size(), plan.partial_slots, swg::kStaticMaxTasks,
+        swg::kStaticMaxSlots);
     return SWG_ERR_UNSUPPORTED;
   }
   int device = 0, sm_count = 0;
@@ -623,6 +780,7 @@ int swg_segsoftmax_f32(const float *values, const int32_t *offsets, float *out,
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t e;
   const swg::Probe *probe = next_probe();
+  if (plan) note_launch(plan, s);
   if (plan && schedule >= SWG_SCHED_SPLIT)
     e = swg::launch_segsoftmax_planned(values, offsets, out, value_count,
                                        plan->dev, s, probe);

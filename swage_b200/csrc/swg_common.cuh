@@ -234,6 +234,10 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar,
       : "memory");
 }
 
+// One probe.  The hardware parks the thread for a system-chosen time while
+// the phase is incomplete.  (An explicit 20 us suspend-time hint and a
+// __nanosleep between probes both measured no different: the waiting warps do
+// not take issue slots from the working ones.)
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
@@ -267,6 +271,17 @@ __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// Asks L2 to fetch [src, src + bytes) (16-byte aligned, a multiple of 16
+// bytes); nothing is delivered to the SM.  L2 is the point of coherence for
+// global memory, so a line prefetched before its last writer has finished
+// still holds that writer's data when it is read later.
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src_gmem,
+                                                 uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_gmem),
+               "r"(bytes)
+               : "memory");
+}
+
 // global -> shared bulk copy, completion counted in bytes on `bar`.  Both
 // addresses 16-byte aligned, `bytes` a multiple of 16.  No multicast.
 __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem,
@@ -276,6 +291,28 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem,
       "[%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
       "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// Error words of a plan's control block: control[2] = code (first one wins),
+// control[3] = detail.  control[12..13] may hold the address of a host-visible
+// copy {code, detail} (pinned memory), which the host can read without a CUDA
+// call once the kernel has finished.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kErrTimeout = 1u, kErrBadTask = 2u, kErrBadSegment = 3u;
+
+__device__ __forceinline__ void report(uint32_t *control, uint32_t code,
+                                       uint32_t detail) {
+  if (atomicCAS(control + 2, 0u, code) != 0u) return;
+  atomicExch(control + 3, detail);
+  volatile uint32_t *host = reinterpret_cast<volatile uint32_t *>(
+      *reinterpret_cast<unsigned long long *>(control + 12));
+  if (host != nullptr) {
+    host[1] = detail;
+    __threadfence_system();
+    host[0] = code;
+    __threadfence_system();
+  }
 }
 
 }  // namespace swg

@@ -1,24 +1,26 @@
 // Offsets validation and planning on the GPU: the offsets never leave the
-// device.  The host reads back one small summary per call (the first rule an
-// offsets array breaks, in the order of the reference's host loop --
+// device.  The host reads back one small summary per validation (the first
+// rule an offsets array breaks, in the order of the reference's host loop --
 // python/swage/_segmented_qualification.py:30-55 -- plus a content hash, the
-// last offset, the length histogram and the bucket counts), and a second one
-// (three counters) when a reduce plan is built.
+// last offset, the length histogram and the class counts); building a plan
+// from validated offsets needs no further read-back.
 //
 // Reduce plan.  The host planner walks the segments one after the other; here
 // every tile is found independently (merge-path): the sequence of items --
-// per segment one header item, then its values -- is cut every kDeviceTile
-// items, a binary search over p(s) = offsets[s] + s finds the segment each
+// per segment kHeaderItems header items, then its values -- is cut every
+// kDeviceTile items, a binary search over p(s) = offsets[s] + kHeaderItems * s
+// finds the segment each
 // cut falls in, and a tile becomes one task of the same two kinds the host
 // planner emits: a packed run of segments whose first and last may be pieces
 // of segments that continue in the neighbouring tiles, or a chunk when the
-// whole tile lies inside one segment.  Every piece of a cut segment needs a
-// partial slot, contiguous per segment for the merge pass; with r(s) the rank
-// of s among the cut segments, the piece of s in tile t gets slot t + r(s):
-// consecutive tiles give consecutive slots, and the next cut segment starts
-// one slot further even when it shares a tile.  r comes from one prefix sum
-// over the tile boundaries (a boundary counts when the segment it cuts was
-// not already cut by the boundary before).
+// whole tile lies inside one segment.  A cut segment needs a partial slot per
+// piece; tile t owns slots 2t (for the piece of a segment that began before
+// it) and 2t + 1 (for the piece of a segment that goes on after it), so a
+// segment whose header lies in tile t0 has its pieces at 2*t0 + 1, 2*(t0+1),
+// 2*(t0+2), ...  The merge pass gets one record per tile: the segment that
+// begins a cut there (none: an empty record).  Every tile derives all of this
+// from the offsets alone -- no prefix sum, one kernel, nothing to bring to
+// the host.
 //
 // Softmax plan.  A stable partition of the non-empty segments into the length
 // classes (memory order inside a class): per-block class counts, a scan over
@@ -44,8 +46,6 @@ struct Summary {
   int softmax_count[kSoftmaxBuckets];
   int last_offset;
   int max_length;
-  // written by the boundary scan
-  int split_count, big_count, medium_count, pad;
 };
 
 // rules, in the order the host loop meets them at one index
@@ -86,7 +86,6 @@ summary_reset_kernel(Summary *summary) {
     summary->hash = 0;
     summary->last_offset = 0;
     summary->max_length = 0;
-    summary->split_count = summary->big_count = summary->medium_count = 0;
   }
   if (i < kHistogramBins) {
     summary->histogram[i] = 0;
@@ -182,190 +181,127 @@ validate_kernel(const int32_t *__restrict__ offsets, int32_t segment_count,
 // reduce plan
 // ---------------------------------------------------------------------------
 
-// Item position of segment s's header.
+// Item position of the first header item of segment s.
 __device__ __forceinline__ int64_t header_at(const int32_t *offsets,
                                              int64_t s) {
-  return (int64_t)__ldg(offsets + s) + s;
+  return (int64_t)__ldg(offsets + s) + kHeaderItems * s;
 }
 
-// Tile t starts at item t * kDeviceTile: the segment that item belongs to,
-// with bit 31 set when the item is one of its values (the segment began in an
-// earlier tile: the boundary cuts it).
-__global__ void __launch_bounds__(256)
-tile_start_kernel(const int32_t *__restrict__ offsets, int32_t segment_count,
-                  int32_t tile_count, uint32_t *__restrict__ start) {
-  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= tile_count) return;
-  const int64_t d = t * kDeviceTile;
+// The tile boundary at item d: the segment that item belongs to, whether the
+// boundary cuts it (the item is not the first of its header: the segment began
+// before d), and the first value at or behind the boundary.
+struct Boundary {
+  int32_t seg;
+  bool cut;
+  int64_t value;
+};
+
+__device__ __forceinline__ Boundary boundary_at(const int32_t *offsets,
+                                                int32_t segment_count,
+                                                int64_t d) {
   int64_t lo = 0, hi = (int64_t)segment_count - 1;  // header_at(lo) <= d
   while (lo < hi) {
     const int64_t mid = (lo + hi + 1) >> 1;
     if (header_at(offsets, mid) <= d) lo = mid;
     else hi = mid - 1;
   }
-  const bool cut = d > header_at(offsets, lo);
-  start[t] = (uint32_t)lo | (cut ? 0x80000000u : 0u);
+  const int64_t begin = __ldg(offsets + lo);
+  const int64_t past_header = d - (begin + kHeaderItems * lo) - kHeaderItems;
+  // a boundary inside the header leaves the whole segment behind it (its
+  // piece before the boundary is empty)
+  return Boundary{(int32_t)lo, d > begin + kHeaderItems * lo,
+                  begin + (past_header > 0 ? past_header : 0)};
 }
 
-struct Boundary {
-  bool first_cut;  // the segment this boundary cuts was not cut before it
-  int pieces;      // then: pieces of that segment
-};
-
-__device__ __forceinline__ Boundary
-boundary_at(const uint32_t *__restrict__ start,
-            const int32_t *__restrict__ offsets, int64_t t) {
-  Boundary b{false, 0};
-  if (t == 0) return b;
-  const uint32_t here = start[t], before = start[t - 1];
-  if (!(here >> 31)) return b;
-  if ((before >> 31) && ((before ^ here) & 0x7fffffffu) == 0) return b;
-  const int64_t seg = here & 0x7fffffffu;
-  // the segment's last item: its last value (or its header when empty, but an
-  // empty segment is never cut)
-  const int64_t last_item = (int64_t)__ldg(offsets + seg + 1) + seg;
-  b.first_cut = true;
-  b.pieces = (int)(last_item / kDeviceTile - t + 2);
-  return b;
+// Tile holding the first header item of segment s / its last value.
+__device__ __forceinline__ int64_t first_tile(const int32_t *offsets,
+                                              int64_t s) {
+  return header_at(offsets, s) / kDeviceTile;
+}
+__device__ __forceinline__ int64_t last_tile(const int32_t *offsets,
+                                             int64_t s) {
+  return ((int64_t)__ldg(offsets + s + 1) + kHeaderItems * s +
+          (kHeaderItems - 1)) /
+         kDeviceTile;
 }
 
-// One CTA: inclusive counts, per boundary, of first cuts (all / big / medium).
-// The CTA walks the boundaries kScanThreads at a time (coalesced), scans the
-// three flags of a batch with warp shuffles and carries the running totals.
-constexpr int kScanThreads = 1024;
-
-__global__ void __launch_bounds__(kScanThreads)
-boundary_scan_kernel(const uint32_t *__restrict__ start,
-                     const int32_t *__restrict__ offsets, int32_t tile_count,
-                     int32_t *__restrict__ cuts, int32_t *__restrict__ bigs,
-                     int32_t *__restrict__ mediums, Summary *summary) {
-  __shared__ int warp_totals[3][kScanThreads / 32];
-  __shared__ int carry[3];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid < 3) carry[tid] = 0;
-  __syncthreads();
-  for (int64_t base = 0; base < tile_count; base += kScanThreads) {
-    const int64_t t = base + tid;
-    int v[3] = {0, 0, 0};
-    if (t < tile_count) {
-      const Boundary b = boundary_at(start, offsets, t);
-      if (b.first_cut) {
-        v[0] = 1;
-        v[1] = b.pieces >= kBigSplit;
-        v[2] = b.pieces < kBigSplit && b.pieces > kTinySplit;
-      }
-    }
-    // inclusive scan inside the warp
-#pragma unroll
-    for (int k = 0; k < 3; ++k) {
-#pragma unroll
-      for (int delta = 1; delta < 32; delta <<= 1) {
-        const int up = __shfl_up_sync(kFullMask, v[k], delta);
-        if (lane >= delta) v[k] += up;
-      }
-      if (lane == 31) warp_totals[k][warp] = v[k];
-    }
-    __syncthreads();
-    if (warp == 0) {
-#pragma unroll
-      for (int k = 0; k < 3; ++k) {
-        int w = warp_totals[k][lane];
-#pragma unroll
-        for (int delta = 1; delta < 32; delta <<= 1) {
-          const int up = __shfl_up_sync(kFullMask, w, delta);
-          if (lane >= delta) w += up;
-        }
-        warp_totals[k][lane] = w;  // inclusive over the warps
-      }
-    }
-    __syncthreads();
-    int before[3];
-#pragma unroll
-    for (int k = 0; k < 3; ++k)
-      before[k] = carry[k] + (warp > 0 ? warp_totals[k][warp - 1] : 0);
-    if (t < tile_count) {
-      cuts[t] = before[0] + v[0];
-      bigs[t] = before[1] + v[1];
-      mediums[t] = before[2] + v[2];
-    }
-    __syncthreads();
-    if (tid < 3) carry[tid] += warp_totals[tid][kScanThreads / 32 - 1];
-    __syncthreads();
-  }
-  if (tid == 0) {
-    summary->split_count = carry[0];
-    summary->big_count = carry[1];
-    summary->medium_count = carry[2];
-  }
-}
-
-// One thread per tile: its task, and the merge-list entry of the segment its
-// left boundary cuts for the first time.
+// One thread per tile: its task and its merge record.  counts[0] += chunk
+// tasks, counts[1] += cut segments (statistics only; one atomic per warp).
+// A segment of more than kWarpMerge pieces spans more than kWarpMerge tiles,
+// so there are fewer than tiles / kWarpMerge + 1 of them: the capacity of
+// `bigs`.
 __global__ void __launch_bounds__(256)
-tile_emit_kernel(const int32_t *__restrict__ offsets, int32_t segment_count,
-                 int32_t tile_count, const uint32_t *__restrict__ start,
-                 const int32_t *__restrict__ cuts,
-                 const int32_t *__restrict__ bigs,
-                 const int32_t *__restrict__ mediums,
-                 const Summary *__restrict__ summary, Task *__restrict__ tasks,
-                 SplitSegment *__restrict__ splits) {
+tile_plan_kernel(const int32_t *__restrict__ offsets, int32_t segment_count,
+                 int32_t tile_count, Task *__restrict__ tasks,
+                 MergeRecord *__restrict__ merges,
+                 MergeRecord *__restrict__ bigs, int32_t big_capacity,
+                 int32_t *__restrict__ big_count,
+                 unsigned long long *__restrict__ counts) {
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= tile_count) return;
-  const uint32_t here = start[t];
-  const int32_t first = (int32_t)(here & 0x7fffffffu);
-  const bool head_cut = (here >> 31) != 0;
-  const int64_t d = t * kDeviceTile;
-  const int64_t vbegin = head_cut ? d - first - 1 : d - first;
-  int32_t last;
-  bool tail_cut;
-  int64_t vend;
-  if (t + 1 < tile_count) {
-    const uint32_t next = start[t + 1];
-    const int32_t next_first = (int32_t)(next & 0x7fffffffu);
-    tail_cut = (next >> 31) != 0;
-    last = tail_cut ? next_first : next_first - 1;
-    const int64_t d1 = d + kDeviceTile;
-    vend = tail_cut ? d1 - next_first - 1 : d1 - next_first;
-  } else {
-    tail_cut = false;
-    last = segment_count - 1;
-    vend = __ldg(offsets + segment_count);
-  }
-  const int32_t head_slot = head_cut ? (int32_t)(t + cuts[t] - 1) : -1;
-  const int32_t tail_slot = tail_cut ? (int32_t)(t + cuts[t + 1] - 1) : -1;
-  Task task;
-  task.vbegin = (int32_t)vbegin;
-  task.reserved0 = task.reserved1 = 0;
-  if (first == last && head_cut && tail_cut) {
+  bool is_chunk = false, opens_cut = false;
+  if (t < tile_count) {
+    const int64_t d = t * kDeviceTile;
+    const Boundary here = boundary_at(offsets, segment_count, d);
+    const int32_t first = here.seg;
+    const bool head_cut = here.cut;
+    const int64_t vbegin = here.value;
+    int32_t last;
+    bool tail_cut;
+    int64_t vend;
+    if (t + 1 < tile_count) {
+      const int64_t d1 = d + kDeviceTile;
+      const Boundary next = boundary_at(offsets, segment_count, d1);
+      tail_cut = next.cut;
+      last = tail_cut ? next.seg : next.seg - 1;
+      vend = next.value;
+    } else {
+      tail_cut = false;
+      last = segment_count - 1;
+      vend = __ldg(offsets + segment_count);
+    }
+    Task task;
     task.seg = first;
-    task.count = head_slot;  // == tail_slot: one piece, one slot
-    task.vcount_kind = (uint32_t)(vend - vbegin) | (kTaskChunk << 28);
-    task.head_slot = task.tail_slot = -1;
-  } else {
-    task.seg = first;
-    task.count = last - first + 1;
-    task.vcount_kind = (uint32_t)(vend - vbegin) | (kTaskPack << 28);
-    task.head_slot = head_slot;
-    task.tail_slot = tail_slot;
+    task.vbegin = (int32_t)vbegin;
+    if (first == last && head_cut && tail_cut) {
+      // the whole tile lies inside one segment: piece t - t0 of it
+      const int64_t t0 = first_tile(offsets, first);
+      task.count = (int32_t)(2 * t);
+      task.vcount_kind = (uint32_t)(vend - vbegin) | (kTaskChunk << 28);
+      task.head_slot = task.tail_slot = -1;
+      task.link_first = (int32_t)(2 * t0 + 1);
+      task.link_pieces = (int32_t)(last_tile(offsets, first) - t0 + 1);
+      is_chunk = true;
+    } else {
+      task.count = last - first + 1;
+      task.vcount_kind = (uint32_t)(vend - vbegin) | (kTaskPack << 28);
+      task.head_slot = head_cut ? (int32_t)(2 * t) : -1;
+      task.tail_slot = tail_cut ? (int32_t)(2 * t + 1) : -1;
+      task.link_first =
+          head_cut ? (int32_t)(2 * first_tile(offsets, first) + 1) : -1;
+      task.link_pieces =
+          tail_cut ? (int32_t)(last_tile(offsets, last) - t + 1) : 0;
+      opens_cut = tail_cut;
+    }
+    tasks[t] = task;
+    MergeRecord record{0, 0, 0, 0};
+    if (opens_cut) {
+      record.seg = last;
+      record.first = task.tail_slot;
+      record.pieces = task.link_pieces;
+      // the few segments of very many pieces are also listed apart: the
+      // merge pass gives each of them a CTA (any order: they are independent)
+      if (record.pieces > kWarpMerge) {
+        const int32_t at = atomicAdd(big_count, 1);
+        if (at < big_capacity) bigs[at] = record;
+      }
+    }
+    merges[t] = record;
   }
-  tasks[t] = task;
-
-  const Boundary b = boundary_at(start, offsets, t);
-  if (b.first_cut) {
-    const int32_t rank = cuts[t] - 1;
-    int32_t where;
-    if (b.pieces >= kBigSplit) where = bigs[t] - 1;
-    else if (b.pieces > kTinySplit)
-      where = summary->big_count + mediums[t] - 1;
-    else
-      where = summary->big_count + summary->medium_count +
-              (cuts[t] - bigs[t] - mediums[t]) - 1;
-    SplitSegment s;
-    s.seg = first;
-    s.slot_begin = (int32_t)(t - 1) + rank;
-    s.slot_count = b.pieces;
-    s.pad = 0;
-    splits[where] = s;
+  const unsigned chunks = __ballot_sync(kFullMask, is_chunk);
+  const unsigned cuts = __ballot_sync(kFullMask, opens_cut);
+  if ((threadIdx.x & 31) == 0) {
+    if (chunks) atomicAdd(counts, (unsigned long long)__popc(chunks));
+    if (cuts) atomicAdd(counts + 1, (unsigned long long)__popc(cuts));
   }
 }
 
@@ -373,6 +309,7 @@ tile_emit_kernel(const int32_t *__restrict__ offsets, int32_t segment_count,
 // softmax plan
 // ---------------------------------------------------------------------------
 constexpr int kListBlock = 1024;  // segments ranked by one warp
+constexpr int kScanThreads = 1024;
 
 struct BucketBegins {
   int32_t begin[kSoftmaxBuckets];
@@ -467,6 +404,10 @@ struct Scratch {
   bool ready = false;
   Summary *device = nullptr;
   Summary *host = nullptr;  // pinned
+  // which array the summary in `host` describes (nullptr: none)
+  const int32_t *seen_offsets = nullptr;
+  int32_t seen_segments = 0;
+  int32_t seen_values = 0;
 };
 std::mutex g_scratch_lock;
 Scratch g_scratch[64];
@@ -498,6 +439,7 @@ int rule_to_reason(unsigned rule) {
 cudaError_t summarise(const int32_t *offsets, int32_t segment_count,
                       int32_t value_count, int sm_count, cudaStream_t stream,
                       Scratch *scratch) {
+  scratch->seen_offsets = nullptr;
   summary_reset_kernel<<<1, 256, 0, stream>>>(scratch->device);
   int64_t grid = ((int64_t)segment_count + 1 + 255) / 256;
   const int64_t cap = (int64_t)sm_count * 8;
@@ -509,10 +451,59 @@ cudaError_t summarise(const int32_t *offsets, int32_t segment_count,
   e = cudaMemcpyAsync(scratch->host, scratch->device, sizeof(Summary),
                       cudaMemcpyDeviceToHost, stream);
   if (e != cudaSuccess) return e;
-  return cudaStreamSynchronize(stream);
+  e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return e;
+  scratch->seen_offsets = offsets;
+  scratch->seen_segments = segment_count;
+  scratch->seen_values = value_count;
+  return cudaSuccess;
 }
 
+// Plan blocks come from the device's default stream-ordered pool, told once
+// to keep what is freed: after the first plans a new one costs no cudaMalloc
+// (and none of its implicit synchronisation).
+bool g_pool_ready[64] = {false};
+std::mutex g_pool_lock;
+
 }  // namespace
+
+cudaError_t plan_block_allocate(DevicePlan *dev, size_t bytes,
+                                cudaStream_t stream) {
+  {
+    std::lock_guard<std::mutex> guard(g_pool_lock);
+    if (!g_pool_ready[dev->device]) {
+      cudaMemPool_t pool;
+      cudaError_t e = cudaDeviceGetDefaultMemPool(&pool, dev->device);
+      if (e != cudaSuccess) return e;
+      unsigned long long keep = ~0ull;
+      e = cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+      if (e != cudaSuccess) return e;
+      g_pool_ready[dev->device] = true;
+    }
+  }
+  dev->block = nullptr;
+  dev->block_bytes = 0;
+  if (bytes == 0) return cudaSuccess;
+  const cudaError_t e = cudaMallocAsync(&dev->block, bytes, stream);
+  if (e != cudaSuccess) return e;
+  dev->block_bytes = bytes;
+  dev->pooled = true;
+  return cudaSuccess;
+}
+
+void plan_block_release(DevicePlan *dev, cudaStream_t after, bool ordered) {
+  if (dev->block == nullptr) return;
+  // stream-ordered behind the plan's last launch when every launch went to
+  // one stream; otherwise (or if that stream is gone) a synchronising free
+  cudaError_t e = cudaErrorUnknown;
+  if (dev->pooled && ordered) e = cudaFreeAsync(dev->block, after);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(dev->block);
+  }
+  dev->block = nullptr;
+  dev->block_bytes = 0;
+}
 
 cudaError_t device_validate(const int32_t *offsets, int32_t segment_count,
                             int32_t value_count, int device, int sm_count,
@@ -540,18 +531,82 @@ cudaError_t device_validate(const int32_t *offsets, int32_t segment_count,
   return cudaSuccess;
 }
 
+namespace {
+
+constexpr size_t aligned256(size_t bytes) { return (bytes + 255) / 256 * 256; }
+
+// Carves the plan's block: padded offsets copy, control words (and the
+// planner's two counters), tasks, merge records, partials.  What a launch
+// expects to find at zero is cleared on `stream`; nothing here synchronises.
+cudaError_t reduce_block(DevicePlan *dev, const int32_t *offsets,
+                         int64_t tiles, cudaStream_t stream) {
+  const size_t noffsets = (size_t)dev->segment_count + 1;
+  const size_t padded = ((noffsets + 3) / 4) * 4 + 4;
+  const size_t slots = (size_t)tiles * 2;
+  const size_t offsets_bytes = aligned256(padded * sizeof(int32_t));
+  const size_t control_bytes = aligned256(kControlWords * sizeof(uint32_t) +
+                                          2 * sizeof(unsigned long long) +
+                                          sizeof(int32_t));
+  const size_t big_capacity = (size_t)tiles / kWarpMerge + 1;
+  const size_t big_bytes = aligned256(big_capacity * sizeof(MergeRecord));
+  const size_t task_bytes = aligned256((size_t)tiles * sizeof(Task));
+  const size_t merge_bytes = aligned256((size_t)tiles * sizeof(MergeRecord));
+  const size_t slot_bytes = aligned256(slots * sizeof(float));
+  cudaError_t e = plan_block_allocate(
+      dev,
+      offsets_bytes + control_bytes + task_bytes + merge_bytes + big_bytes +
+          slot_bytes,
+      stream);
+  if (e != cudaSuccess) return e;
+  unsigned char *at = static_cast<unsigned char *>(dev->block);
+  dev->offsets = reinterpret_cast<int32_t *>(at);
+  at += offsets_bytes;
+  dev->control = reinterpret_cast<uint32_t *>(at);
+  dev->counts = reinterpret_cast<int64_t *>(dev->control + kControlWords);
+  dev->big_count = reinterpret_cast<int32_t *>(dev->counts + 2);
+  at += control_bytes;
+  dev->tasks = reinterpret_cast<Task *>(at);
+  at += task_bytes;
+  dev->merges = reinterpret_cast<MergeRecord *>(at);
+  dev->merge_count = (int32_t)tiles;
+  at += merge_bytes;
+  dev->bigs = reinterpret_cast<MergeRecord *>(at);
+  dev->big_capacity = tiles > 0 ? (int32_t)big_capacity : 0;
+  at += big_bytes;
+  dev->partials = reinterpret_cast<float *>(at);
+  dev->partial_slots = (int32_t)slots;
+  dev->slot_step = 2;
+  e = cudaMemsetAsync(dev->offsets + noffsets, 0,
+                      (padded - noffsets) * sizeof(int32_t), stream);
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(dev->offsets, offsets, noffsets * sizeof(int32_t),
+                        cudaMemcpyDeviceToDevice, stream);
+  if (e == cudaSuccess)
+    e = cudaMemsetAsync(dev->control, 0, control_bytes, stream);
+  return e;
+}
+
+}  // namespace
+
 cudaError_t device_plan(const int32_t *offsets, int32_t segment_count,
                         int32_t value_count, int op, cudaStream_t stream,
-                        DevicePlan *dev, HostPlan *host, int32_t *reason,
-                        int64_t *index) {
+                        const unsigned long long *known_hash, DevicePlan *dev,
+                        HostPlan *host, int32_t *reason, int64_t *index) {
   std::lock_guard<std::mutex> guard(g_scratch_lock);
   Scratch *scratch = nullptr;
   cudaError_t e = scratch_for(dev->device, &scratch);
   if (e != cudaSuccess) return e;
-  e = summarise(offsets, segment_count, value_count, dev->sm_count, stream,
-                scratch);
-  if (e != cudaSuccess) return e;
-  Summary &s = *scratch->host;
+  const bool reusable =
+      known_hash != nullptr && scratch->seen_offsets == offsets &&
+      scratch->seen_segments == segment_count &&
+      scratch->seen_values == value_count &&
+      scratch->host->hash == *known_hash;
+  if (!reusable) {
+    e = summarise(offsets, segment_count, value_count, dev->sm_count, stream,
+                  scratch);
+    if (e != cudaSuccess) return e;
+  }
+  const Summary &s = *scratch->host;
   if (s.first_bad != kNoViolation) {
     *reason = rule_to_reason((unsigned)(s.first_bad & 7u));
     *index = (int64_t)(s.first_bad >> 3);
@@ -572,23 +627,6 @@ cudaError_t device_plan(const int32_t *offsets, int32_t segment_count,
   }
   dev->segment_count = segment_count;
 
-  // an aligned, padded copy of the offsets for the tile kernels' bulk copies
-  const size_t noffsets = (size_t)segment_count + 1;
-  const size_t padded = ((noffsets + 3) / 4) * 4 + 4;
-  e = cudaMalloc((void **)&dev->offsets, padded * sizeof(int32_t));
-  if (e != cudaSuccess) return e;
-  e = cudaMemsetAsync(dev->offsets + noffsets, 0,
-                      (padded - noffsets) * sizeof(int32_t), stream);
-  if (e != cudaSuccess) return e;
-  e = cudaMemcpyAsync(dev->offsets, offsets, noffsets * sizeof(int32_t),
-                      cudaMemcpyDeviceToDevice, stream);
-  if (e != cudaSuccess) return e;
-  e = cudaMalloc((void **)&dev->control, kControlWords * sizeof(uint32_t));
-  if (e != cudaSuccess) return e;
-  e = cudaMemsetAsync(dev->control, 0, kControlWords * sizeof(uint32_t),
-                      stream);
-  if (e != cudaSuccess) return e;
-
   if (op == SWG_OP_SOFTMAX) {
     host->schedule = SWG_SCHED_SPLIT;
     int64_t total = 0;
@@ -599,14 +637,22 @@ cudaError_t device_plan(const int32_t *offsets, int32_t segment_count,
       dev->softmax_count[b] = host->softmax_count[b] = s.softmax_count[b];
       total += s.softmax_count[b];
     }
-    if (total == 0) return cudaStreamSynchronize(stream);
+    // one block: control words, the class lists, the planner's block counts
     const int32_t blocks = (segment_count + kListBlock - 1) / kListBlock;
-    int32_t *counts = nullptr;
-    e = cudaMalloc((void **)&dev->softmax_segments, total * sizeof(int32_t));
+    const size_t control_bytes = aligned256(kControlWords * sizeof(uint32_t));
+    const size_t list_bytes = aligned256((size_t)total * sizeof(int32_t));
+    const size_t count_bytes =
+        aligned256((size_t)blocks * kSoftmaxBuckets * sizeof(int32_t));
+    e = plan_block_allocate(dev, control_bytes + list_bytes + count_bytes,
+                            stream);
     if (e != cudaSuccess) return e;
-    e = cudaMalloc((void **)&counts,
-                   (size_t)blocks * kSoftmaxBuckets * sizeof(int32_t));
-    if (e != cudaSuccess) return e;
+    unsigned char *at = static_cast<unsigned char *>(dev->block);
+    dev->control = reinterpret_cast<uint32_t *>(at);
+    dev->softmax_segments = reinterpret_cast<int32_t *>(at + control_bytes);
+    int32_t *counts =
+        reinterpret_cast<int32_t *>(at + control_bytes + list_bytes);
+    e = cudaMemsetAsync(dev->control, 0, control_bytes, stream);
+    if (e != cudaSuccess || total == 0) return e;
     const unsigned grid = (unsigned)(((int64_t)blocks * 32 + 255) / 256);
     bucket_count_kernel<<<grid, 256, 0, stream>>>(offsets, segment_count,
                                                   blocks, counts);
@@ -614,60 +660,40 @@ cudaError_t device_plan(const int32_t *offsets, int32_t segment_count,
                                                                      counts);
     bucket_fill_kernel<<<grid, 256, 0, stream>>>(
         offsets, segment_count, blocks, counts, begins, dev->softmax_segments);
-    e = cudaGetLastError();
-    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
-    cudaFree(counts);
-    return e;
+    return cudaGetLastError();
   }
 
   host->schedule = choose_schedule(host->elements_in_bin, host->value_count,
                                    host->max_length, host->mean_length);
-  const int64_t items = (int64_t)s.last_offset + segment_count;
+  const int64_t items =
+      (int64_t)s.last_offset + (int64_t)kHeaderItems * segment_count;
   const int64_t tiles = (items + kDeviceTile - 1) / kDeviceTile;
   dev->task_count = (int32_t)tiles;
-  if (tiles == 0) return cudaStreamSynchronize(stream);
-  // one allocation for what the plan keeps (tasks, merge list, partials), one
-  // for what only the planner needs (tile starts and the three scans)
-  const size_t task_bytes = (size_t)tiles * sizeof(Task);
-  const size_t split_bytes = (size_t)tiles * sizeof(SplitSegment);
-  const size_t partial_bytes = (size_t)tiles * 2 * sizeof(float);
-  unsigned char *kept = nullptr, *scratch_block = nullptr;
-  e = cudaMalloc((void **)&kept, task_bytes + split_bytes + partial_bytes);
-  if (e != cudaSuccess) return e;
-  dev->tasks = reinterpret_cast<Task *>(kept);  // owns the block
-  dev->splits = reinterpret_cast<SplitSegment *>(kept + task_bytes);
-  dev->partials = reinterpret_cast<float *>(kept + task_bytes + split_bytes);
-  dev->shared_block = true;
-  e = cudaMalloc((void **)&scratch_block, (size_t)tiles * 4 * sizeof(int32_t));
-  if (e == cudaSuccess) {
-    uint32_t *start = reinterpret_cast<uint32_t *>(scratch_block);
-    int32_t *scans = reinterpret_cast<int32_t *>(scratch_block) + tiles;
-    const unsigned grid = (unsigned)((tiles + 255) / 256);
-    tile_start_kernel<<<grid, 256, 0, stream>>>(offsets, segment_count,
-                                                (int32_t)tiles, start);
-    boundary_scan_kernel<<<1, kScanThreads, 0, stream>>>(
-        start, offsets, (int32_t)tiles, scans, scans + tiles,
-        scans + 2 * tiles, scratch->device);
-    tile_emit_kernel<<<grid, 256, 0, stream>>>(
-        offsets, segment_count, (int32_t)tiles, start, scans, scans + tiles,
-        scans + 2 * tiles, scratch->device, dev->tasks, dev->splits);
-    e = cudaGetLastError();
-  }
-  if (e == cudaSuccess)
-    e = cudaMemcpyAsync(scratch->host, scratch->device, sizeof(Summary),
-                        cudaMemcpyDeviceToHost, stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
-  cudaFree(scratch_block);
-  if (e != cudaSuccess) return e;
-  dev->split_count = s.split_count;
-  dev->big_split_count = s.big_count;
-  dev->medium_split_count = s.medium_count;
-  dev->partial_slots = (int32_t)(tiles + s.split_count);
-  host->partial_slots = dev->partial_slots;
-  host->big_split_count = s.big_count;
-  host->medium_split_count = s.medium_count;
   host->task_total = tiles;
-  host->split_total = s.split_count;
+  host->slot_step = 2;
+  e = reduce_block(dev, offsets, tiles, stream);
+  if (e != cudaSuccess) return e;
+  host->partial_slots = dev->partial_slots;
+  if (tiles == 0) return cudaSuccess;
+  const unsigned grid = (unsigned)((tiles + 255) / 256);
+  tile_plan_kernel<<<grid, 256, 0, stream>>>(
+      offsets, segment_count, (int32_t)tiles, dev->tasks, dev->merges,
+      dev->bigs, dev->big_capacity, dev->big_count,
+      reinterpret_cast<unsigned long long *>(dev->counts));
+  return cudaGetLastError();
+}
+
+cudaError_t device_plan_counts(const DevicePlan &dev, int64_t *chunk_tasks,
+                               int64_t *split_segments) {
+  *chunk_tasks = *split_segments = 0;
+  if (dev.counts == nullptr) return cudaSuccess;
+  int64_t both[2] = {0, 0};
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess)
+    e = cudaMemcpy(both, dev.counts, sizeof(both), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return e;
+  *chunk_tasks = both[0];
+  *split_segments = both[1];
   return cudaSuccess;
 }
 

@@ -9,7 +9,8 @@
 namespace swg {
 
 constexpr int kTicketBase = 4;
-constexpr int kControlWords = kTicketBase + kSoftmaxBuckets + 4;  // 16
+constexpr int kStatusWord = kTicketBase + kSoftmaxBuckets;  // 12
+constexpr int kControlWords = kStatusWord + 4;              // 16
 
 // Device-resident part of a plan; every pointer is owned by the plan.
 struct DevicePlan {
@@ -19,18 +20,26 @@ struct DevicePlan {
   int32_t task_count = 0;
   int32_t segment_count = 0;
   int32_t *offsets = nullptr;      // aligned, padded copy of the CSR offsets
-  SplitSegment *splits = nullptr;
-  int32_t split_count = 0;
-  int32_t big_split_count = 0;     // leading splits that get a CTA each
-  int32_t medium_split_count = 0;  // then those that get a warp each
-  float *partials = nullptr;       // one float per partial slot
+  float *partials = nullptr;       // one float per partial slot of a cut segment
   int32_t partial_slots = 0;
+  int32_t slot_step = 1;           // see Task
+  MergeRecord *merges = nullptr;   // what the merge pass walks: cut segments
+  int32_t merge_count = 0;         // of up to kWarpMerge pieces (or empty)
+  MergeRecord *bigs = nullptr;     // and those with more, listed apart;
+  int32_t *big_count = nullptr;    // how many (device-resident)
+  int32_t big_capacity = 0;        // and how many the list can hold
   int32_t *softmax_segments = nullptr;  // bucketed segment ids
   int32_t softmax_begin[kSoftmaxBuckets] = {0};
   int32_t softmax_count[kSoftmaxBuckets] = {0};
   uint32_t *control = nullptr;     // [0] ticket, [1] finished, [2] error, [3] detail,
-                                   // [kTicketBase + class] softmax ticket counters
-  bool shared_block = false;       // tasks, splits and partials are one allocation
+                                   // [kTicketBase + class] softmax ticket counters,
+                                   // [kStatusWord, +1] address of the host-visible
+                                   // copy of the error word (0: none)
+  int64_t *counts = nullptr;       // device planner: {chunk tasks, cut segments}
+  void *block = nullptr;           // the one allocation the pointers above live in
+  size_t block_bytes = 0;
+  bool pooled = false;             // block came from the stream-ordered pool
+  uint32_t *host_status = nullptr; // pinned, device-visible: {error, detail}
 };
 
 // Optional pair of events recorded around the dominant kernel of a call.
@@ -64,18 +73,18 @@ cudaError_t launch_segreduce_sum_max(const float *values,
                                      float *out_max, int32_t value_count,
                                      int32_t segment_count, int sm_count,
                                      cudaStream_t stream, const Probe *probe);
-// One tile task per CTA + combine pass.
+// One tile task per warp, two per CTA + merge pass.
 cudaError_t launch_segreduce_split(int kind, const float *values, float *out,
                                    int32_t value_count, const DevicePlan &plan,
                                    cudaStream_t stream, const Probe *probe);
-// Persistent CTAs, bulk-copy ring, ticket counter + combine pass.
+// Persistent CTAs, bulk-copy ring, ticket counter + merge pass.
 cudaError_t launch_segreduce_persistent(int kind, const float *values,
                                         float *out, int32_t value_count,
                                         const DevicePlan &plan,
                                         cudaStream_t stream,
                                         const Probe *probe);
 // One resident CTA per SM, one stage per warp, tasks at a fixed stride +
-// combine pass.
+// merge pass.
 cudaError_t launch_segreduce_resident(int kind, const float *values,
                                       float *out, int32_t value_count,
                                       const DevicePlan &plan,
@@ -95,19 +104,30 @@ cudaError_t device_validate(const int32_t *offsets, int32_t segment_count,
                             int32_t value_count, int device, int sm_count,
                             cudaStream_t stream, int32_t *reason,
                             int64_t *index, DeviceDigest *digest);
-// Validates, then fills `dev` (device, sm_count preset by the caller) and the
-// summary fields of `host`.  *reason != SWG_OFFSETS_OK: nothing was planned.
+// Fills `dev` (device, sm_count preset by the caller) and the summary fields
+// of `host` for offsets that pass validation.  *reason != SWG_OFFSETS_OK:
+// nothing was planned.  With `known_hash` the summary of the validation pass
+// that returned this digest for the same array is reused when it is still the
+// latest one on the device (no second pass, no synchronisation); else the
+// pass runs here and `stream` is synchronised once to read it.
 cudaError_t device_plan(const int32_t *offsets, int32_t segment_count,
                         int32_t value_count, int op, cudaStream_t stream,
-                        DevicePlan *dev, HostPlan *host, int32_t *reason,
-                        int64_t *index);
+                        const unsigned long long *known_hash, DevicePlan *dev,
+                        HostPlan *host, int32_t *reason, int64_t *index);
+// Brings the device planner's task statistics to the host (synchronises).
+cudaError_t device_plan_counts(const DevicePlan &dev, int64_t *chunk_tasks,
+                               int64_t *split_segments);
+// Plan memory: one block per plan from the device's stream-ordered pool
+// (kept by the library between plans, so a new plan costs no cudaMalloc).
+cudaError_t plan_block_allocate(DevicePlan *dev, size_t bytes,
+                                cudaStream_t stream);
+void plan_block_release(DevicePlan *dev, cudaStream_t after, bool ordered);
 
 // Allocation-free variant: the split schedule run out of a fixed-size
 // file-scope device array.  Limits of that array:
 constexpr int kStaticMaxSegments = 1 << 18;
 constexpr int kStaticMaxTasks = 1 << 15;
 constexpr int kStaticMaxSlots = 1 << 15;
-constexpr int kStaticMaxSplits = 1 << 13;
 cudaError_t launch_segreduce_static(int kind, const float *values, float *out,
                                     int32_t value_count,
                                     const int32_t *host_offsets,

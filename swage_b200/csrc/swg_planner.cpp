@@ -95,8 +95,11 @@ struct Packer {
   HostPlan *plan;
   int32_t seg_begin = 0, nseg = 0, vbegin = 0, vcount = 0;
   int32_t head_slot = -1, tail_slot = -1;
+  int32_t head_first = -1, tail_pieces = 0;  // see Task::link_*
 
-  int32_t room() const { return kTileItems - (vcount + nseg); }
+  int32_t room() const {
+    return kTileItems - (vcount + kHeaderItems * nseg);
+  }
 
   void flush() {
     if (nseg == 0) return;
@@ -107,12 +110,14 @@ struct Packer {
     task.vcount_kind = (kTaskPack << 28) | (uint32_t)vcount;
     task.head_slot = head_slot;
     task.tail_slot = tail_slot;
-    task.reserved0 = task.reserved1 = 0;
+    task.link_first = head_first;
+    task.link_pieces = tail_pieces;
     plan->tasks.push_back(task);
     plan->pack_tasks++;
     nseg = 0;
     vcount = 0;
-    head_slot = tail_slot = -1;
+    head_slot = tail_slot = head_first = -1;
+    tail_pieces = 0;
   }
 
   // append `length` values of segment `seg` starting at value `start`
@@ -125,14 +130,17 @@ struct Packer {
     vcount += length;
   }
 
-  void chunk(int32_t seg, int32_t start, int32_t length, int32_t slot) {
+  // `first` / `pieces`: the slots of the segment this chunk is a piece of
+  void chunk(int32_t seg, int32_t start, int32_t length, int32_t slot,
+             int32_t first, int32_t pieces) {
     Task task;
     task.seg = seg;
     task.count = slot;
     task.vbegin = start;
     task.vcount_kind = (kTaskChunk << 28) | (uint32_t)length;
     task.head_slot = task.tail_slot = -1;
-    task.reserved0 = task.reserved1 = 0;
+    task.link_first = first;
+    task.link_pieces = pieces;
     plan->tasks.push_back(task);
     plan->chunk_tasks++;
   }
@@ -146,16 +154,16 @@ void plan_reduce(const int32_t *offsets, int32_t segment_count,
     const int32_t start = offsets[seg];
     const int32_t length = offsets[seg + 1] - start;
     if (packer.nseg >= kTileMaxSegments) packer.flush();
-    if (length + 1 <= packer.room()) {
+    if (length + kHeaderItems <= packer.room()) {
       packer.append(seg, start, length);
       continue;
     }
-    if (length <= kSplitMinimum || length + 1 <= kTileItems) {
+    if (length <= kSplitMinimum || length + kHeaderItems <= kTileItems) {
       // short: never cut.  Medium and the open tile nearly full: not worth
       // a cut either when the whole segment fits a tile and the open tile
       // has less than a useful piece of room.
       if (length <= kSplitMinimum ||
-          packer.room() - 1 < kSplitMinimumPiece) {
+          packer.room() - kHeaderItems < kSplitMinimumPiece) {
         packer.flush();
         packer.append(seg, start, length);
         continue;
@@ -165,8 +173,9 @@ void plan_reduce(const int32_t *offsets, int32_t segment_count,
     // tile, whole-tile chunks, and a head piece that opens the next tile.
     int32_t position = start, remaining = length;
     int32_t tail_piece = 0;
-    if (packer.nseg > 0 && packer.room() - 1 >= kSplitMinimumPiece)
-      tail_piece = packer.room() - 1;
+    if (packer.nseg > 0 &&
+        packer.room() - kHeaderItems >= kSplitMinimumPiece)
+      tail_piece = packer.room() - kHeaderItems;
     const int32_t after_tail = remaining - tail_piece;
     const int32_t whole_chunks = after_tail / kTileValues;
     const int32_t last_piece = after_tail - whole_chunks * kTileValues;
@@ -175,53 +184,39 @@ void plan_reduce(const int32_t *offsets, int32_t segment_count,
     if (pieces == 1) {
       // one chunk on its own (2032..2048 values): straight to out
       packer.flush();
-      packer.chunk(seg, start, length, -1);
+      packer.chunk(seg, start, length, -1, -1, 0);
       continue;
     }
-    SplitSegment split;
-    split.seg = seg;
-    split.slot_begin = plan->partial_slots;
-    split.slot_count = pieces;
-    split.pad = 0;
-    plan->splits.push_back(split);
-    int32_t slot = plan->partial_slots;
+    const int32_t first = plan->partial_slots;
+    int32_t slot = first;
     plan->partial_slots += pieces;
+    plan->split_segments++;
+    (pieces > kWarpMerge ? plan->big_merges : plan->merges)
+        .push_back(MergeRecord{seg, first, pieces, 0});
     if (tail_piece > 0) {
       packer.append(seg, position, tail_piece);
       packer.tail_slot = slot++;
+      packer.tail_pieces = pieces;
       position += tail_piece;
       remaining -= tail_piece;
     }
     packer.flush();
     for (int32_t c = 0; c < whole_chunks; ++c) {
-      packer.chunk(seg, position, kTileValues, slot++);
+      packer.chunk(seg, position, kTileValues, slot++, first, pieces);
       position += kTileValues;
       remaining -= kTileValues;
     }
     if (last_piece > 0) {
-      if (last_piece + 1 <= kTileItems) {
+      if (last_piece + kHeaderItems <= kTileItems) {
         packer.append(seg, position, last_piece);
         packer.head_slot = slot++;
+        packer.head_first = first;
       } else {
-        packer.chunk(seg, position, last_piece, slot++);
+        packer.chunk(seg, position, last_piece, slot++, first, pieces);
       }
     }
   }
   packer.flush();
-  // second pass: segments with many partials first (a CTA each), then the
-  // middle (a warp each), then those with a handful (a thread each)
-  auto big = [](const SplitSegment &split) {
-    return split.slot_count >= kBigSplit;
-  };
-  auto not_tiny = [](const SplitSegment &split) {
-    return split.slot_count > kTinySplit;
-  };
-  auto after_big =
-      std::stable_partition(plan->splits.begin(), plan->splits.end(), big);
-  auto after_medium =
-      std::stable_partition(after_big, plan->splits.end(), not_tiny);
-  plan->big_split_count = (int32_t)(after_big - plan->splits.begin());
-  plan->medium_split_count = (int32_t)(after_medium - after_big);
 }
 
 // Softmax: bucket the non-empty segments by length.  Inside a bucket segments
@@ -314,7 +309,7 @@ std::string describe_host_plan(const HostPlan &plan) {
            plan.mean_length, (long long)plan.max_length,
            plan.task_total >= 0 ? (size_t)plan.task_total : plan.tasks.size(),
            (long long)plan.pack_tasks, (long long)plan.chunk_tasks,
-           plan.split_total >= 0 ? (size_t)plan.split_total : plan.splits.size(),
+           (size_t)plan.split_segments,
            plan.partial_slots, kTileValues, kTileItems,
            kTileMaxSegments,
            kSplitMinimum, plan.softmax_count[0], plan.softmax_count[1],

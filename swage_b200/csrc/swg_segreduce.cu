@@ -1,19 +1,23 @@
-// Segmented sum / max over dense fp32 values addressed by CSR int32 offsets.
+// Segmented sum / max / min over dense fp32 values addressed by CSR int32
+// offsets.
 //
 // Replaces the kernels the reference generates in
 // lib/Conversion/SegmentedReduction/SegmentedReduction.cpp:185-283 (one
 // 128-thread CTA per segment, block-stride scalar loads, gpu.all_reduce).
-// Four schedules:
+// Schedules:
 //
 //   warp        one warp per segment, 128-bit loads straight from global
 //   cta         one CTA per segment (the reference's own mapping, vectorised)
-//   split       the plan's tile tasks, one per warp, eight per CTA; segments
-//               longer than a tile are chunked into partials and merged by a
-//               second pass
+//   split       the plan's tile tasks, one per warp, two per CTA
 //   persistent  the same tile tasks, drawn from a ticket counter by the
 //               warps of one resident CTA per SM; every warp keeps three
-//               tiles in flight in its own shared-memory ring, filled with
-//               bulk async copies (TMA), and reduces them as they land
+//               tiles in flight in its own shared-memory ring
+//   resident    the same tile tasks at a fixed stride per SM, one stage per
+//               warp of one resident CTA per SM
+//
+// The three tile schedules stage tiles with bulk async copies (TMA); segments
+// that cross a tile boundary leave partials that a small merge pass, launched
+// right behind the tile kernel, combines.
 //
 // All of them are HBM-bound: 4 bytes per value + 4 per offset + 4 per output.
 // No floating-point atomics anywhere: every result is produced by a fixed
@@ -114,13 +118,22 @@ __global__ void segreduce_cta_kernel(const float *__restrict__ values,
 }
 
 // ---------------------------------------------------------------------------
-// Tile tasks (split and persistent schedules)
+// Tile tasks (split, persistent and resident schedules)
 //
 // A task is small enough (kTileValues values, kTileMaxSegments segments) for
 // ONE WARP to own it from the bulk copy to the output store, so no CTA-wide
 // barrier appears anywhere: every warp runs its own copy -> wait -> reduce
 // pipeline on its own shared-memory stages and its own mbarriers, and the SM
 // overlaps the phases of its resident warps.
+//
+// A segment that crosses a tile boundary is cut into pieces that different
+// warps reduce; each piece leaves its partial in the plan's scratch and a
+// merge pass -- a second, small kernel launched right behind the tile kernel
+// -- combines the partials of every cut segment in slot order.  (Merging
+// inside the tile kernel, by whichever warp delivers a segment's last partial,
+// was built and measured: the device-wide fence each piece then needs before
+// it counts itself in costs 20 - 50 % of the kernel's throughput, far more
+// than the second launch.)
 // ---------------------------------------------------------------------------
 #ifndef SWG_WIDE_VECTOR
 #define SWG_WIDE_VECTOR 0  // 1: whole-warp segments of a packed tile by 128-bit loads
@@ -135,6 +148,7 @@ constexpr int kTileFloats = kTileValues + 8;
 constexpr int kStageBytes = ((kTileFloats * 4 + 127) / 128) * 128;
 static_assert(kTileItems + 3 + 3 + 8 <= kTileFloats,
               "values, padding and offsets of a packed task fit one stage");
+static_assert(kStatusWord == 12, "report() reads control[12..13]");
 
 // First tile slot of the offsets of a packed task: the 16-byte line after
 // its values.
@@ -146,6 +160,7 @@ constexpr uint32_t kTaskStop = 15u;  // sentinel kind: no more tasks
 #ifndef SWG_SPLIT_WARPS
 #define SWG_SPLIT_WARPS 2
 #endif
+
 constexpr int kSplitWarps = SWG_SPLIT_WARPS;  // split: tasks per CTA, one stage each
 
 struct Stage {
@@ -174,7 +189,8 @@ __device__ __forceinline__ Task stop_task() {
   t.vbegin = 0;
   t.vcount_kind = kTaskStop << 28;
   t.head_slot = t.tail_slot = -1;
-  t.reserved0 = t.reserved1 = 0;
+  t.link_first = -1;
+  t.link_pieces = 0;
   return t;
 }
 
@@ -191,7 +207,8 @@ __device__ __forceinline__ Task shuffle_task(const Task &mine, int src) {
   t.vcount_kind = __shfl_sync(kFullMask, mine.vcount_kind, src);
   t.head_slot = __shfl_sync(kFullMask, mine.head_slot, src);
   t.tail_slot = __shfl_sync(kFullMask, mine.tail_slot, src);
-  t.reserved0 = t.reserved1 = 0;
+  t.link_first = __shfl_sync(kFullMask, mine.link_first, src);
+  t.link_pieces = __shfl_sync(kFullMask, mine.link_pieces, src);
   return t;
 }
 
@@ -202,43 +219,90 @@ struct Limits {
   int32_t value_count;
   int32_t segment_count;
   int32_t partial_slots;
+  int32_t slot_step;
 };
 
-// Error codes left in control[2] (first one wins; control[3] = detail).
-constexpr uint32_t kErrTimeout = 1u, kErrBadTask = 2u, kErrBadSegment = 3u;
+// Slot of piece k of a segment whose piece 0 has slot `first` (see Task).
+__device__ __forceinline__ int piece_slot(int first, int k, int step) {
+  return first + k * step - (k > 0 ? step - 1 : 0);
+}
+__device__ __forceinline__ int piece_index(int first, int slot, int step) {
+  return slot == first ? 0 : (slot - first + step - 1) / step;
+}
 
-__device__ __forceinline__ void report(uint32_t *control, uint32_t code,
-                                       uint32_t detail) {
-  if (atomicCAS(control + 2, 0u, code) == 0u) atomicExch(control + 3, detail);
+// Slots first .. piece_slot(pieces - 1) lie inside the scratch.
+__device__ __forceinline__ bool slots_ok(int first, int pieces,
+                                         const Limits &limits) {
+  return first >= 0 && pieces >= 2 &&
+         (int64_t)first + (int64_t)(pieces - 1) * limits.slot_step <
+             (int64_t)limits.partial_slots + (limits.slot_step - 1);
 }
 
 __device__ __forceinline__ bool task_ok(const Task &t, const Limits &limits) {
   const uint32_t kind = t.vcount_kind >> 28;
   const int64_t vcount = (int64_t)(t.vcount_kind & kTaskCountMask);
+  const int step = limits.slot_step;
   if (t.seg < 0 || t.seg >= limits.segment_count) return false;
   if (t.vbegin < 0 || vcount > kTileValues ||
       (int64_t)t.vbegin + vcount > limits.value_count)
     return false;
-  if (kind == kTaskPack)
-    return t.count >= 1 && t.count <= kTileMaxSegments &&
-           vcount + t.count <= kTileItems &&
-           (int64_t)t.seg + t.count <= limits.segment_count &&
-           t.head_slot >= -1 && t.head_slot < limits.partial_slots &&
-           t.tail_slot >= -1 && t.tail_slot < limits.partial_slots &&
-           !(t.count == 1 && t.head_slot >= 0 && t.tail_slot >= 0);
-  if (kind == kTaskChunk)
-    return t.count >= -1 && t.count < limits.partial_slots;
+  if (kind == kTaskPack) {
+    if (!(t.count >= 1 && t.count <= kTileMaxSegments &&
+          vcount + t.count <= kTileItems &&
+          (int64_t)t.seg + t.count <= limits.segment_count &&
+          t.head_slot >= -1 && t.head_slot < limits.partial_slots &&
+          t.tail_slot >= -1 && t.tail_slot < limits.partial_slots &&
+          !(t.count == 1 && t.head_slot >= 0 && t.tail_slot >= 0)))
+      return false;
+    // the head piece is the last piece of a segment that began at link_first
+    if (t.head_slot >= 0 &&
+        !(t.link_first >= 0 && t.link_first < t.head_slot &&
+          piece_slot(t.link_first,
+                     piece_index(t.link_first, t.head_slot, step),
+                     step) == t.head_slot))
+      return false;
+    // the tail piece is piece 0 of a segment of link_pieces pieces
+    if (t.tail_slot >= 0 && !slots_ok(t.tail_slot, t.link_pieces, limits))
+      return false;
+    return true;
+  }
+  if (kind == kTaskChunk) {
+    if (t.count < 0) return t.count == -1;
+    if (t.count >= limits.partial_slots ||
+        !slots_ok(t.link_first, t.link_pieces, limits))
+      return false;
+    const int j = piece_index(t.link_first, t.count, step);
+    return j < t.link_pieces && piece_slot(t.link_first, j, step) == t.count;
+  }
   return false;
 }
 
-// Stage one task; runs entirely in the calling thread, so several lanes of a
-// producer warp can stage several tasks at once.  `mis` is the phase of the
-// values pointer inside a 16-byte line, in elements.  The bulk copy takes
-// every 16-byte line that intersects the task's value range and lies wholly
-// inside the values array (neighbouring elements that ride along are never
-// read); the at most three elements at either end of the array that no such
-// line covers are fetched with plain loads.  Element i lands at
-// tile[i - origin] with origin = vbegin - ((vbegin + mis) & 3).
+// The lines of `values` a task's bulk copy takes: every 16-byte line that
+// intersects the task's value range and lies wholly inside the values array
+// (neighbouring elements that ride along are never read).  Element i lands at
+// tile[i - origin] with origin = vbegin - ((vbegin + mis) & 3); `mis` is the
+// phase of the values pointer inside a 16-byte line, in elements.
+struct CopyRange {
+  int64_t origin, lo, hi;  // copy [lo, hi); hi <= lo: nothing to copy
+};
+
+__device__ __forceinline__ CopyRange copy_range(const Task &task, int mis,
+                                                int32_t value_count) {
+  const int64_t vb = task.vbegin;
+  const int64_t ve = vb + (int64_t)(task.vcount_kind & kTaskCountMask);
+  CopyRange r;
+  r.origin = vb - ((vb + mis) & 3);
+  r.lo = r.origin < 0 ? r.origin + 4 : r.origin;
+  r.hi = ve + ((4 - ((ve + mis) & 3)) & 3);
+  const int64_t last_line = (int64_t)value_count - ((value_count + mis) & 3);
+  if (r.hi > last_line) r.hi = last_line;
+  if (r.hi < r.lo) r.hi = r.lo;
+  return r;
+}
+
+// Stage one task; runs entirely in the calling thread.  The at most three
+// elements at either end of the array that no whole line covers are fetched
+// with plain loads.
 __device__ __forceinline__ void issue_task(const Task &task,
                                            const float *__restrict__ values,
                                            int mis, int32_t value_count,
@@ -247,12 +311,8 @@ __device__ __forceinline__ void issue_task(const Task &task,
   const uint32_t kind = task.vcount_kind >> 28;
   const int64_t vb = task.vbegin;
   const int64_t ve = vb + (int64_t)(task.vcount_kind & kTaskCountMask);
-  const int64_t origin = vb - ((vb + mis) & 3);
-  int64_t lo = origin < 0 ? origin + 4 : origin;
-  int64_t hi = ve + ((4 - ((ve + mis) & 3)) & 3);
-  const int64_t last_line = (int64_t)value_count - ((value_count + mis) & 3);
-  if (hi > last_line) hi = last_line;
-  if (hi < lo) hi = lo;
+  const CopyRange r = copy_range(task, mis, value_count);
+  const int64_t origin = r.origin, lo = r.lo, hi = r.hi;
   if (lo > vb || hi < ve) {
     // only the first and the last task of an array can get here
     for (int64_t idx = vb; idx < ve && idx < lo; ++idx)
@@ -278,6 +338,15 @@ __device__ __forceinline__ void issue_task(const Task &task,
              d_off + o_lo, bytes_o, full);
 }
 
+// 128-bit load from a stage, explicitly in the shared window.
+__device__ __forceinline__ float4 lds4(const float4 *p) {
+  float4 q;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(q.x), "=f"(q.y), "=f"(q.z), "=f"(q.w)
+               : "r"(smem_u32(p)));
+  return q;
+}
+
 // Warp-collective: reduces tile[lo, hi) -- scalar ends, 128-bit body, four
 // independent accumulators per lane -- and returns the result to every lane.
 template <class Op>
@@ -293,14 +362,14 @@ __device__ __forceinline__ float warp_range(const float *tile, int lo, int hi,
   const int vlo = blo >> 2, vhi = bhi >> 2;
   int v = vlo + lane;
   for (; v + 96 < vhi; v += 128) {
-    const float4 q0 = body[v], q1 = body[v + 32], q2 = body[v + 64],
-                 q3 = body[v + 96];
+    const float4 q0 = lds4(body + v), q1 = lds4(body + v + 32),
+                 q2 = lds4(body + v + 64), q3 = lds4(body + v + 96);
     a0 = fold4<Op>(a0, q0);
     a1 = fold4<Op>(a1, q1);
     a2 = fold4<Op>(a2, q2);
     a3 = fold4<Op>(a3, q3);
   }
-  for (; v < vhi; v += 32) a0 = fold4<Op>(a0, body[v]);
+  for (; v < vhi; v += 32) a0 = fold4<Op>(a0, lds4(body + v));
   const int tail = bhi > head_end ? bhi : head_end;
   if (tail + lane < hi) a1 = Op::apply(a1, tile[tail + lane]);
   return warp_reduce<Op>(Op::apply(Op::apply(a0, a1), Op::apply(a2, a3)));
@@ -372,8 +441,28 @@ __device__ __forceinline__ void process_task(const Task &task,
     const bool medium =
         valid && length > kLaneSegment && length <= kGroupSegment;
     const bool wide = valid && length > kGroupSegment;
-    if (valid && length <= kLaneSegment)
-      for (int i = a; i < b; ++i) acc = Op::apply(acc, tile[i]);
+    // tiny segments: the loads are issued eight at a time under a predicate
+    // (independent of one another) and folded left to right; slots past the
+    // segment's end hold the identity, which leaves the result unchanged
+    const bool tiny = valid && length <= kLaneSegment;
+    if (tiny) {
+      float x[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        x[i] = a + i < b ? tile[a + i] : Op::identity();
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc = Op::apply(acc, x[i]);
+    }
+    if (__any_sync(kFullMask, tiny && length > 8)) {
+      if (tiny) {
+        float x[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          x[i] = a + 8 + i < b ? tile[a + 8 + i] : Op::identity();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = Op::apply(acc, x[i]);
+      }
+    }
     const unsigned medium_mask = __ballot_sync(kFullMask, medium);
     const unsigned wide_mask = __ballot_sync(kFullMask, wide);
     float *target = out + task.seg + k;
@@ -443,6 +532,15 @@ __device__ __forceinline__ void process_task(const Task &task,
 }
 
 // split schedule: CTA b, warp w reduces task b * kSplitWarps + w.
+//
+// Launched with programmatic stream serialisation.  Everything before
+// griddepcontrol.wait (CTA placement, barrier set-up, the descriptor round
+// trip) touches only memory the plan owns and may overlap the tail of the
+// kernel before; the CTAs of the first wave (blockIdx < prefetch_ctas) also
+// ask L2 to fetch their tile there, so that the first copies of the launch
+// find their lines on the way instead of starting a cold DRAM round trip
+// after the wait.  The caller's arrays are read into the SM and written only
+// after the kernel before has finished.
 template <class Op>
 __global__ void __launch_bounds__(kSplitWarps * 32)
 segreduce_split_kernel(const float *__restrict__ values,
@@ -450,14 +548,16 @@ segreduce_split_kernel(const float *__restrict__ values,
                        const Task *__restrict__ tasks, int32_t task_count,
                        const int32_t *__restrict__ d_off,
                        float *__restrict__ partials,
-                       uint32_t *__restrict__ control, Limits limits) {
+                       uint32_t *__restrict__ control, Limits limits,
+                       uint32_t prefetch_ctas) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full[kSplitWarps];
   __shared__ WarpScratch scratch[kSplitWarps];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int mis = (int)(((uintptr_t)values >> 2) & 3);
-  // let the merge kernel that follows be placed as soon as slots free up; it
-  // waits for this grid to finish before it reads a partial
+  // let the kernel that follows in the stream be placed as soon as slots free
+  // up; it waits for this grid to finish before it touches anything of the
+  // caller's
   asm volatile("griddepcontrol.launch_dependents;");
   const int64_t index = (int64_t)blockIdx.x * kSplitWarps + warp;
   if (index >= task_count) return;
@@ -468,12 +568,14 @@ segreduce_split_kernel(const float *__restrict__ values,
   __syncwarp();
   const Task task = tasks[index];
   const Stage stage = stage_at(smem, warp);
-  // Launched with programmatic stream serialisation: everything up to here
-  // (CTA placement, barrier set-up, the descriptor round trip) touches only
-  // memory the plan owns and may overlap the tail of the kernel before; the
-  // caller's arrays are read and written only after that kernel has finished.
+  const bool ok = task_ok(task, limits);
+  if (ok && lane == 0 && blockIdx.x < prefetch_ctas) {
+    const CopyRange r = copy_range(task, mis, value_count);
+    if (r.hi > r.lo)
+      bulk_prefetch_l2(values + r.lo, (uint32_t)(r.hi - r.lo) * 4u);
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (!task_ok(task, limits)) {
+  if (!ok) {
     if (lane == 0) report(control, kErrBadTask, (uint32_t)index);
     return;
   }
@@ -503,7 +605,7 @@ segreduce_persistent_kernel(const float *__restrict__ values,
                             float *__restrict__ out, int32_t value_count,
                             const Task *__restrict__ tasks, int32_t task_count,
                             const int32_t *__restrict__ d_off,
-                            float *__restrict__ partials,
+                       float *__restrict__ partials,
                             uint32_t *__restrict__ control, Limits limits) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full[kWarps * kStages];
@@ -618,7 +720,7 @@ segreduce_resident_kernel(const float *__restrict__ values,
                           float *__restrict__ out, int32_t value_count,
                           const Task *__restrict__ tasks, int32_t task_count,
                           const int32_t *__restrict__ d_off,
-                          float *__restrict__ partials,
+                       float *__restrict__ partials,
                           uint32_t *__restrict__ control, Limits limits) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full[kWarps];
@@ -643,6 +745,14 @@ segreduce_resident_kernel(const float *__restrict__ values,
   int64_t index = draw();
   if (index >= task_count) return;
   Task task = tasks[index];
+  // the first tile of every warp: L2 starts fetching it while the kernel
+  // before this one drains (see segreduce_split_kernel)
+  if (lane == 0 && task_ok(task, limits)) {
+    const CopyRange r = copy_range(task, mis, value_count);
+    if (r.hi > r.lo)
+      bulk_prefetch_l2(values + r.lo, (uint32_t)(r.hi - r.lo) * 4u);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   uint32_t parity = 0;
   auto start = [&](const Task &t) {
     if (lane == 0) {
@@ -673,76 +783,131 @@ segreduce_resident_kernel(const float *__restrict__ values,
   }
 }
 
-// Second pass of the split / persistent schedules: merge the partials of each
-// cut segment in slot order.  The plan lists the segments with at least
-// kBigSplit partials first (a CTA each: CTAs 0..big-1), then the middle (a
-// warp each), then those with at most kTinySplit partials (a thread each).
-// Thread-strided partial sums then a butterfly, so the result does not depend
-// on timing.  Launched with programmatic stream serialisation: its CTAs may be
-// placed while the tile kernel drains, and wait here until that kernel's
-// writes are visible.
-constexpr int kCombineThreads = 256;
+// Merge pass of the tile schedules: combines the partials of every cut
+// segment in slot order and writes out[seg].
+//
+// CTAs [0, record_ctas): one thread per record (the host planner lists the
+// cut segments; the device planner writes one record per tile, empty where no
+// segment begins a cut there).  A segment of up to kLaneMerge pieces is merged
+// by its thread, up to kWarpMerge by its warp.
+// CTAs [record_ctas, gridDim): the segments with more pieces than that, which
+// the planners list apart (`bigs`, *big_count of them, a number only the
+// device needs to know): a CTA each, every thread with up to sixteen
+// partials in flight.
+// Thread- or lane-strided partial results, then a butterfly, so the result
+// does not depend on timing.  Launched with programmatic stream
+// serialisation: its CTAs are placed and read their records (plan-owned
+// memory) while the tile kernel drains, and wait for that kernel's partials
+// to be visible before they read one.
+constexpr int kMergeThreads = 512;
 
 template <class Op>
-__global__ void __launch_bounds__(kCombineThreads)
-segreduce_combine_kernel(const SplitSegment *__restrict__ splits,
-                         int32_t split_count, int32_t big_count,
-                         int32_t medium_count,
-                         const float *__restrict__ partials,
-                         float *__restrict__ out) {
+__global__ void __launch_bounds__(kMergeThreads)
+segreduce_merge_kernel(const MergeRecord *__restrict__ records, int32_t count,
+                       uint32_t record_ctas,
+                       const MergeRecord *__restrict__ bigs,
+                       const int32_t *__restrict__ big_count,
+                       const float *__restrict__ partials,
+                       float *__restrict__ out, Limits limits) {
   __shared__ float scratch[32];
   // the next launch in the stream, if it is one of the tile kernels, may
   // place its CTAs and fetch its descriptors while this grid runs
   asm volatile("griddepcontrol.launch_dependents;");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int lane = threadIdx.x & 31;
-  const int32_t medium_ctas = (medium_count + 7) / 8;
-  int32_t block = (int32_t)blockIdx.x;
-  if (block < big_count) {
-    const SplitSegment s = splits[block];
-    const float *p = partials + s.slot_begin;
-    float a0 = Op::identity(), a1 = Op::identity(), a2 = Op::identity(),
-          a3 = Op::identity();
-    int i = threadIdx.x;
-    for (; i + 3 * kCombineThreads < s.slot_count; i += 4 * kCombineThreads) {
-      a0 = Op::apply(a0, p[i]);
-      a1 = Op::apply(a1, p[i + kCombineThreads]);
-      a2 = Op::apply(a2, p[i + 2 * kCombineThreads]);
-      a3 = Op::apply(a3, p[i + 3 * kCombineThreads]);
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int step = limits.slot_step;
+  // a record that does not fit the launch's arrays is skipped, not followed
+  auto fits = [&](const MergeRecord &r) {
+    return r.pieces >= 2 && r.seg >= 0 && r.seg < limits.segment_count &&
+           slots_ok(r.first, r.pieces, limits);
+  };
+  if (blockIdx.x < record_ctas) {
+    const int64_t index = (int64_t)blockIdx.x * kMergeThreads + tid;
+    MergeRecord r{0, 0, 0, 0};
+    if (index < count) r = records[index];
+    const bool valid = fits(r) && r.pieces <= kWarpMerge;
+    const bool small = valid && r.pieces <= kLaneMerge;
+    const bool medium = valid && !small;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // (all the loads of a segment are issued before the first is used: one
+    // round trip to L2, where the partials were just written, per segment)
+    if (small) {
+      float q[kLaneMerge];
+#pragma unroll
+      for (int k = 0; k < kLaneMerge; ++k)
+        if (k < r.pieces) q[k] = partials[piece_slot(r.first, k, step)];
+      float acc = Op::identity();
+#pragma unroll
+      for (int k = 0; k < kLaneMerge; ++k)
+        if (k < r.pieces) acc = Op::apply(acc, q[k]);
+      out[r.seg] = acc;
     }
-    for (; i < s.slot_count; i += kCombineThreads) a0 = Op::apply(a0, p[i]);
-    const float r = cta_reduce<Op>(
-        Op::apply(Op::apply(a0, a1), Op::apply(a2, a3)), scratch);
-    if (threadIdx.x == 0) out[s.seg] = r;
-    return;
+    unsigned waiting = __ballot_sync(kFullMask, medium);
+    while (waiting) {
+      const int src = __ffs(waiting) - 1;
+      waiting &= waiting - 1;
+      const int seg = __shfl_sync(kFullMask, r.seg, src);
+      const int first = __shfl_sync(kFullMask, r.first, src);
+      const int pieces = __shfl_sync(kFullMask, r.pieces, src);
+      float q[kWarpMerge / 32];
+#pragma unroll
+      for (int u = 0; u < kWarpMerge / 32; ++u)
+        if (lane + 32 * u < pieces)
+          q[u] = partials[piece_slot(first, lane + 32 * u, step)];
+      float acc = Op::identity();
+#pragma unroll
+      for (int u = 0; u < kWarpMerge / 32; ++u)
+        if (lane + 32 * u < pieces) acc = Op::apply(acc, q[u]);
+      acc = warp_reduce<Op>(acc);
+      if (lane == 0) out[seg] = acc;
+    }
+  } else {
+    const int total = bigs != nullptr ? *big_count : 0;
+    const int stride = (int)(gridDim.x - record_ctas);
+    int i = (int)(blockIdx.x - record_ctas);
+    MergeRecord r{0, 0, 0, 0};
+    if (i < total) r = bigs[i];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    while (i < total) {
+      const bool valid = fits(r);  // uniform over the CTA
+      const int first = r.first, pieces = valid ? r.pieces : 0;
+      // sixteen partials per thread are requested before the first is
+      // used: a segment of up to 16 * kMergeThreads pieces costs one round
+      // trip to L2
+      float a[4] = {Op::identity(), Op::identity(), Op::identity(),
+                    Op::identity()};
+      for (int k = tid; k < pieces; k += 16 * kMergeThreads) {
+        float q[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+          if (k + u * kMergeThreads < pieces)
+            q[u] = partials[piece_slot(first, k + u * kMergeThreads, step)];
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+          if (k + u * kMergeThreads < pieces)
+            a[u & 3] = Op::apply(a[u & 3], q[u]);
+      }
+      const float mine =
+          Op::apply(Op::apply(a[0], a[1]), Op::apply(a[2], a[3]));
+      const float v = cta_reduce<Op>(mine, scratch);
+      if (tid == 0 && valid) out[r.seg] = v;
+      i += stride;
+      if (i < total) r = bigs[i];
+    }
   }
-  block -= big_count;
-  if (block < medium_ctas) {
-    const int32_t j = block * 8 + (int32_t)(threadIdx.x >> 5);
-    if (j >= medium_count) return;
-    const SplitSegment s = splits[big_count + j];
-    float acc = Op::identity();
-    for (int i = lane; i < s.slot_count; i += 32)
-      acc = Op::apply(acc, partials[s.slot_begin + i]);
-    acc = warp_reduce<Op>(acc);
-    if (lane == 0) out[s.seg] = acc;
-    return;
-  }
-  block -= medium_ctas;
-  const int64_t j = (int64_t)big_count + medium_count +
-                    (int64_t)block * kCombineThreads + threadIdx.x;
-  if (j >= split_count) return;
-  const SplitSegment s = splits[j];
-  float acc = Op::identity();
-  for (int i = 0; i < s.slot_count; ++i)
-    acc = Op::apply(acc, partials[s.slot_begin + i]);
-  out[s.seg] = acc;
 }
 
 // ---------------------------------------------------------------------------
 // launchers
 // ---------------------------------------------------------------------------
 constexpr int kSplitBytes = kSplitWarps * kStageBytes;
+#ifndef SWG_SPLIT_CTAS_PER_SM
+#define SWG_SPLIT_CTAS_PER_SM 12  // residency of the split kernel (shared memory)
+#endif
+
+static Limits limits_of(const DevicePlan &plan, int32_t value_count) {
+  return Limits{value_count, plan.segment_count, plan.partial_slots,
+                plan.slot_step};
+}
 
 template <class Op, int kWarps, int kStages>
 static cudaError_t persistent_launch(const float *values, float *out,
@@ -763,8 +928,7 @@ static cudaError_t persistent_launch(const float *values, float *out,
   segreduce_persistent_kernel<Op, kWarps, kStages>
       <<<grid, kWarps * 32, kBytes, stream>>>(
           values, out, value_count, plan.tasks, plan.task_count, plan.offsets,
-          plan.partials, plan.control,
-          Limits{value_count, plan.segment_count, plan.partial_slots});
+          plan.partials, plan.control, limits_of(plan, value_count));
   return cudaGetLastError();
 }
 
@@ -882,36 +1046,42 @@ cudaError_t launch_segreduce_cta(int kind, const float *values,
   return e;
 }
 
-template <class Op>
-static cudaError_t launch_combine_as(const DevicePlan &plan, float *out,
-                                     cudaStream_t stream) {
-  const int32_t tiny =
-      plan.split_count - plan.big_split_count - plan.medium_split_count;
+// A tile kernel launched with programmatic stream serialisation: it may be
+// placed while the kernel before it in the stream drains (see the kernels).
+template <class Kernel, class... Args>
+static cudaError_t launch_serialised(Kernel kernel, unsigned grid,
+                                     unsigned block, size_t shared,
+                                     cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3((unsigned)(
-      (int64_t)plan.big_split_count +
-      ((int64_t)plan.medium_split_count + 7) / 8 +
-      ((int64_t)tiny + kCombineThreads - 1) / kCombineThreads));
-  config.blockDim = dim3(kCombineThreads);
-  config.dynamicSmemBytes = 0;
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(block);
+  config.dynamicSmemBytes = shared;
   config.stream = stream;
   cudaLaunchAttribute attribute;
   attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute.val.programmaticStreamSerializationAllowed = 1;
   config.attrs = &attribute;
   config.numAttrs = 1;
-  return cudaLaunchKernelEx(&config, segreduce_combine_kernel<Op>,
-                            (const SplitSegment *)plan.splits,
-                            plan.split_count, plan.big_split_count,
-                            plan.medium_split_count,
-                            (const float *)plan.partials, out);
+  return cudaLaunchKernelEx(&config, kernel, args...);
 }
 
-static cudaError_t launch_combine(int kind, const DevicePlan &plan, float *out,
-                                  cudaStream_t stream) {
-  if (plan.split_count == 0) return cudaSuccess;
+static cudaError_t launch_merge(int kind, const DevicePlan &plan, float *out,
+                                int32_t value_count, cudaStream_t stream) {
+  if (plan.merge_count == 0 && plan.big_capacity == 0) return cudaSuccess;
+  const unsigned record_ctas =
+      (unsigned)(((int64_t)plan.merge_count + kMergeThreads - 1) /
+                 kMergeThreads);
+  // a CTA per listed long segment, as many as the list can hold but no more
+  // than two rounds of the machine (they loop over the list)
+  int big_ctas = plan.big_capacity;
+  if (big_ctas > 2 * plan.sm_count) big_ctas = 2 * plan.sm_count;
   return with_op(kind, [&](auto op) {
-    return launch_combine_as<decltype(op)>(plan, out, stream);
+    return launch_serialised(
+        segreduce_merge_kernel<decltype(op)>, record_ctas + (unsigned)big_ctas,
+        kMergeThreads, 0, stream, (const MergeRecord *)plan.merges,
+        plan.merge_count, record_ctas, (const MergeRecord *)plan.bigs,
+        (const int32_t *)plan.big_count, (const float *)plan.partials, out,
+        limits_of(plan, value_count));
   });
 }
 
@@ -921,27 +1091,21 @@ cudaError_t launch_segreduce_split(int kind, const float *values, float *out,
   if (plan.task_count == 0) return cudaSuccess;
   const unsigned grid =
       (unsigned)((plan.task_count + kSplitWarps - 1) / kSplitWarps);
-  const Limits limits{value_count, plan.segment_count, plan.partial_slots};
+  const uint32_t first_wave =
+      (uint32_t)plan.sm_count * SWG_SPLIT_CTAS_PER_SM;
   probe_begin(probe, stream);
-  cudaError_t e = with_op(kind, [&](auto op) {
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(grid);
-    config.blockDim = dim3(kSplitWarps * 32);
-    config.dynamicSmemBytes = kSplitBytes;
-    config.stream = stream;
-    cudaLaunchAttribute attribute;
-    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute.val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = &attribute;
-    config.numAttrs = 1;
-    return cudaLaunchKernelEx(
-        &config, segreduce_split_kernel<decltype(op)>, values, out,
-        value_count, (const Task *)plan.tasks, plan.task_count,
-        (const int32_t *)plan.offsets, plan.partials, plan.control, limits);
+  const cudaError_t e = with_op(kind, [&](auto op) {
+    return launch_serialised(
+        segreduce_split_kernel<decltype(op)>, grid, kSplitWarps * 32,
+        kSplitBytes, stream, values, out, value_count,
+        (const Task *)plan.tasks, plan.task_count,
+        (const int32_t *)plan.offsets, plan.partials, plan.control,
+        limits_of(plan, value_count), first_wave);
   });
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;
-  return launch_combine(kind, plan, out, stream);
+  const cudaError_t merged = launch_merge(kind, plan, out, value_count, stream);
+  return merged;
 }
 
 cudaError_t launch_segreduce_persistent(int kind, const float *values,
@@ -951,13 +1115,13 @@ cudaError_t launch_segreduce_persistent(int kind, const float *values,
                                         const Probe *probe) {
   if (plan.task_count == 0) return cudaSuccess;
   probe_begin(probe, stream);
-  cudaError_t e = with_op(kind, [&](auto op) {
+  const cudaError_t e = with_op(kind, [&](auto op) {
     return persistent_dispatch<decltype(op)>(values, out, value_count, plan,
                                              stream, false);
   });
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;
-  return launch_combine(kind, plan, out, stream);
+  return launch_merge(kind, plan, out, value_count, stream);
 }
 
 cudaError_t launch_segreduce_resident(int kind, const float *values,
@@ -970,27 +1134,29 @@ cudaError_t launch_segreduce_resident(int kind, const float *values,
   const int needed = (plan.task_count + kResidentWarps - 1) / kResidentWarps;
   if (grid > needed) grid = needed;
   probe_begin(probe, stream);
-  cudaError_t e = with_op(kind, [&](auto op) {
-    segreduce_resident_kernel<decltype(op), kResidentWarps>
-        <<<grid, kResidentWarps * 32, kResidentWarps * kStageBytes, stream>>>(
-            values, out, value_count, plan.tasks, plan.task_count,
-            plan.offsets, plan.partials, plan.control,
-            Limits{value_count, plan.segment_count, plan.partial_slots});
-    return cudaGetLastError();
+  const cudaError_t e = with_op(kind, [&](auto op) {
+    return launch_serialised(
+        segreduce_resident_kernel<decltype(op), kResidentWarps>,
+        (unsigned)grid, kResidentWarps * 32,
+        (size_t)kResidentWarps * kStageBytes, stream, values, out, value_count,
+        (const Task *)plan.tasks, plan.task_count,
+        (const int32_t *)plan.offsets, plan.partials, plan.control,
+        limits_of(plan, value_count));
   });
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;
-  return launch_combine(kind, plan, out, stream);
+  return launch_merge(kind, plan, out, value_count, stream);
 }
 
 // ---------------------------------------------------------------------------
 // Allocation-free variant of the split schedule.
 //
-// Everything the split schedule normally keeps in plan-owned cudaMalloc memory
-// (task list, aligned offsets copy, split-segment list, partials, control
-// words) lives instead in one file-scope device array of fixed size, so the
-// call path contains no cudaMalloc / cudaFree.  Every GPU that loads this
-// library holds the array (about 1.8 MB) until the process exits.
+// Everything the split schedule normally keeps in plan-owned device memory
+// (task list, aligned offsets copy, the list of cut segments, their partials,
+// control words) lives instead in one file-scope device array of fixed size,
+// so the call path contains no cudaMalloc / cudaFree.  Every GPU that loads
+// this library holds the array (kStaticBytes = 2,490,880 bytes, about 2.5 MB)
+// until the process exits.
 //
 // The array's name is only a host-side handle: the address kernels can use is
 // obtained once per device with cudaGetSymbolAddress, with that device
@@ -1000,19 +1166,25 @@ constexpr size_t round256(size_t bytes) { return (bytes + 255) / 256 * 256; }
 constexpr size_t kStaticOffsetBytes =
     round256(((size_t)kStaticMaxSegments + 8) * 4);
 constexpr size_t kStaticTaskBytes = (size_t)kStaticMaxTasks * sizeof(Task);
-constexpr size_t kStaticSplitBytes =
-    (size_t)kStaticMaxSplits * sizeof(SplitSegment);
+// a cut segment has at least two partials; the long ones (more than
+// kWarpMerge) are listed behind the others, the count of them last
+constexpr size_t kStaticMergeBytes =
+    (size_t)(kStaticMaxSlots / 2) * sizeof(MergeRecord);
+constexpr int kStaticMaxBigs = kStaticMaxSlots / kWarpMerge;
 constexpr size_t kStaticPartialBytes = (size_t)kStaticMaxSlots * 4;
 constexpr size_t kStaticControlBytes = 256;
+static_assert(kStaticControlBytes >= kControlWords * 4 + 4,
+              "the count of long cut segments sits behind the control words");
 constexpr size_t kStaticOffsetAt = 0;
 constexpr size_t kStaticTaskAt = kStaticOffsetAt + kStaticOffsetBytes;
-constexpr size_t kStaticSplitAt = kStaticTaskAt + kStaticTaskBytes;
-constexpr size_t kStaticPartialAt = kStaticSplitAt + kStaticSplitBytes;
+constexpr size_t kStaticMergeAt = kStaticTaskAt + kStaticTaskBytes;
+constexpr size_t kStaticPartialAt = kStaticMergeAt + kStaticMergeBytes;
 constexpr size_t kStaticControlAt = kStaticPartialAt + kStaticPartialBytes;
 constexpr size_t kStaticBytes = kStaticControlAt + kStaticControlBytes;
-static_assert(kStaticTaskAt % 256 == 0 && kStaticSplitAt % 256 == 0 &&
+static_assert(kStaticTaskAt % 256 == 0 && kStaticMergeAt % 256 == 0 &&
                   kStaticPartialAt % 256 == 0 && kStaticControlAt % 256 == 0,
               "regions of the static scratch keep 256-byte alignment");
+static_assert(kStaticBytes == 2490880, "size quoted in the documentation");
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
 
@@ -1046,9 +1218,8 @@ cudaError_t launch_segreduce_static(int kind, const float *values, float *out,
   if (e != cudaSuccess) return e;
   int32_t *d_off = reinterpret_cast<int32_t *>(base + kStaticOffsetAt);
   Task *d_tasks = reinterpret_cast<Task *>(base + kStaticTaskAt);
-  SplitSegment *d_splits =
-      reinterpret_cast<SplitSegment *>(base + kStaticSplitAt);
-  float *d_partials = reinterpret_cast<float *>(base + kStaticPartialAt);
+  MergeRecord *d_merges =
+      reinterpret_cast<MergeRecord *>(base + kStaticMergeAt);
   uint32_t *d_control = reinterpret_cast<uint32_t *>(base + kStaticControlAt);
 
   const size_t noffsets = (size_t)segment_count + 1;
@@ -1066,12 +1237,26 @@ cudaError_t launch_segreduce_static(int kind, const float *values, float *out,
                       plan.tasks.size() * sizeof(Task), cudaMemcpyHostToDevice,
                       stream);
   if (e != cudaSuccess) return e;
-  if (!plan.splits.empty()) {
-    e = cudaMemcpyAsync(d_splits, plan.splits.data(),
-                        plan.splits.size() * sizeof(SplitSegment),
+  // short and long cut segments share the region: the long ones fill it
+  // from the end
+  MergeRecord *d_bigs = d_merges + (kStaticMaxSlots / 2 - kStaticMaxBigs);
+  int32_t *d_big_count = reinterpret_cast<int32_t *>(d_control + kControlWords);
+  if (!plan.merges.empty()) {
+    e = cudaMemcpyAsync(d_merges, plan.merges.data(),
+                        plan.merges.size() * sizeof(MergeRecord),
                         cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) return e;
   }
+  if (!plan.big_merges.empty()) {
+    e = cudaMemcpyAsync(d_bigs, plan.big_merges.data(),
+                        plan.big_merges.size() * sizeof(MergeRecord),
+                        cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return e;
+  }
+  const int32_t big_total = (int32_t)plan.big_merges.size();
+  e = cudaMemcpyAsync(d_big_count, &big_total, sizeof(big_total),
+                      cudaMemcpyHostToDevice, stream);
+  if (e != cudaSuccess) return e;
   DevicePlan dev;
   dev.device = device;
   dev.sm_count = sm_count;
@@ -1079,12 +1264,14 @@ cudaError_t launch_segreduce_static(int kind, const float *values, float *out,
   dev.task_count = (int32_t)plan.tasks.size();
   dev.segment_count = segment_count;
   dev.offsets = d_off;
-  dev.splits = d_splits;
-  dev.split_count = (int32_t)plan.splits.size();
-  dev.big_split_count = plan.big_split_count;
-  dev.medium_split_count = plan.medium_split_count;
-  dev.partials = d_partials;
+  dev.partials = reinterpret_cast<float *>(base + kStaticPartialAt);
   dev.partial_slots = plan.partial_slots;
+  dev.slot_step = plan.slot_step;
+  dev.merges = d_merges;
+  dev.merge_count = (int32_t)plan.merges.size();
+  dev.bigs = d_bigs;
+  dev.big_count = d_big_count;
+  dev.big_capacity = big_total;
   dev.control = d_control;
   return launch_segreduce_split(kind, values, out, value_count, dev, stream,
                                 nullptr);

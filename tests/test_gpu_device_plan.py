@@ -194,9 +194,14 @@ def test_device_plan_statistics_equal_the_host_plan():
                     "elements_in_bin", "schedule"):
             assert a[key] == b[key], key
         assert abs(a["mean_length"] - b["mean_length"]) < 1e-6
-        items = int(offsets[-1]) + len(offsets) - 1
+        # a segment counts for its values plus four header items
+        items = int(offsets[-1]) + 4 * (len(offsets) - 1)
         assert b["tasks"] == -(-items // 2031)
-        assert b["partial_slots"] == b["tasks"] + b["split_segments"]
+        # two partial slots per tile; the cut segments are those longer than
+        # a tile plus the shorter ones a boundary happens to fall in
+        assert b["partial_slots"] == 2 * b["tasks"]
+        assert b["pack_tasks"] + b["chunk_tasks"] == b["tasks"]
+        assert b["split_segments"] >= int((np.diff(offsets) > 2031).sum())
     finally:
         host.close()
         device.close()
@@ -262,6 +267,55 @@ def test_automatic_launch_plans_on_the_device_and_caches_by_content():
     launch_gpu(values, torch.as_tensor(shifted).cuda(), output, "max")
     assert len(runner._device_plan_cache) == (
         2 if not np.array_equal(shifted, offsets) else 1)
+    runner.clear_plan_cache()
+
+
+def test_status_can_be_read_without_synchronising():
+    """``peek`` reads the kernels' error word from pinned host memory: no CUDA
+    call, so the launch functions can afford it before every launch.  After
+    clean launches both it and the synchronising ``check`` stay silent."""
+    offsets = workloads.c5_offsets(segments=1 << 14, total=1 << 22, giants=2,
+                                   giant_length=1 << 20)
+    values = torch.randn(int(offsets[-1]), device="cuda")
+    output = torch.empty(len(offsets) - 1, device="cuda")
+    plan = device_plan(offsets)
+    try:
+        for schedule in ("split", "persistent", "resident"):
+            launch_gpu(values, torch.as_tensor(offsets).cuda(), output, "sum",
+                       plan=plan, schedule=schedule)
+            plan.peek()
+        torch.cuda.synchronize()
+        plan.peek()
+        plan.check()
+    finally:
+        plan.close()
+
+
+def test_two_streams_over_the_same_offsets_get_a_plan_each():
+    """Launches that share a plan share its merge scratch; the drop-in call
+    therefore caches plans per stream.  Two streams reducing over the same CSR
+    structure at the same time must both match the oracle."""
+    runner.clear_plan_cache()
+    offsets = workloads.c5_offsets(segments=1 << 16, total=1 << 24, giants=4,
+                                   giant_length=1 << 21)
+    segments = len(offsets) - 1
+    device_offsets = torch.as_tensor(offsets).cuda()
+    host_values = [np.random.default_rng(s).standard_normal(
+        int(offsets[-1])).astype(np.float32) for s in (1, 2)]
+    values = [torch.as_tensor(v).cuda() for v in host_values]
+    outputs = [torch.empty(segments, device="cuda") for _ in range(2)]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
+    for _ in range(4):
+        for stream, v, out in zip(streams, values, outputs):
+            with torch.cuda.stream(stream):
+                launch_gpu(v, device_offsets, out, "sum")
+    torch.cuda.synchronize()
+    assert len(runner._device_plan_cache) == 2
+    for v, out in zip(host_values, outputs):
+        exact = oracle.segsum_f64(v, offsets)
+        bound = oracle.sum_tolerance(v, offsets)
+        assert np.all(np.abs(out.cpu().numpy() - exact) <= bound)
     runner.clear_plan_cache()
 
 

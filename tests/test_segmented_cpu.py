@@ -97,7 +97,9 @@ def check_tasks_cover_everything(offsets, tasks, info):
     covered = np.zeros(int(offsets[-1]) + 1, dtype=np.int64)
     tile, items = info["tile_values"], info["tile_items"]
     pieces = {}
-    for seg, count, vbegin, vcount, kind, head, tail in tasks:
+    links = {}  # segment -> what its tasks say about its slots
+    for (seg, count, vbegin, vcount, kind, head, tail, link_first,
+         link_pieces) in tasks:
         assert 0 <= vcount <= tile
         covered[vbegin] += 1
         covered[vbegin + vcount] -= 1
@@ -112,6 +114,7 @@ def check_tasks_cover_everything(offsets, tasks, info):
                 assert offsets[seg] < vbegin
                 end = min(int(offsets[seg + 1]), vend)
                 pieces.setdefault(seg, []).append((vbegin, end - vbegin, head))
+                links.setdefault(seg, []).append(("first", link_first))
                 first_whole = seg + 1
             else:
                 assert offsets[seg] == vbegin
@@ -119,6 +122,7 @@ def check_tasks_cover_everything(offsets, tasks, info):
                 assert offsets[last + 1] > vend
                 start = max(int(offsets[last]), vbegin)
                 pieces.setdefault(last, []).append((start, vend - start, tail))
+                links.setdefault(last, []).append(("pieces", link_pieces))
                 last_whole = last - 1
             else:
                 assert offsets[last + 1] == vend
@@ -131,6 +135,8 @@ def check_tasks_cover_everything(offsets, tasks, info):
                 whole[seg] += 1
             else:
                 pieces.setdefault(seg, []).append((vbegin, vcount, count))
+                links.setdefault(seg, []).append(("first", link_first))
+                links.setdefault(seg, []).append(("pieces", link_pieces))
     for seg, parts in pieces.items():
         assert whole[seg] == 0
         whole[seg] += 1
@@ -142,6 +148,10 @@ def check_tasks_cover_everything(offsets, tasks, info):
             assert b0 + c0 == b1
         slots = [slot for _, _, slot in parts]
         assert slots == list(range(slots[0], slots[0] + len(slots)))
+        # every piece knows where the segment's slots begin and how many
+        # pieces there are: what the in-kernel merge goes by
+        for what, said in links[seg]:
+            assert said == (slots[0] if what == "first" else len(slots))
     assert np.all(whole == 1)
     assert np.all(np.cumsum(covered)[:-1] == 1)
     assert info["tasks"] == len(tasks)
