@@ -51,6 +51,16 @@ typedef enum swg_status {
                           dialect's kind<min> (ADR-0008), which the reference's
                           lowering rejects (SegmentedReduction.cpp:106-108) */
 
+/* Element types of segmented reductions.  The reference lowers f32 only
+ * (SegmentedReduction.cpp:110-119); its dialect also admits f16, bf16 and
+ * integer segments (include/swage/Dialect/Swage/IR/SwageOps.td:101-105).
+ * f16 / bf16 values are widened exactly and reduced in fp32, results are fp32;
+ * i32 values give i32 results (wrap-around sum, signed max / min). */
+#define SWG_DTYPE_F32 0
+#define SWG_DTYPE_F16 1
+#define SWG_DTYPE_BF16 2
+#define SWG_DTYPE_I32 3
+
 /* Operation a plan is built for. */
 #define SWG_OP_REDUCE 0
 #define SWG_OP_SOFTMAX 1
@@ -204,6 +214,23 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
                       float *out, int32_t value_count, int32_t segment_count,
                       const swg_plan *plan, int schedule, int32_t block_hint,
                       void *stream);
+
+/* swg_segreduce_f32 for the other element types the dialect admits:
+ * `values` holds elements of `dtype` (SWG_DTYPE_*), `out` fp32 results for the
+ * floating types (f16 / bf16 are widened exactly and reduced in fp32) and
+ * int32 results for SWG_DTYPE_I32 (sum wraps around in two's complement --
+ * integer addition is associative, so the bits are those of the sequential
+ * sum; max / min are signed).  Same plans (a plan does not depend on the
+ * element type), same schedules: the tile schedules stage 2048 elements per
+ * task whatever their size; without a plan a warp or a CTA reduces each
+ * segment.  WARP with a plan and PERSISTENT fall back to SPLIT for these
+ * types.  No reference counterpart: the reference's lowering accepts f32
+ * only (lib/Conversion/SegmentedReduction/SegmentedReduction.cpp:110-119);
+ * identities per its ADR-0008 (lines 34-39). */
+int swg_segreduce(int kind, int dtype, const void *values,
+                  const int32_t *offsets, void *out, int32_t value_count,
+                  int32_t segment_count, const swg_plan *plan, int schedule,
+                  int32_t block_hint, void *stream);
 
 /* Sum AND max of every segment in one pass over the values:
  * out_sum[s] = swg_segreduce_f32(SWG_KIND_SUM)[s] to the documented tolerance,

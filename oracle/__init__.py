@@ -66,6 +66,8 @@ def _load():
     i64 = ctypes.c_int64
     lib.swg_oracle_segreduce_f32.argtypes = [
         ctypes.c_int, f32p, i32p, f32p, i64, ctypes.c_int]
+    lib.swg_oracle_segreduce_i32.argtypes = [ctypes.c_int, i32p, i32p, i32p,
+                                             i64]
     lib.swg_oracle_segsum_f64.argtypes = [f32p, i32p, f64p, i64, ctypes.c_int]
     lib.swg_oracle_segabsmax_f64.argtypes = [
         f32p, i32p, f64p, i64, ctypes.c_int]
@@ -76,7 +78,8 @@ def _load():
     lib.swg_oracle_vadd_f32.argtypes = [f32p, f32p, f32p, i64, i64,
                                         ctypes.c_int]
     for name in (
-        "swg_oracle_segreduce_f32", "swg_oracle_segsum_f64",
+        "swg_oracle_segreduce_f32", "swg_oracle_segreduce_i32",
+        "swg_oracle_segsum_f64",
         "swg_oracle_segabsmax_f64", "swg_oracle_segsoftmax_f64",
         "swg_oracle_segsoftmax_f32", "swg_oracle_vadd_f32",
         "swg_oracle_max_threads",
@@ -137,6 +140,20 @@ def segreduce_f32(values, offsets, kind, threads=1):
         out.size, int(threads))
     if used < 0:
         raise ValueError("reduction kind must be 'sum' or 'max'")
+    return out
+
+
+def segreduce_i32(values, offsets, kind):
+    """Sequential int32 segmented sum (wrap-around) / max / min."""
+    values, vp = _i32(values)
+    offsets, op = _i32(offsets)
+    _check_offsets(offsets, values.size)
+    out = np.empty(offsets.size - 1, dtype=np.int32)
+    used = _load().swg_oracle_segreduce_i32(
+        _KINDS[kind], vp, op,
+        out.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), out.size)
+    if used < 0:
+        raise ValueError("reduction kind must be 'sum', 'max' or 'min'")
     return out
 
 
@@ -266,6 +283,6 @@ def cpu_oracle(values, offsets, kind):
 
 __all__ = [
     "build", "cpu_oracle", "host_threads", "max_threads", "py_segreduce", "segabsmax_f64",
-    "segreduce_f32", "segsoftmax_f32", "segsoftmax_f64", "segsum_f64",
+    "segreduce_f32", "segreduce_i32", "segsoftmax_f32", "segsoftmax_f64", "segsum_f64",
     "sum_tolerance", "vadd_f32",
 ]

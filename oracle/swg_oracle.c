@@ -109,6 +109,32 @@ int swg_oracle_segreduce_f32(int kind, const float *values,
   return used;
 }
 
+/* Integer segments (the dialect's kind<...> over i32 elements; the reference's
+ * lowering accepts f32 only, SegmentedReduction.cpp:110-119, so this is the
+ * sequential loop of :131-183 with the integer identities of ADR-0008 :34-39:
+ * sum from 0 with two's-complement wrap-around, signed max from INT32_MIN,
+ * signed min from INT32_MAX).  Unpinned: the reference holds no test for it. */
+int swg_oracle_segreduce_i32(int kind, const int32_t *values,
+                             const int32_t *offsets, int32_t *out,
+                             int64_t segment_count) {
+  if (kind != SWG_ORACLE_SUM && kind != SWG_ORACLE_MAX &&
+      kind != SWG_ORACLE_MIN)
+    return -1;
+  for (int64_t sid = 0; sid < segment_count; ++sid) {
+    uint32_t sum = 0;
+    int32_t top = INT32_MIN, bottom = INT32_MAX;
+    for (int64_t i = offsets[sid]; i < offsets[sid + 1]; ++i) {
+      sum += (uint32_t)values[i];
+      if (values[i] > top) top = values[i];
+      if (values[i] < bottom) bottom = values[i];
+    }
+    out[sid] = kind == SWG_ORACLE_SUM   ? (int32_t)sum
+               : kind == SWG_ORACLE_MAX ? top
+                                        : bottom;
+  }
+  return 1;
+}
+
 /* fp64 accumulation of the same sum: the quantity the fp32 tolerance
  * |err| <= 1e-5 * sqrt(len) * max|x| is stated against. */
 int swg_oracle_segsum_f64(const float *values, const int32_t *offsets,

@@ -18,7 +18,8 @@ import threading
 LIBRARY_PATH = pathlib.Path(__file__).resolve().parent / "libswage_b200.so"
 
 # mirrors of the header's constants
-KIND_SUM, KIND_MAX = 0, 1
+KIND_SUM, KIND_MAX, KIND_MIN = 0, 1, 2
+DTYPE_F32, DTYPE_F16, DTYPE_BF16, DTYPE_I32 = range(4)
 OP_REDUCE, OP_SOFTMAX = 0, 1
 (SCHED_AUTO, SCHED_WARP, SCHED_CTA, SCHED_SPLIT, SCHED_PERSISTENT,
  SCHED_RESIDENT) = range(6)
@@ -44,7 +45,7 @@ EXPORTS = (
     "swg_profile_stop", "swg_segreduce_f32_noalloc",
     "swg_validate_offsets_device", "swg_plan_create_device",
     "swg_segreduce_sum_max_f32", "swg_plan_create_validated",
-    "swg_plan_peek_status",
+    "swg_plan_peek_status", "swg_segreduce",
 )
 
 _lock = threading.Lock()
@@ -82,6 +83,9 @@ def _declare(lib):
     lib.swg_segreduce_f32.restype = c_int
     lib.swg_segreduce_f32.argtypes = [
         c_int, ptr, ptr, ptr, c_i32, c_i32, ptr, c_int, c_i32, ptr]
+    lib.swg_segreduce.restype = c_int
+    lib.swg_segreduce.argtypes = [
+        c_int, c_int, ptr, ptr, ptr, c_i32, c_i32, ptr, c_int, c_i32, ptr]
     lib.swg_segsoftmax_f32.restype = c_int
     lib.swg_segsoftmax_f32.argtypes = [
         ptr, ptr, ptr, c_i32, c_i32, ptr, c_int, ptr]
@@ -151,6 +155,17 @@ def segreduce(kind, values_ptr, offsets_ptr, out_ptr, value_count,
             kind, values_ptr, offsets_ptr, out_ptr, value_count,
             segment_count, plan_handle, schedule, block, stream),
         "swg_segreduce_f32",
+    )
+
+
+def segreduce_typed(kind, dtype, values_ptr, offsets_ptr, out_ptr, value_count,
+                    segment_count, plan_handle, schedule, block, stream):
+    """``segreduce`` for f16 / bf16 / i32 values (``dtype``: ``DTYPE_*``)."""
+    check(
+        library().swg_segreduce(
+            kind, dtype, values_ptr, offsets_ptr, out_ptr, value_count,
+            segment_count, plan_handle, schedule, block, stream),
+        "swg_segreduce",
     )
 
 

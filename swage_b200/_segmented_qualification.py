@@ -128,7 +128,8 @@ def _raise_offsets_error(reason, segment_count, value_count, output_count,
 
 
 def _validate_tensors(values, offsets, output, *, require_cuda=True,
-                      elementwise_output=False, _host_offsets=None):
+                      elementwise_output=False, _host_offsets=None,
+                      extended_dtypes=False):
     """Check dtype / rank / layout / offsets / device; return both counts.
 
     Same order and messages as the reference (:58-93).  With
@@ -140,7 +141,16 @@ def _validate_tensors(values, offsets, output, *, require_cuda=True,
     for name, tensor in named:
         if not isinstance(tensor, torch.Tensor):
             raise TypeError(f"{name} must be a torch.Tensor")
+    wide = extended_dtypes and isinstance(values, torch.Tensor) and (
+        values.dtype in (torch.float16, torch.bfloat16, torch.int32))
     for name, tensor in (named[0], named[2]):
+        if wide and name == "values":
+            continue
+        if wide and values.dtype == torch.int32:
+            if tensor.dtype != torch.int32:
+                raise TypeError(
+                    f"{name} must have dtype torch.int32 for int32 values")
+            continue
         if tensor.dtype != torch.float32:
             raise TypeError(f"{name} must have dtype torch.float32")
     if offsets.dtype != torch.int32:
@@ -537,12 +547,18 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
     ``resident``.
     With ``extensions=True`` ``kind`` may also be ``"min"`` (NaN-propagating
     minimum from ``+inf``: the dialect's ``kind<min>``, which the reference's
-    lowering rejects, ``SegmentedReduction.cpp:106-108``); without it the
-    reference's error is kept.
+    lowering rejects, ``SegmentedReduction.cpp:106-108``), and ``values`` may
+    hold ``float16`` / ``bfloat16`` (widened exactly, reduced in fp32,
+    ``output`` fp32) or ``int32`` (wrap-around sum, signed max / min,
+    ``output`` int32): element types the dialect admits
+    (``SwageOps.td:101-105``) and the lowering rejects
+    (``SegmentedReduction.cpp:110-119``).  Without it the reference's errors
+    are kept.
     """
     torch = _runtime._import_torch()
     if _validated is None:
-        value_count, segment_count = _validate_tensors(values, offsets, output)
+        value_count, segment_count = _validate_tensors(
+            values, offsets, output, extended_dtypes=bool(extensions))
     else:
         value_count, segment_count = _validated
     _check_block(block_size, torch)
@@ -571,12 +587,23 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
     if plan is not None:
         _peek(plan)
     stream = torch.cuda.current_stream()
-    _native.segreduce(
-        kind_code, values.data_ptr(), offsets.data_ptr(), output.data_ptr(),
-        value_count, segment_count,
-        plan.handle if plan is not None else None,
-        code, block_size, stream.cuda_stream,
-    )
+    if values.dtype == torch.float32:
+        _native.segreduce(
+            kind_code, values.data_ptr(), offsets.data_ptr(),
+            output.data_ptr(), value_count, segment_count,
+            plan.handle if plan is not None else None,
+            code, block_size, stream.cuda_stream,
+        )
+    else:
+        dtype = {torch.float16: _native.DTYPE_F16,
+                 torch.bfloat16: _native.DTYPE_BF16,
+                 torch.int32: _native.DTYPE_I32}[values.dtype]
+        _native.segreduce_typed(
+            kind_code, dtype, values.data_ptr(), offsets.data_ptr(),
+            output.data_ptr(), value_count, segment_count,
+            plan.handle if plan is not None else None,
+            code, block_size, stream.cuda_stream,
+        )
     for tensor in (values, offsets, output):
         tensor.record_stream(stream)
     return None

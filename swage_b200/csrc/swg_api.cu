@@ -579,24 +579,28 @@ int swg_plan_status(swg_plan *plan) {
   return SWG_OK;
 }
 
-int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
-                      float *out, int32_t value_count, int32_t segment_count,
-                      const swg_plan *plan, int schedule, int32_t block_hint,
-                      void *stream) {
+static int segreduce(const char *who, int kind, int dtype, const void *values,
+                     const int32_t *offsets, void *out, int32_t value_count,
+                     int32_t segment_count, const swg_plan *plan, int schedule,
+                     int32_t block_hint, void *stream) {
   swg::clear_error();
   if (kind != SWG_KIND_SUM && kind != SWG_KIND_MAX && kind != SWG_KIND_MIN) {
     swg::set_error(
         "reduction kind must be SWG_KIND_SUM, SWG_KIND_MAX or SWG_KIND_MIN");
     return SWG_ERR_INVALID_ARGUMENT;
   }
+  if (dtype < SWG_DTYPE_F32 || dtype > SWG_DTYPE_I32) {
+    swg::set_error("%s: element type must be one of SWG_DTYPE_*", who);
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
   if (value_count < 0 || segment_count < 0 || block_hint < 0 ||
       schedule < SWG_SCHED_AUTO || schedule > SWG_SCHED_RESIDENT) {
-    swg::set_error("swg_segreduce_f32: bad count, block or schedule");
+    swg::set_error("%s: bad count, block or schedule", who);
     return SWG_ERR_INVALID_ARGUMENT;
   }
   if (segment_count == 0) return SWG_OK;
   if (!offsets || !out || (!values && value_count > 0)) {
-    swg::set_error("swg_segreduce_f32: null pointer");
+    swg::set_error("%s: null pointer", who);
     return SWG_ERR_INVALID_ARGUMENT;
   }
   int device = 0, sm_count = 0;
@@ -614,6 +618,11 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
       return SWG_ERR_PLAN_MISMATCH;
     }
     if (schedule == SWG_SCHED_AUTO) schedule = plan->host.schedule;
+    // the plan-free and ticketed schedules exist for f32 only: the other
+    // element types run the same tile tasks on the split schedule instead
+    if (dtype != SWG_DTYPE_F32 &&
+        (schedule == SWG_SCHED_WARP || schedule == SWG_SCHED_PERSISTENT))
+      schedule = SWG_SCHED_SPLIT;
   } else {
     if (schedule == SWG_SCHED_SPLIT || schedule == SWG_SCHED_PERSISTENT ||
         schedule == SWG_SCHED_RESIDENT) {
@@ -630,30 +639,58 @@ int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
   cudaError_t e = cudaSuccess;
   const swg::Probe *probe = next_probe();
   if (plan) note_launch(plan, s);
+  const bool f32 = dtype == SWG_DTYPE_F32;
   switch (schedule) {
     case SWG_SCHED_WARP:
-      e = swg::launch_segreduce_warp(kind, values, offsets, out, segment_count,
-                                     sm_count, s, probe);
-      break;
     case SWG_SCHED_CTA:
-      e = swg::launch_segreduce_cta(kind, values, offsets, out, segment_count,
-                                    block_hint, sm_count, s, probe);
+      if (!f32)
+        e = swg::launch_segreduce_typed(kind, dtype, values, offsets, out,
+                                        value_count, segment_count,
+                                        schedule == SWG_SCHED_CTA, sm_count, s,
+                                        probe);
+      else if (schedule == SWG_SCHED_WARP)
+        e = swg::launch_segreduce_warp(kind, (const float *)values, offsets,
+                                       (float *)out, segment_count, sm_count,
+                                       s, probe);
+      else
+        e = swg::launch_segreduce_cta(kind, (const float *)values, offsets,
+                                      (float *)out, segment_count, block_hint,
+                                      sm_count, s, probe);
       break;
     case SWG_SCHED_SPLIT:
-      e = swg::launch_segreduce_split(kind, values, out, value_count,
+      e = swg::launch_segreduce_split(kind, dtype, values, out, value_count,
                                       plan->dev, s, probe);
       break;
     case SWG_SCHED_RESIDENT:
-      e = swg::launch_segreduce_resident(kind, values, out, value_count,
+      e = swg::launch_segreduce_resident(kind, dtype, values, out, value_count,
                                          plan->dev, s, probe);
       break;
     default:
-      e = swg::launch_segreduce_persistent(kind, values, out, value_count,
+      e = swg::launch_segreduce_persistent(kind, (const float *)values,
+                                           (float *)out, value_count,
                                            plan->dev, s, probe);
       break;
   }
   if (e != cudaSuccess) return cuda_failure("segmented reduce launch", e);
   return SWG_OK;
+}
+
+int swg_segreduce_f32(int kind, const float *values, const int32_t *offsets,
+                      float *out, int32_t value_count, int32_t segment_count,
+                      const swg_plan *plan, int schedule, int32_t block_hint,
+                      void *stream) {
+  return segreduce("swg_segreduce_f32", kind, SWG_DTYPE_F32, values, offsets,
+                   out, value_count, segment_count, plan, schedule, block_hint,
+                   stream);
+}
+
+int swg_segreduce(int kind, int dtype, const void *values,
+                  const int32_t *offsets, void *out, int32_t value_count,
+                  int32_t segment_count, const swg_plan *plan, int schedule,
+                  int32_t block_hint, void *stream) {
+  return segreduce("swg_segreduce", kind, dtype, values, offsets, out,
+                   value_count, segment_count, plan, schedule, block_hint,
+                   stream);
 }
 
 int swg_segreduce_sum_max_f32(const float *values, const int32_t *offsets,

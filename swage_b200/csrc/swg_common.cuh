@@ -4,6 +4,8 @@
 // mbarrier, bulk async copy).
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <math_constants.h>
 #include <stdint.h>
@@ -21,6 +23,7 @@ constexpr unsigned kFullMask = 0xffffffffu;
 // -0.0 ordered below +0.0; identity -inf.  max.NaN.f32 has exactly these rules.
 // ---------------------------------------------------------------------------
 struct SumOp {
+  using Acc = float;
   static __device__ __forceinline__ float identity() { return 0.0f; }
   static __device__ __forceinline__ float apply(float a, float b) {
     return __fadd_rn(a, b);  // never contracted into an fma
@@ -28,6 +31,7 @@ struct SumOp {
 };
 
 struct MaxOp {
+  using Acc = float;
   static __device__ __forceinline__ float identity() {
     return -CUDART_INF_F;
   }
@@ -42,6 +46,7 @@ struct MaxOp {
 // identity +inf).  The reference's dialect admits kind<min> (ADR-0008) but its
 // lowering rejects it (SegmentedReduction.cpp:106-108).
 struct MinOp {
+  using Acc = float;
   static __device__ __forceinline__ float identity() { return CUDART_INF_F; }
   static __device__ __forceinline__ float apply(float a, float b) {
     float r;
@@ -50,15 +55,95 @@ struct MinOp {
   }
 };
 
+// Integer segments (the dialect's element types include i32; the reference's
+// lowering accepts f32 only, SegmentedReduction.cpp:106-119): two's-complement
+// wrap-around sum from 0, signed max from INT32_MIN, signed min from INT32_MAX.
+// Integer addition is associative, so every summation order gives the same
+// bits as the sequential one.
+struct ISumOp {
+  using Acc = int32_t;
+  static __device__ __forceinline__ int32_t identity() { return 0; }
+  static __device__ __forceinline__ int32_t apply(int32_t a, int32_t b) {
+    return (int32_t)((uint32_t)a + (uint32_t)b);
+  }
+};
+struct IMaxOp {
+  using Acc = int32_t;
+  static __device__ __forceinline__ int32_t identity() { return INT32_MIN; }
+  static __device__ __forceinline__ int32_t apply(int32_t a, int32_t b) {
+    return a > b ? a : b;
+  }
+};
+struct IMinOp {
+  using Acc = int32_t;
+  static __device__ __forceinline__ int32_t identity() { return INT32_MAX; }
+  static __device__ __forceinline__ int32_t apply(int32_t a, int32_t b) {
+    return a < b ? a : b;
+  }
+};
+
+// Element types a tile may hold, and what they accumulate in: f16 / bf16
+// values are widened to fp32 (exactly) and reduced in fp32.
+template <class T>
+struct Elem;
+template <>
+struct Elem<float> {
+  using Acc = float;
+  static __device__ __forceinline__ float get(float v) { return v; }
+};
+template <>
+struct Elem<int32_t> {
+  using Acc = int32_t;
+  static __device__ __forceinline__ int32_t get(int32_t v) { return v; }
+};
+template <>
+struct Elem<__half> {
+  using Acc = float;
+  static __device__ __forceinline__ float get(__half v) {
+    return __half2float(v);
+  }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  using Acc = float;
+  static __device__ __forceinline__ float get(__nv_bfloat16 v) {
+    return __bfloat162float(v);
+  }
+};
+
 template <class Op>
 __device__ __forceinline__ float fold4(float acc, float4 q) {
   return Op::apply(Op::apply(acc, Op::apply(q.x, q.y)), Op::apply(q.z, q.w));
 }
 
+// One 16-byte line of elements of type T folded into acc: four 32-bit
+// elements as fold4 does, or eight 16-bit ones as two such groups.
+template <class Op, class T>
+__device__ __forceinline__ typename Op::Acc fold_line(typename Op::Acc acc,
+                                                      uint4 raw) {
+  using A = typename Op::Acc;
+  if constexpr (sizeof(T) == 4) {
+    T v[4];
+    memcpy(v, &raw, 16);
+    const A x = Elem<T>::get(v[0]), y = Elem<T>::get(v[1]),
+            z = Elem<T>::get(v[2]), w = Elem<T>::get(v[3]);
+    return Op::apply(Op::apply(acc, Op::apply(x, y)), Op::apply(z, w));
+  } else {
+    T v[8];
+    memcpy(v, &raw, 16);
+    A e[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) e[i] = Elem<T>::get(v[i]);
+    const A lo = Op::apply(Op::apply(e[0], e[1]), Op::apply(e[2], e[3]));
+    const A hi = Op::apply(Op::apply(e[4], e[5]), Op::apply(e[6], e[7]));
+    return Op::apply(Op::apply(acc, lo), hi);
+  }
+}
+
 // Butterfly over the 32 lanes; every lane ends with the same value and the
 // combine order is fixed, so results do not depend on timing.
 template <class Op>
-__device__ __forceinline__ float warp_reduce(float v) {
+__device__ __forceinline__ typename Op::Acc warp_reduce(typename Op::Acc v) {
 #pragma unroll
   for (int delta = 16; delta > 0; delta >>= 1)
     v = Op::apply(v, __shfl_xor_sync(kFullMask, v, delta));
@@ -67,23 +152,28 @@ __device__ __forceinline__ float warp_reduce(float v) {
 
 // Reduce over a sub-group of `width` adjacent lanes (width a power of two).
 template <class Op>
-__device__ __forceinline__ float group_reduce(float v, int width) {
+__device__ __forceinline__ typename Op::Acc group_reduce(typename Op::Acc v,
+                                                         int width) {
   for (int delta = width >> 1; delta > 0; delta >>= 1)
     v = Op::apply(v, __shfl_xor_sync(kFullMask, v, delta));
   return v;
 }
 
-// CTA-wide reduce through `scratch` (>= 32 floats of shared memory).  All
+// CTA-wide reduce through `scratch` (>= 32 words of shared memory).  All
 // threads of the CTA must call it; the value is returned to every thread.
 template <class Op>
-__device__ __forceinline__ float cta_reduce(float v, float *scratch) {
+__device__ __forceinline__ typename Op::Acc cta_reduce(typename Op::Acc v,
+                                                       float *scratch) {
+  using A = typename Op::Acc;
+  static_assert(sizeof(A) == 4, "accumulators are 32-bit");
+  A *words = reinterpret_cast<A *>(scratch);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nwarps = (blockDim.x + 31) >> 5;
   v = warp_reduce<Op>(v);
   __syncthreads();  // scratch may still be read from a previous call
-  if (lane == 0) scratch[warp] = v;
+  if (lane == 0) words[warp] = v;
   __syncthreads();
-  float r = lane < nwarps ? scratch[lane] : Op::identity();
+  A r = lane < nwarps ? words[lane] : Op::identity();
   return warp_reduce<Op>(r);
 }
 

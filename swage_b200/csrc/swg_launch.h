@@ -74,9 +74,11 @@ cudaError_t launch_segreduce_sum_max(const float *values,
                                      int32_t segment_count, int sm_count,
                                      cudaStream_t stream, const Probe *probe);
 // One tile task per warp, two per CTA + merge pass.
-cudaError_t launch_segreduce_split(int kind, const float *values, float *out,
-                                   int32_t value_count, const DevicePlan &plan,
-                                   cudaStream_t stream, const Probe *probe);
+// (dtype: SWG_DTYPE_*; `out` holds fp32, or int32 for i32 values)
+cudaError_t launch_segreduce_split(int kind, int dtype, const void *values,
+                                   void *out, int32_t value_count,
+                                   const DevicePlan &plan, cudaStream_t stream,
+                                   const Probe *probe);
 // Persistent CTAs, bulk-copy ring, ticket counter + merge pass.
 cudaError_t launch_segreduce_persistent(int kind, const float *values,
                                         float *out, int32_t value_count,
@@ -85,10 +87,16 @@ cudaError_t launch_segreduce_persistent(int kind, const float *values,
                                         const Probe *probe);
 // One resident CTA per SM, one stage per warp, tasks at a fixed stride +
 // merge pass.
-cudaError_t launch_segreduce_resident(int kind, const float *values,
-                                      float *out, int32_t value_count,
+cudaError_t launch_segreduce_resident(int kind, int dtype, const void *values,
+                                      void *out, int32_t value_count,
                                       const DevicePlan &plan,
                                       cudaStream_t stream, const Probe *probe);
+// A warp or a CTA per segment for f16 / bf16 / i32 values (no plan).
+cudaError_t launch_segreduce_typed(int kind, int dtype, const void *values,
+                                   const int32_t *offsets, void *out,
+                                   int32_t value_count, int32_t segment_count,
+                                   bool cta, int sm_count, cudaStream_t stream,
+                                   const Probe *probe);
 cudaError_t configure_segreduce_kernels();
 cudaError_t configure_softmax_kernels();
 

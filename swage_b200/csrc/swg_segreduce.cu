@@ -99,6 +99,48 @@ segreduce_sum_max_kernel(const float *__restrict__ values,
 }
 
 // ---------------------------------------------------------------------------
+// warp or CTA per segment for f16 / bf16 / i32 values: the plan-free mapping
+// of small inputs.  Coalesced element loads, four accumulators per thread.
+// ---------------------------------------------------------------------------
+template <class Op, class T, bool kCta>
+__global__ void __launch_bounds__(kWarpKernelThreads)
+segreduce_typed_kernel(const T *__restrict__ values,
+                       const int32_t *__restrict__ offsets,
+                       typename Op::Acc *__restrict__ out,
+                       int32_t segment_count) {
+  using A = typename Op::Acc;
+  __shared__ float scratch[32];
+  const int lane = threadIdx.x & 31;
+  const int rank = kCta ? (int)threadIdx.x : lane;
+  const int width = kCta ? kWarpKernelThreads : kWarp;
+  const int64_t first =
+      kCta ? (int64_t)blockIdx.x
+           : ((int64_t)blockIdx.x * kWarpKernelThreads + threadIdx.x) >> 5;
+  const int64_t stride =
+      kCta ? (int64_t)gridDim.x
+           : ((int64_t)gridDim.x * kWarpKernelThreads) >> 5;
+  for (int64_t seg = first; seg < segment_count; seg += stride) {
+    const int64_t begin = __ldg(offsets + seg);
+    const int64_t end = __ldg(offsets + seg + 1);
+    A a0 = Op::identity(), a1 = Op::identity(), a2 = Op::identity(),
+      a3 = Op::identity();
+    int64_t i = begin + rank;
+    for (; i + 3 * width < end; i += 4 * width) {
+      const T q0 = values[i], q1 = values[i + width],
+              q2 = values[i + 2 * width], q3 = values[i + 3 * width];
+      a0 = Op::apply(a0, Elem<T>::get(q0));
+      a1 = Op::apply(a1, Elem<T>::get(q1));
+      a2 = Op::apply(a2, Elem<T>::get(q2));
+      a3 = Op::apply(a3, Elem<T>::get(q3));
+    }
+    for (; i < end; i += width) a0 = Op::apply(a0, Elem<T>::get(values[i]));
+    A r = Op::apply(Op::apply(a0, a1), Op::apply(a2, a3));
+    r = kCta ? cta_reduce<Op>(r, scratch) : warp_reduce<Op>(r);
+    if (rank == 0) out[seg] = r;
+  }
+}
+
+// ---------------------------------------------------------------------------
 // CTA per segment
 // ---------------------------------------------------------------------------
 template <class Op>
@@ -150,10 +192,18 @@ static_assert(kTileItems + 3 + 3 + 8 <= kTileFloats,
               "values, padding and offsets of a packed task fit one stage");
 static_assert(kStatusWord == 12, "report() reads control[12..13]");
 
-// First tile slot of the offsets of a packed task: the 16-byte line after
-// its values.
-__device__ __forceinline__ int offsets_base(int shift, int vcount) {
-  return (shift + vcount + 3) & ~3;
+// Elements of type T per 16-byte line, and the first 32-bit word of the
+// offsets of a packed task in its stage: the 16-byte line after its values.
+template <class T>
+constexpr int kPerLine = 16 / (int)sizeof(T);
+// Phase of the values pointer inside a 16-byte line, in elements.
+template <class T>
+__device__ __forceinline__ int value_phase(const T *values) {
+  return (int)(((uintptr_t)values / sizeof(T)) & (kPerLine<T> - 1));
+}
+template <class T>
+__device__ __forceinline__ int offsets_word(int shift, int vcount) {
+  return (((shift + vcount) * (int)sizeof(T) + 15) >> 4) << 2;
 }
 constexpr uint32_t kTaskStop = 15u;  // sentinel kind: no more tasks
 
@@ -164,7 +214,7 @@ constexpr uint32_t kTaskStop = 15u;  // sentinel kind: no more tasks
 constexpr int kSplitWarps = SWG_SPLIT_WARPS;  // split: tasks per CTA, one stage each
 
 struct Stage {
-  float *tile;
+  unsigned char *tile;  // element i of the task at ((T *)tile)[i - origin]
 };
 
 // Per-warp lists of the segments (of the current 32) that more than one lane
@@ -172,13 +222,13 @@ struct Stage {
 struct WarpScratch {
   int begin[32];
   int end[32];
-  float result[32];
+  uint32_t result[32];  // accumulator words (fp32 or int32)
 };
 
 __device__ __forceinline__ Stage stage_at(unsigned char *base, int index) {
   unsigned char *p = base + (size_t)index * kStageBytes;
   Stage s;
-  s.tile = reinterpret_cast<float *>(p);
+  s.tile = p;
   return s;
 }
 
@@ -280,21 +330,25 @@ __device__ __forceinline__ bool task_ok(const Task &t, const Limits &limits) {
 // The lines of `values` a task's bulk copy takes: every 16-byte line that
 // intersects the task's value range and lies wholly inside the values array
 // (neighbouring elements that ride along are never read).  Element i lands at
-// tile[i - origin] with origin = vbegin - ((vbegin + mis) & 3); `mis` is the
-// phase of the values pointer inside a 16-byte line, in elements.
+// tile[i - origin] with origin = vbegin - ((vbegin + mis) mod P), P the
+// elements per line; `mis` is the phase of the values pointer inside a 16-byte
+// line, in elements.
 struct CopyRange {
   int64_t origin, lo, hi;  // copy [lo, hi); hi <= lo: nothing to copy
 };
 
+template <class T>
 __device__ __forceinline__ CopyRange copy_range(const Task &task, int mis,
                                                 int32_t value_count) {
+  constexpr int P = kPerLine<T>;
   const int64_t vb = task.vbegin;
   const int64_t ve = vb + (int64_t)(task.vcount_kind & kTaskCountMask);
   CopyRange r;
-  r.origin = vb - ((vb + mis) & 3);
-  r.lo = r.origin < 0 ? r.origin + 4 : r.origin;
-  r.hi = ve + ((4 - ((ve + mis) & 3)) & 3);
-  const int64_t last_line = (int64_t)value_count - ((value_count + mis) & 3);
+  r.origin = vb - ((vb + mis) & (P - 1));
+  r.lo = r.origin < 0 ? r.origin + P : r.origin;
+  r.hi = ve + ((P - ((ve + mis) & (P - 1))) & (P - 1));
+  const int64_t last_line =
+      (int64_t)value_count - ((value_count + mis) & (P - 1));
   if (r.hi > last_line) r.hi = last_line;
   if (r.hi < r.lo) r.hi = r.lo;
   return r;
@@ -303,24 +357,26 @@ __device__ __forceinline__ CopyRange copy_range(const Task &task, int mis,
 // Stage one task; runs entirely in the calling thread.  The at most three
 // elements at either end of the array that no whole line covers are fetched
 // with plain loads.
+template <class T>
 __device__ __forceinline__ void issue_task(const Task &task,
-                                           const float *__restrict__ values,
+                                           const T *__restrict__ values,
                                            int mis, int32_t value_count,
                                            const int32_t *__restrict__ d_off,
                                            Stage stage, uint64_t *full) {
   const uint32_t kind = task.vcount_kind >> 28;
   const int64_t vb = task.vbegin;
   const int64_t ve = vb + (int64_t)(task.vcount_kind & kTaskCountMask);
-  const CopyRange r = copy_range(task, mis, value_count);
+  const CopyRange r = copy_range<T>(task, mis, value_count);
   const int64_t origin = r.origin, lo = r.lo, hi = r.hi;
+  T *tile = reinterpret_cast<T *>(stage.tile);
   if (lo > vb || hi < ve) {
     // only the first and the last task of an array can get here
     for (int64_t idx = vb; idx < ve && idx < lo; ++idx)
-      stage.tile[idx - origin] = values[idx];
+      tile[idx - origin] = values[idx];
     for (int64_t idx = hi > vb ? hi : vb; idx < ve; ++idx)
-      if (idx >= hi || idx < lo) stage.tile[idx - origin] = values[idx];
+      if (idx >= hi || idx < lo) tile[idx - origin] = values[idx];
   }
-  const uint32_t bytes_v = (uint32_t)(hi - lo) * 4u;
+  const uint32_t bytes_v = (uint32_t)(hi - lo) * (uint32_t)sizeof(T);
   uint32_t bytes_o = 0;
   int32_t o_lo = 0;
   if (kind == kTaskPack) {
@@ -332,70 +388,75 @@ __device__ __forceinline__ void issue_task(const Task &task,
   // below write it through the async proxy
   fence_proxy_async();
   mbar_arrive_expect_tx(full, bytes_v + bytes_o);
-  if (bytes_v) bulk_g2s(stage.tile + (lo - origin), values + lo, bytes_v, full);
+  if (bytes_v) bulk_g2s(tile + (lo - origin), values + lo, bytes_v, full);
   if (bytes_o)
-    bulk_g2s(stage.tile + offsets_base((int)(vb - origin), (int)(ve - vb)),
+    bulk_g2s(reinterpret_cast<int32_t *>(stage.tile) +
+                 offsets_word<T>((int)(vb - origin), (int)(ve - vb)),
              d_off + o_lo, bytes_o, full);
 }
 
 // 128-bit load from a stage, explicitly in the shared window.
-__device__ __forceinline__ float4 lds4(const float4 *p) {
-  float4 q;
-  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(q.x), "=f"(q.y), "=f"(q.z), "=f"(q.w)
+__device__ __forceinline__ uint4 lds_line(const void *p) {
+  uint4 q;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
                : "r"(smem_u32(p)));
   return q;
 }
 
-// Warp-collective: reduces tile[lo, hi) -- scalar ends, 128-bit body, four
-// independent accumulators per lane -- and returns the result to every lane.
-template <class Op>
-__device__ __forceinline__ float warp_range(const float *tile, int lo, int hi,
-                                            int lane) {
-  int blo = (lo + 3) & ~3, bhi = hi & ~3;
+// Warp-collective: reduces tile[lo, hi) (element indices) -- scalar ends,
+// 128-bit body, four independent accumulators per lane -- and returns the
+// result to every lane.
+template <class Op, class T>
+__device__ __forceinline__ typename Op::Acc warp_range(const T *tile, int lo,
+                                                       int hi, int lane) {
+  using A = typename Op::Acc;
+  constexpr int P = kPerLine<T>;
+  int blo = (lo + P - 1) & ~(P - 1), bhi = hi & ~(P - 1);
   if (blo > bhi) blo = bhi = hi;  // too short for an aligned body
   const int head_end = blo < hi ? blo : hi;
-  float a0 = Op::identity(), a1 = Op::identity(), a2 = Op::identity(),
-        a3 = Op::identity();
-  if (lo + lane < head_end) a0 = Op::apply(a0, tile[lo + lane]);
-  const float4 *body = reinterpret_cast<const float4 *>(tile);
-  const int vlo = blo >> 2, vhi = bhi >> 2;
+  A a0 = Op::identity(), a1 = Op::identity(), a2 = Op::identity(),
+    a3 = Op::identity();
+  if (lo + lane < head_end) a0 = Op::apply(a0, Elem<T>::get(tile[lo + lane]));
+  const uint4 *body = reinterpret_cast<const uint4 *>(tile);
+  const int vlo = blo / P, vhi = bhi / P;
   int v = vlo + lane;
   for (; v + 96 < vhi; v += 128) {
-    const float4 q0 = lds4(body + v), q1 = lds4(body + v + 32),
-                 q2 = lds4(body + v + 64), q3 = lds4(body + v + 96);
-    a0 = fold4<Op>(a0, q0);
-    a1 = fold4<Op>(a1, q1);
-    a2 = fold4<Op>(a2, q2);
-    a3 = fold4<Op>(a3, q3);
+    const uint4 q0 = lds_line(body + v), q1 = lds_line(body + v + 32),
+                q2 = lds_line(body + v + 64), q3 = lds_line(body + v + 96);
+    a0 = fold_line<Op, T>(a0, q0);
+    a1 = fold_line<Op, T>(a1, q1);
+    a2 = fold_line<Op, T>(a2, q2);
+    a3 = fold_line<Op, T>(a3, q3);
   }
-  for (; v < vhi; v += 32) a0 = fold4<Op>(a0, lds4(body + v));
+  for (; v < vhi; v += 32) a0 = fold_line<Op, T>(a0, lds_line(body + v));
   const int tail = bhi > head_end ? bhi : head_end;
-  if (tail + lane < hi) a1 = Op::apply(a1, tile[tail + lane]);
+  if (tail + lane < hi) a1 = Op::apply(a1, Elem<T>::get(tile[tail + lane]));
   return warp_reduce<Op>(Op::apply(Op::apply(a0, a1), Op::apply(a2, a3)));
 }
 
 // Warp-collective: reduce one staged task.
-template <class Op>
-__device__ __forceinline__ void process_task(const Task &task,
-                                             const Stage &stage, int mis,
-                                             float *__restrict__ out,
-                                             float *__restrict__ partials,
-                                             WarpScratch *scratch,
-                                             const Limits &limits,
-                                             uint32_t *control, int lane) {
+template <class Op, class T>
+__device__ __forceinline__ void process_task(
+    const Task &task, const Stage &stage, int mis,
+    typename Op::Acc *__restrict__ out,
+    typename Op::Acc *__restrict__ partials, WarpScratch *scratch,
+    const Limits &limits, uint32_t *control, int lane) {
+  using A = typename Op::Acc;
+  constexpr int P = kPerLine<T>;
   if (!task_ok(task, limits)) {
     if (lane == 0) report(control, kErrBadTask, (uint32_t)task.seg);
     return;
   }
   const uint32_t kind = task.vcount_kind >> 28;
   const int vcount = (int)(task.vcount_kind & kTaskCountMask);
-  const int shift = (int)(((int64_t)task.vbegin + mis) & 3);
-  const float *tile = stage.tile;
+  const int shift = (int)(((int64_t)task.vbegin + mis) & (P - 1));
+  const T *tile = reinterpret_cast<const T *>(stage.tile);
+  A *results = reinterpret_cast<A *>(scratch->result);
 
   if (kind == kTaskChunk) {
     // One piece of a long segment occupies tile[shift, shift + vcount).
-    const float r = warp_range<Op>(tile, shift, shift + vcount, lane);
+    const A r = warp_range<Op, T>(tile, shift, shift + vcount, lane);
     if (lane == 0) {
       if (task.count < 0) out[task.seg] = r;
       else partials[task.count] = r;
@@ -411,9 +472,8 @@ __device__ __forceinline__ void process_task(const Task &task,
   // Listed results come back through the warp's scratch to their owning
   // lanes, so the 32 results leave in one coalesced store.  Tile-relative
   // bounds of segment k are soff[k] - origin and soff[k + 1] - origin.
-  const int32_t *soff =
-      reinterpret_cast<const int32_t *>(tile + offsets_base(shift, vcount)) +
-      (task.seg & 3);
+  const int32_t *soff = reinterpret_cast<const int32_t *>(stage.tile) +
+                        offsets_word<T>(shift, vcount) + (task.seg & 3);
   const int origin = task.vbegin - shift;
   const unsigned below = (1u << lane) - 1u;
   const int group = lane >> 3, sub = lane & 7;
@@ -437,7 +497,7 @@ __device__ __forceinline__ void process_task(const Task &task,
       a = b = shift;
     }
     const int length = b - a;
-    float acc = Op::identity();
+    A acc = Op::identity();
     const bool medium =
         valid && length > kLaneSegment && length <= kGroupSegment;
     const bool wide = valid && length > kGroupSegment;
@@ -446,26 +506,27 @@ __device__ __forceinline__ void process_task(const Task &task,
     // segment's end hold the identity, which leaves the result unchanged
     const bool tiny = valid && length <= kLaneSegment;
     if (tiny) {
-      float x[8];
+      A x[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i)
-        x[i] = a + i < b ? tile[a + i] : Op::identity();
+        x[i] = a + i < b ? Elem<T>::get(tile[a + i]) : Op::identity();
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc = Op::apply(acc, x[i]);
     }
     if (__any_sync(kFullMask, tiny && length > 8)) {
       if (tiny) {
-        float x[8];
+        A x[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          x[i] = a + 8 + i < b ? tile[a + 8 + i] : Op::identity();
+          x[i] = a + 8 + i < b ? Elem<T>::get(tile[a + 8 + i])
+                               : Op::identity();
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc = Op::apply(acc, x[i]);
       }
     }
     const unsigned medium_mask = __ballot_sync(kFullMask, medium);
     const unsigned wide_mask = __ballot_sync(kFullMask, wide);
-    float *target = out + task.seg + k;
+    A *target = out + task.seg + k;
     if (head_piece) target = partials + task.head_slot;
     if (tail_piece) target = partials + task.tail_slot;
     if ((medium_mask | wide_mask) == 0) {
@@ -484,48 +545,48 @@ __device__ __forceinline__ void process_task(const Task &task,
     __syncwarp();
     for (int e = group; e < medium_count; e += 4) {
       const int ea = scratch->begin[e], eb = scratch->end[e];
-      float p0 = Op::identity(), p1 = Op::identity(), p2 = Op::identity(),
-            p3 = Op::identity();
+      A p0 = Op::identity(), p1 = Op::identity(), p2 = Op::identity(),
+        p3 = Op::identity();
       int i = ea + sub;
       for (; i + 24 < eb; i += 32) {
-        p0 = Op::apply(p0, tile[i]);
-        p1 = Op::apply(p1, tile[i + 8]);
-        p2 = Op::apply(p2, tile[i + 16]);
-        p3 = Op::apply(p3, tile[i + 24]);
+        p0 = Op::apply(p0, Elem<T>::get(tile[i]));
+        p1 = Op::apply(p1, Elem<T>::get(tile[i + 8]));
+        p2 = Op::apply(p2, Elem<T>::get(tile[i + 16]));
+        p3 = Op::apply(p3, Elem<T>::get(tile[i + 24]));
       }
-      for (; i < eb; i += 8) p0 = Op::apply(p0, tile[i]);
-      float r = Op::apply(Op::apply(p0, p1), Op::apply(p2, p3));
+      for (; i < eb; i += 8) p0 = Op::apply(p0, Elem<T>::get(tile[i]));
+      A r = Op::apply(Op::apply(p0, p1), Op::apply(p2, p3));
       r = Op::apply(r, __shfl_xor_sync(group_mask, r, 4));
       r = Op::apply(r, __shfl_xor_sync(group_mask, r, 2));
       r = Op::apply(r, __shfl_xor_sync(group_mask, r, 1));
-      if (sub == 0) scratch->result[e] = r;
+      if (sub == 0) results[e] = r;
     }
     __syncwarp();
     for (int e = medium_count; e < listed; ++e) {
       // (the 128-bit range reduce of the chunk path was tried here: same
       // speed on the lognormal workload, eight more registers everywhere)
 #if SWG_WIDE_VECTOR
-      const float r =
-          warp_range<Op>(tile, scratch->begin[e], scratch->end[e], lane);
+      const A r =
+          warp_range<Op, T>(tile, scratch->begin[e], scratch->end[e], lane);
 #else
       const int ea = scratch->begin[e], eb = scratch->end[e];
-      float p0 = Op::identity(), p1 = Op::identity(), p2 = Op::identity(),
-            p3 = Op::identity();
+      A p0 = Op::identity(), p1 = Op::identity(), p2 = Op::identity(),
+        p3 = Op::identity();
       int i = ea + lane;
       for (; i + 96 < eb; i += 128) {
-        p0 = Op::apply(p0, tile[i]);
-        p1 = Op::apply(p1, tile[i + 32]);
-        p2 = Op::apply(p2, tile[i + 64]);
-        p3 = Op::apply(p3, tile[i + 96]);
+        p0 = Op::apply(p0, Elem<T>::get(tile[i]));
+        p1 = Op::apply(p1, Elem<T>::get(tile[i + 32]));
+        p2 = Op::apply(p2, Elem<T>::get(tile[i + 64]));
+        p3 = Op::apply(p3, Elem<T>::get(tile[i + 96]));
       }
-      for (; i < eb; i += 32) p0 = Op::apply(p0, tile[i]);
-      const float r =
+      for (; i < eb; i += 32) p0 = Op::apply(p0, Elem<T>::get(tile[i]));
+      const A r =
           warp_reduce<Op>(Op::apply(Op::apply(p0, p1), Op::apply(p2, p3)));
 #endif
-      if (lane == 0) scratch->result[e] = r;
+      if (lane == 0) results[e] = r;
     }
     __syncwarp();
-    if (slot >= 0) acc = scratch->result[slot];
+    if (slot >= 0) acc = results[slot];
     if (valid) *target = acc;
     __syncwarp();  // the lists are rewritten by the next 32 segments
   }
@@ -541,20 +602,20 @@ __device__ __forceinline__ void process_task(const Task &task,
 // find their lines on the way instead of starting a cold DRAM round trip
 // after the wait.  The caller's arrays are read into the SM and written only
 // after the kernel before has finished.
-template <class Op>
+template <class Op, class T>
 __global__ void __launch_bounds__(kSplitWarps * 32)
-segreduce_split_kernel(const float *__restrict__ values,
-                       float *__restrict__ out, int32_t value_count,
+segreduce_split_kernel(const T *__restrict__ values,
+                       typename Op::Acc *__restrict__ out, int32_t value_count,
                        const Task *__restrict__ tasks, int32_t task_count,
                        const int32_t *__restrict__ d_off,
-                       float *__restrict__ partials,
+                       typename Op::Acc *__restrict__ partials,
                        uint32_t *__restrict__ control, Limits limits,
                        uint32_t prefetch_ctas) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full[kSplitWarps];
   __shared__ WarpScratch scratch[kSplitWarps];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int mis = (int)(((uintptr_t)values >> 2) & 3);
+  const int mis = value_phase(values);
   // let the kernel that follows in the stream be placed as soon as slots free
   // up; it waits for this grid to finish before it touches anything of the
   // caller's
@@ -570,9 +631,10 @@ segreduce_split_kernel(const float *__restrict__ values,
   const Stage stage = stage_at(smem, warp);
   const bool ok = task_ok(task, limits);
   if (ok && lane == 0 && blockIdx.x < prefetch_ctas) {
-    const CopyRange r = copy_range(task, mis, value_count);
+    const CopyRange r = copy_range<T>(task, mis, value_count);
     if (r.hi > r.lo)
-      bulk_prefetch_l2(values + r.lo, (uint32_t)(r.hi - r.lo) * 4u);
+      bulk_prefetch_l2(values + r.lo,
+                       (uint32_t)(r.hi - r.lo) * (uint32_t)sizeof(T));
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (!ok) {
@@ -585,8 +647,8 @@ segreduce_split_kernel(const float *__restrict__ values,
     if (lane == 0) report(control, kErrTimeout, (uint32_t)index);
     return;
   }
-  process_task<Op>(task, stage, mis, out, partials, &scratch[warp], limits,
-                   control, lane);
+  process_task<Op, T>(task, stage, mis, out, partials, &scratch[warp], limits,
+                      control, lane);
 }
 
 // persistent schedule: one resident CTA per SM, every warp an independent
@@ -605,13 +667,13 @@ segreduce_persistent_kernel(const float *__restrict__ values,
                             float *__restrict__ out, int32_t value_count,
                             const Task *__restrict__ tasks, int32_t task_count,
                             const int32_t *__restrict__ d_off,
-                       float *__restrict__ partials,
+                            float *__restrict__ partials,
                             uint32_t *__restrict__ control, Limits limits) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full[kWarps * kStages];
   __shared__ WarpScratch scratch[kWarps];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int mis = (int)(((uintptr_t)values >> 2) & 3);
+  const int mis = value_phase(values);
   uint64_t *bars = full + warp * kStages;
   unsigned char *ring = smem + (size_t)warp * kStages * kStageBytes;
   if (lane == 0) {
@@ -674,8 +736,8 @@ segreduce_persistent_kernel(const float *__restrict__ values,
         running = false;
         break;
       }
-      process_task<Op>(t, stage_at(ring, s), mis, out, partials,
-                       &scratch[warp], limits, control, lane);
+      process_task<Op, float>(t, stage_at(ring, s), mis, out, partials,
+                              &scratch[warp], limits, control, lane);
       __syncwarp();  // every lane is done with the stage before it is refilled
       const Task n = shuffle_task(nxt, s);
       if (!is_stop(n)) stage_in(n, s);
@@ -714,20 +776,21 @@ segreduce_persistent_kernel(const float *__restrict__ values,
 // hold many segments (their reduction keeps a stage busy longest), 7 % slower
 // where nearly every tile is a chunk of a long segment -- the planner picks by
 // the share of values in long segments.
-template <class Op, int kWarps>
+template <class Op, class T, int kWarps>
 __global__ void __launch_bounds__(kWarps * 32, 1)
-segreduce_resident_kernel(const float *__restrict__ values,
-                          float *__restrict__ out, int32_t value_count,
+segreduce_resident_kernel(const T *__restrict__ values,
+                          typename Op::Acc *__restrict__ out,
+                          int32_t value_count,
                           const Task *__restrict__ tasks, int32_t task_count,
                           const int32_t *__restrict__ d_off,
-                       float *__restrict__ partials,
+                          typename Op::Acc *__restrict__ partials,
                           uint32_t *__restrict__ control, Limits limits) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full[kWarps];
   __shared__ WarpScratch scratch[kWarps];
   __shared__ int next_round;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int mis = (int)(((uintptr_t)values >> 2) & 3);
+  const int mis = value_phase(values);
   asm volatile("griddepcontrol.launch_dependents;");
   if (lane == 0) {
     mbar_init(&full[warp], 1);
@@ -748,9 +811,10 @@ segreduce_resident_kernel(const float *__restrict__ values,
   // the first tile of every warp: L2 starts fetching it while the kernel
   // before this one drains (see segreduce_split_kernel)
   if (lane == 0 && task_ok(task, limits)) {
-    const CopyRange r = copy_range(task, mis, value_count);
+    const CopyRange r = copy_range<T>(task, mis, value_count);
     if (r.hi > r.lo)
-      bulk_prefetch_l2(values + r.lo, (uint32_t)(r.hi - r.lo) * 4u);
+      bulk_prefetch_l2(values + r.lo,
+                       (uint32_t)(r.hi - r.lo) * (uint32_t)sizeof(T));
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   uint32_t parity = 0;
@@ -773,8 +837,8 @@ segreduce_resident_kernel(const float *__restrict__ values,
       return;
     }
     parity ^= 1u;
-    process_task<Op>(task, stage, mis, out, partials, &scratch[warp], limits,
-                     control, lane);
+    process_task<Op, T>(task, stage, mis, out, partials, &scratch[warp],
+                        limits, control, lane);
     if (!more) return;
     __syncwarp();  // every lane is done with the stage before it is refilled
     task = next;
@@ -807,8 +871,9 @@ segreduce_merge_kernel(const MergeRecord *__restrict__ records, int32_t count,
                        uint32_t record_ctas,
                        const MergeRecord *__restrict__ bigs,
                        const int32_t *__restrict__ big_count,
-                       const float *__restrict__ partials,
-                       float *__restrict__ out, Limits limits) {
+                       const typename Op::Acc *__restrict__ partials,
+                       typename Op::Acc *__restrict__ out, Limits limits) {
+  using A = typename Op::Acc;
   __shared__ float scratch[32];
   // the next launch in the stream, if it is one of the tile kernels, may
   // place its CTAs and fetch its descriptors while this grid runs
@@ -831,11 +896,11 @@ segreduce_merge_kernel(const MergeRecord *__restrict__ records, int32_t count,
     // (all the loads of a segment are issued before the first is used: one
     // round trip to L2, where the partials were just written, per segment)
     if (small) {
-      float q[kLaneMerge];
+      A q[kLaneMerge];
 #pragma unroll
       for (int k = 0; k < kLaneMerge; ++k)
         if (k < r.pieces) q[k] = partials[piece_slot(r.first, k, step)];
-      float acc = Op::identity();
+      A acc = Op::identity();
 #pragma unroll
       for (int k = 0; k < kLaneMerge; ++k)
         if (k < r.pieces) acc = Op::apply(acc, q[k]);
@@ -848,12 +913,12 @@ segreduce_merge_kernel(const MergeRecord *__restrict__ records, int32_t count,
       const int seg = __shfl_sync(kFullMask, r.seg, src);
       const int first = __shfl_sync(kFullMask, r.first, src);
       const int pieces = __shfl_sync(kFullMask, r.pieces, src);
-      float q[kWarpMerge / 32];
+      A q[kWarpMerge / 32];
 #pragma unroll
       for (int u = 0; u < kWarpMerge / 32; ++u)
         if (lane + 32 * u < pieces)
           q[u] = partials[piece_slot(first, lane + 32 * u, step)];
-      float acc = Op::identity();
+      A acc = Op::identity();
 #pragma unroll
       for (int u = 0; u < kWarpMerge / 32; ++u)
         if (lane + 32 * u < pieces) acc = Op::apply(acc, q[u]);
@@ -873,10 +938,10 @@ segreduce_merge_kernel(const MergeRecord *__restrict__ records, int32_t count,
       // sixteen partials per thread are requested before the first is
       // used: a segment of up to 16 * kMergeThreads pieces costs one round
       // trip to L2
-      float a[4] = {Op::identity(), Op::identity(), Op::identity(),
-                    Op::identity()};
+      A a[4] = {Op::identity(), Op::identity(), Op::identity(),
+                Op::identity()};
       for (int k = tid; k < pieces; k += 16 * kMergeThreads) {
-        float q[16];
+        A q[16];
 #pragma unroll
         for (int u = 0; u < 16; ++u)
           if (k + u * kMergeThreads < pieces)
@@ -886,9 +951,9 @@ segreduce_merge_kernel(const MergeRecord *__restrict__ records, int32_t count,
           if (k + u * kMergeThreads < pieces)
             a[u & 3] = Op::apply(a[u & 3], q[u]);
       }
-      const float mine =
+      const A mine =
           Op::apply(Op::apply(a[0], a[1]), Op::apply(a[2], a[3]));
-      const float v = cta_reduce<Op>(mine, scratch);
+      const A v = cta_reduce<Op>(mine, scratch);
       if (tid == 0 && valid) out[r.seg] = v;
       i += stride;
       if (i < total) r = bigs[i];
@@ -959,26 +1024,83 @@ static cudaError_t with_op(int kind, F &&f) {
   }
 }
 
+// Calls f with the operator and element types of (kind, dtype).
+template <class F>
+static cudaError_t with_types(int kind, int dtype, F &&f) {
+  switch (dtype) {
+    case SWG_DTYPE_F16:
+      return with_op(kind, [&](auto op) { return f(op, __half{}); });
+    case SWG_DTYPE_BF16:
+      return with_op(kind, [&](auto op) { return f(op, __nv_bfloat16{}); });
+    case SWG_DTYPE_I32:
+      switch (kind) {
+        case SWG_KIND_SUM: return f(ISumOp{}, int32_t{});
+        case SWG_KIND_MAX: return f(IMaxOp{}, int32_t{});
+        default: return f(IMinOp{}, int32_t{});
+      }
+    default:
+      return with_op(kind, [&](auto op) { return f(op, float{}); });
+  }
+}
+
 cudaError_t configure_segreduce_kernels() {
   DevicePlan none;
   for (int kind : {SWG_KIND_SUM, SWG_KIND_MAX, SWG_KIND_MIN}) {
     cudaError_t e = with_op(kind, [&](auto op) {
-      using Op = decltype(op);
-      cudaError_t inner =
-          persistent_dispatch<Op>(nullptr, nullptr, 0, none, nullptr, true);
-      if (inner != cudaSuccess) return inner;
-      inner = cudaFuncSetAttribute(
-          segreduce_resident_kernel<Op, kResidentWarps>,
-          cudaFuncAttributeMaxDynamicSharedMemorySize,
-          kResidentWarps * kStageBytes);
-      if (inner != cudaSuccess) return inner;
-      return cudaFuncSetAttribute(segreduce_split_kernel<Op>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kSplitBytes);
+      return persistent_dispatch<decltype(op)>(nullptr, nullptr, 0, none,
+                                               nullptr, true);
     });
     if (e != cudaSuccess) return e;
+    for (int dtype : {SWG_DTYPE_F32, SWG_DTYPE_F16, SWG_DTYPE_BF16,
+                      SWG_DTYPE_I32}) {
+      e = with_types(kind, dtype, [&](auto op, auto element) {
+        using Op = decltype(op);
+        using T = decltype(element);
+        const cudaError_t inner = cudaFuncSetAttribute(
+            segreduce_resident_kernel<Op, T, kResidentWarps>,
+            cudaFuncAttributeMaxDynamicSharedMemorySize,
+            kResidentWarps * kStageBytes);
+        if (inner != cudaSuccess) return inner;
+        return cudaFuncSetAttribute(segreduce_split_kernel<Op, T>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kSplitBytes);
+      });
+      if (e != cudaSuccess) return e;
+    }
   }
   return cudaSuccess;
+}
+
+// Plan-free launch for the element types other than f32.
+cudaError_t launch_segreduce_typed(int kind, int dtype, const void *values,
+                                   const int32_t *offsets, void *out,
+                                   int32_t value_count, int32_t segment_count,
+                                   bool cta, int sm_count, cudaStream_t stream,
+                                   const Probe *probe) {
+  const int per_cta = cta ? 1 : kWarpKernelThreads / 32;
+  int64_t grid = ((int64_t)segment_count + per_cta - 1) / per_cta;
+  const int64_t cap = (int64_t)sm_count * 8 * 4;
+  if (grid > cap) grid = cap;
+  probe_begin(probe, stream);
+  const cudaError_t e = with_types(kind, dtype, [&](auto op, auto element) {
+    using Op = decltype(op);
+    using T = decltype(element);
+    using A = typename Op::Acc;
+    if (cta)
+      segreduce_typed_kernel<Op, T, true>
+          <<<(unsigned)grid, kWarpKernelThreads, 0, stream>>>(
+              static_cast<const T *>(values), offsets, static_cast<A *>(out),
+              segment_count);
+    else
+      segreduce_typed_kernel<Op, T, false>
+          <<<(unsigned)grid, kWarpKernelThreads, 0, stream>>>(
+              static_cast<const T *>(values), offsets, static_cast<A *>(out),
+              segment_count);
+    return cudaGetLastError();
+  });
+  probe_end(probe, stream);
+  (void)value_count;
+  return e;
 }
 
 cudaError_t launch_segreduce_warp(int kind, const float *values,
@@ -1065,8 +1187,9 @@ static cudaError_t launch_serialised(Kernel kernel, unsigned grid,
   return cudaLaunchKernelEx(&config, kernel, args...);
 }
 
-static cudaError_t launch_merge(int kind, const DevicePlan &plan, float *out,
-                                int32_t value_count, cudaStream_t stream) {
+static cudaError_t launch_merge(int kind, int dtype, const DevicePlan &plan,
+                                void *out, int32_t value_count,
+                                cudaStream_t stream) {
   if (plan.merge_count == 0 && plan.big_capacity == 0) return cudaSuccess;
   const unsigned record_ctas =
       (unsigned)(((int64_t)plan.merge_count + kMergeThreads - 1) /
@@ -1075,37 +1198,45 @@ static cudaError_t launch_merge(int kind, const DevicePlan &plan, float *out,
   // than two rounds of the machine (they loop over the list)
   int big_ctas = plan.big_capacity;
   if (big_ctas > 2 * plan.sm_count) big_ctas = 2 * plan.sm_count;
-  return with_op(kind, [&](auto op) {
+  // (the accumulator type decides: f16 / bf16 values merge as fp32)
+  const int acc_dtype = dtype == SWG_DTYPE_I32 ? SWG_DTYPE_I32 : SWG_DTYPE_F32;
+  return with_types(kind, acc_dtype, [&](auto op, auto) {
+    using Op = decltype(op);
+    using A = typename Op::Acc;
     return launch_serialised(
-        segreduce_merge_kernel<decltype(op)>, record_ctas + (unsigned)big_ctas,
+        segreduce_merge_kernel<Op>, record_ctas + (unsigned)big_ctas,
         kMergeThreads, 0, stream, (const MergeRecord *)plan.merges,
         plan.merge_count, record_ctas, (const MergeRecord *)plan.bigs,
-        (const int32_t *)plan.big_count, (const float *)plan.partials, out,
+        (const int32_t *)plan.big_count,
+        reinterpret_cast<const A *>(plan.partials), static_cast<A *>(out),
         limits_of(plan, value_count));
   });
 }
 
-cudaError_t launch_segreduce_split(int kind, const float *values, float *out,
-                                   int32_t value_count, const DevicePlan &plan,
-                                   cudaStream_t stream, const Probe *probe) {
+cudaError_t launch_segreduce_split(int kind, int dtype, const void *values,
+                                   void *out, int32_t value_count,
+                                   const DevicePlan &plan, cudaStream_t stream,
+                                   const Probe *probe) {
   if (plan.task_count == 0) return cudaSuccess;
   const unsigned grid =
       (unsigned)((plan.task_count + kSplitWarps - 1) / kSplitWarps);
   const uint32_t first_wave =
       (uint32_t)plan.sm_count * SWG_SPLIT_CTAS_PER_SM;
   probe_begin(probe, stream);
-  const cudaError_t e = with_op(kind, [&](auto op) {
+  const cudaError_t e = with_types(kind, dtype, [&](auto op, auto element) {
+    using Op = decltype(op);
+    using T = decltype(element);
+    using A = typename Op::Acc;
     return launch_serialised(
-        segreduce_split_kernel<decltype(op)>, grid, kSplitWarps * 32,
-        kSplitBytes, stream, values, out, value_count,
-        (const Task *)plan.tasks, plan.task_count,
-        (const int32_t *)plan.offsets, plan.partials, plan.control,
-        limits_of(plan, value_count), first_wave);
+        segreduce_split_kernel<Op, T>, grid, kSplitWarps * 32, kSplitBytes,
+        stream, static_cast<const T *>(values), static_cast<A *>(out),
+        value_count, (const Task *)plan.tasks, plan.task_count,
+        (const int32_t *)plan.offsets, reinterpret_cast<A *>(plan.partials),
+        plan.control, limits_of(plan, value_count), first_wave);
   });
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;
-  const cudaError_t merged = launch_merge(kind, plan, out, value_count, stream);
-  return merged;
+  return launch_merge(kind, dtype, plan, out, value_count, stream);
 }
 
 cudaError_t launch_segreduce_persistent(int kind, const float *values,
@@ -1121,11 +1252,11 @@ cudaError_t launch_segreduce_persistent(int kind, const float *values,
   });
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;
-  return launch_merge(kind, plan, out, value_count, stream);
+  return launch_merge(kind, SWG_DTYPE_F32, plan, out, value_count, stream);
 }
 
-cudaError_t launch_segreduce_resident(int kind, const float *values,
-                                      float *out, int32_t value_count,
+cudaError_t launch_segreduce_resident(int kind, int dtype, const void *values,
+                                      void *out, int32_t value_count,
                                       const DevicePlan &plan,
                                       cudaStream_t stream,
                                       const Probe *probe) {
@@ -1134,18 +1265,21 @@ cudaError_t launch_segreduce_resident(int kind, const float *values,
   const int needed = (plan.task_count + kResidentWarps - 1) / kResidentWarps;
   if (grid > needed) grid = needed;
   probe_begin(probe, stream);
-  const cudaError_t e = with_op(kind, [&](auto op) {
+  const cudaError_t e = with_types(kind, dtype, [&](auto op, auto element) {
+    using Op = decltype(op);
+    using T = decltype(element);
+    using A = typename Op::Acc;
     return launch_serialised(
-        segreduce_resident_kernel<decltype(op), kResidentWarps>,
-        (unsigned)grid, kResidentWarps * 32,
-        (size_t)kResidentWarps * kStageBytes, stream, values, out, value_count,
+        segreduce_resident_kernel<Op, T, kResidentWarps>, (unsigned)grid,
+        kResidentWarps * 32, (size_t)kResidentWarps * kStageBytes, stream,
+        static_cast<const T *>(values), static_cast<A *>(out), value_count,
         (const Task *)plan.tasks, plan.task_count,
-        (const int32_t *)plan.offsets, plan.partials, plan.control,
-        limits_of(plan, value_count));
+        (const int32_t *)plan.offsets, reinterpret_cast<A *>(plan.partials),
+        plan.control, limits_of(plan, value_count));
   });
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;
-  return launch_merge(kind, plan, out, value_count, stream);
+  return launch_merge(kind, dtype, plan, out, value_count, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -1273,8 +1407,8 @@ cudaError_t launch_segreduce_static(int kind, const float *values, float *out,
   dev.big_count = d_big_count;
   dev.big_capacity = big_total;
   dev.control = d_control;
-  return launch_segreduce_split(kind, values, out, value_count, dev, stream,
-                                nullptr);
+  return launch_segreduce_split(kind, SWG_DTYPE_F32, values, out, value_count,
+                                dev, stream, nullptr);
 }
 
 }  // namespace swg
