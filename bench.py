@@ -847,6 +847,11 @@ def run_ours(args):
     e2e_steps = args.e2e_steps or max(1, min(args.steps, 5))
     e2e_ms, h2d, d2h, host_sources = measure_e2e(problem, e2e_steps, barrier)
     h2d_rank_gbs = h2d * e2e_steps / (e2e_ms * 1e-3) / 1e9
+    if world > 1:
+        rates = torch.zeros(world, device=device, dtype=torch.float64)
+        rates[rank] = h2d_rank_gbs
+        dist.all_reduce(rates)
+        h2d_rank_gbs = [round(float(r), 2) for r in rates.tolist()]
     e2e_ms = max_over_ranks(e2e_ms)
     clocks = sampler.stop() if sampler is not None else None
     parity = None
@@ -962,7 +967,7 @@ def run_ours(args):
                     "unit": "Gelem/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "ms_per_step": e2e_ms / e2e_steps,
-                    "h2d_gbs_rank0": h2d_rank_gbs},
+                    "h2d_gbs_per_rank": h2d_rank_gbs},
             "gpu_launches": args.steps * launches,
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak,

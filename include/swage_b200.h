@@ -144,6 +144,15 @@ int swg_plan_status(swg_plan *plan);
  * counterpart (the reference's kernels have no device-side checks). */
 int swg_plan_peek_status(const swg_plan *plan);
 
+/* Self-test of the kernels' bounded waits: queues a one-warp kernel on `stream`
+ * that waits `limit_us` microseconds (1 .. 1e6) for a copy nobody issues and
+ * then reports the timeout through the plan's error words, exactly as a tile
+ * kernel whose copy never lands would after its two seconds.  Afterwards
+ * swg_plan_status returns SWG_ERR_DEVICE_TIMEOUT (and clears it) and
+ * swg_plan_peek_status reports it once.  Touches no caller memory; the context
+ * stays usable.  No reference counterpart. */
+int swg_plan_selftest_timeout(swg_plan *plan, int32_t limit_us, void *stream);
+
 /* The same rules, order and reason codes as swg_validate_offsets_i32, for
  * offsets[0 .. segment_count] that live on the GPU: one pass on the device, one
  * small read-back (`stream` is synchronised).  *hash (optional) receives a

@@ -45,7 +45,7 @@ EXPORTS = (
     "swg_profile_stop", "swg_segreduce_f32_noalloc",
     "swg_validate_offsets_device", "swg_plan_create_device",
     "swg_segreduce_sum_max_f32", "swg_plan_create_validated",
-    "swg_plan_peek_status", "swg_segreduce",
+    "swg_plan_peek_status", "swg_segreduce", "swg_plan_selftest_timeout",
 )
 
 _lock = threading.Lock()
@@ -109,6 +109,8 @@ def _declare(lib):
     lib.swg_plan_create_validated.restype = c_int
     lib.swg_plan_create_validated.argtypes = [
         ptr, c_i32, c_i32, c_int, ptr, ctypes.c_uint64, ctypes.POINTER(ptr)]
+    lib.swg_plan_selftest_timeout.restype = c_int
+    lib.swg_plan_selftest_timeout.argtypes = [ptr, c_i32, ptr]
     lib.swg_plan_peek_status.restype = c_int
     lib.swg_plan_peek_status.argtypes = [ptr]
     lib.swg_profile_start.restype = c_int
@@ -324,6 +326,13 @@ def plan_host_tasks(host_ptr, segment_count, op=OP_REDUCE):
 
 def plan_status(handle):
     check(library().swg_plan_status(handle), "swg_plan_status")
+
+
+def plan_selftest_timeout(handle, limit_us, stream):
+    """Queue a kernel whose bounded wait runs out after ``limit_us`` and
+    reports it through the plan's error words."""
+    check(library().swg_plan_selftest_timeout(handle, limit_us, stream),
+          "swg_plan_selftest_timeout")
 
 
 def plan_peek_status(handle):

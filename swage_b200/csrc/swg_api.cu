@@ -534,6 +534,27 @@ static int device_error(uint32_t code, uint32_t detail) {
   return code == 1 ? SWG_ERR_DEVICE_TIMEOUT : SWG_ERR_DEVICE_CHECK;
 }
 
+int swg_plan_selftest_timeout(swg_plan *plan, int32_t limit_us, void *stream) {
+  swg::clear_error();
+  if (!plan || limit_us < 1 || limit_us > 1000000) {
+    swg::set_error(
+        "swg_plan_selftest_timeout: needs a plan and a limit of 1 .. 1e6 us");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  int device = 0, sm_count = 0;
+  const int status = current_device(&device, &sm_count);
+  if (status != SWG_OK) return status;
+  if (plan->dev.device != device || plan->dev.control == nullptr) {
+    swg::set_error("swg_plan_selftest_timeout: plan of another device");
+    return SWG_ERR_PLAN_MISMATCH;
+  }
+  note_launch(plan, (cudaStream_t)stream);
+  const cudaError_t e = swg::launch_wait_selftest(
+      plan->dev, (uint64_t)limit_us * 1000ull, (cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_failure("wait self-test launch", e);
+  return SWG_OK;
+}
+
 int swg_plan_peek_status(const swg_plan *plan) {
   swg::clear_error();
   if (!plan) {

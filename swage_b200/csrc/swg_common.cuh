@@ -340,17 +340,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   return done != 0;
 }
 
-// Bounded wait; false = gave up after kWaitLimitNs.  The clock is only read
+// Bounded wait; false = gave up after `limit_ns`.  The clock is only read
 // once the first few probes have failed, so the common case costs one probe.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_for(uint64_t *bar, uint32_t parity,
+                                              uint64_t limit_ns) {
   for (int probe = 0; probe < 16; ++probe)
     if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t deadline = global_timer_ns() + kWaitLimitNs;
+  const uint64_t deadline = global_timer_ns() + limit_ns;
   for (;;) {
     for (int probe = 0; probe < 32; ++probe)
       if (mbar_try_wait(bar, parity)) return true;
     if (global_timer_ns() > deadline) return false;
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+  return mbar_wait_for(bar, parity, kWaitLimitNs);
 }
 
 // Orders this thread's earlier generic-proxy accesses to shared memory (and

@@ -97,6 +97,10 @@ cudaError_t launch_segreduce_typed(int kind, int dtype, const void *values,
                                    int32_t value_count, int32_t segment_count,
                                    bool cta, int sm_count, cudaStream_t stream,
                                    const Probe *probe);
+// Runs a wait that cannot succeed for `limit_ns`, so that the plan's error
+// words report a timeout (see swg_plan_selftest_timeout).
+cudaError_t launch_wait_selftest(const DevicePlan &plan, uint64_t limit_ns,
+                                 cudaStream_t stream);
 cudaError_t configure_segreduce_kernels();
 cudaError_t configure_softmax_kernels();
 

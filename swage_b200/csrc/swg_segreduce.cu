@@ -32,10 +32,19 @@ namespace swg {
 // ---------------------------------------------------------------------------
 // warp per segment
 // ---------------------------------------------------------------------------
-constexpr int kWarpKernelThreads = 256;
+#ifndef SWG_WARP_THREADS
+#define SWG_WARP_THREADS 256
+#endif
+#ifndef SWG_WARP_INFLIGHT
+#define SWG_WARP_INFLIGHT 8
+#endif
+#ifndef SWG_WARP_MINBLOCKS
+#define SWG_WARP_MINBLOCKS 4
+#endif
+constexpr int kWarpKernelThreads = SWG_WARP_THREADS;
 
 template <class Op>
-__global__ void __launch_bounds__(kWarpKernelThreads, 4)
+__global__ void __launch_bounds__(kWarpKernelThreads, SWG_WARP_MINBLOCKS)
 segreduce_warp_kernel(const float *__restrict__ values,
                       const int32_t *__restrict__ offsets,
                       float *__restrict__ out, int32_t segment_count) {
@@ -48,7 +57,7 @@ segreduce_warp_kernel(const float *__restrict__ values,
     const int64_t end = __ldg(offsets + seg + 1);
     // eight 128-bit loads per lane are issued before the first is used: a
     // segment of up to 1024 values is one round trip to memory
-    float acc = strided_partial<Op, 8>(values, begin, end, lane, kWarp);
+    float acc = strided_partial<Op, SWG_WARP_INFLIGHT>(values, begin, end, lane, kWarp);
     acc = warp_reduce<Op>(acc);
     if (lane == 0) out[seg] = acc;
   }
@@ -60,7 +69,7 @@ segreduce_warp_kernel(const float *__restrict__ values,
 // of the two single kernels (SegmentedReduction.cpp:156-161, 236-241,
 // 256-258).  kCta = false: one warp per segment; true: one CTA per segment.
 template <bool kCta>
-__global__ void __launch_bounds__(kWarpKernelThreads, 4)
+__global__ void __launch_bounds__(kWarpKernelThreads, SWG_WARP_MINBLOCKS)
 segreduce_sum_max_kernel(const float *__restrict__ values,
                          const int32_t *__restrict__ offsets,
                          float *__restrict__ out_sum,
@@ -71,8 +80,8 @@ segreduce_sum_max_kernel(const float *__restrict__ values,
     for (int64_t seg = blockIdx.x; seg < segment_count; seg += gridDim.x) {
       const int64_t begin = __ldg(offsets + seg);
       const int64_t end = __ldg(offsets + seg + 1);
-      const SumMax r = strided_sum_max<8>(values, begin, end, threadIdx.x,
-                                          kWarpKernelThreads);
+      const SumMax r = strided_sum_max<SWG_WARP_INFLIGHT>(
+          values, begin, end, threadIdx.x, kWarpKernelThreads);
       const float sum = cta_reduce<SumOp>(r.sum, scratch);
       const float max = cta_reduce<MaxOp>(r.max, scratch);
       if (threadIdx.x == 0) {
@@ -88,7 +97,8 @@ segreduce_sum_max_kernel(const float *__restrict__ values,
   for (int64_t seg = warp; seg < segment_count; seg += nwarps) {
     const int64_t begin = __ldg(offsets + seg);
     const int64_t end = __ldg(offsets + seg + 1);
-    const SumMax r = strided_sum_max<8>(values, begin, end, lane, kWarp);
+    const SumMax r =
+        strided_sum_max<SWG_WARP_INFLIGHT>(values, begin, end, lane, kWarp);
     const float sum = warp_reduce<SumOp>(r.sum);
     const float max = warp_reduce<MaxOp>(r.max);
     if (lane == 0) {
@@ -1280,6 +1290,33 @@ cudaError_t launch_segreduce_resident(int kind, int dtype, const void *values,
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;
   return launch_merge(kind, dtype, plan, out, value_count, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Self-test of the bounded wait: one warp arms an mbarrier for sixteen bytes
+// that no copy will ever deliver, waits for at most `limit_ns`, and -- the
+// wait having run out -- reports kErrTimeout through the plan's error words
+// exactly as the tile kernels do, then returns.  Touches no caller memory.
+// ---------------------------------------------------------------------------
+__global__ void wait_selftest_kernel(uint32_t *control,
+                                     unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  const int lane = threadIdx.x & 31;
+  if (lane == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  if (lane == 0) mbar_arrive_expect_tx(&bar, 16);
+  __syncwarp();
+  if (!mbar_wait_for(&bar, 0, limit_ns) && lane == 0)
+    report(control, kErrTimeout, 0xfeedu);
+}
+
+cudaError_t launch_wait_selftest(const DevicePlan &plan, uint64_t limit_ns,
+                                 cudaStream_t stream) {
+  wait_selftest_kernel<<<1, 32, 0, stream>>>(plan.control, limit_ns);
+  return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------

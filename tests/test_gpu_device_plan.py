@@ -291,6 +291,37 @@ def test_status_can_be_read_without_synchronising():
         plan.close()
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_plan_stays_usable():
+    """Every device-side wait is bounded.  The self-test kernel waits a
+    millisecond for a copy nobody issues, gives up and returns; the error
+    reaches the host both ways (without a CUDA call through ``peek``, with a
+    synchronisation through ``check``), the NEXT drop-in launch raises instead
+    of passing silently, and after that the plan works as before."""
+    offsets = workloads.c5_offsets(segments=1 << 14, total=1 << 22, giants=2,
+                                   giant_length=1 << 20)
+    host_values = np.random.default_rng(6).standard_normal(
+        int(offsets[-1])).astype(np.float32)
+    values = torch.as_tensor(host_values).cuda()
+    device_offsets = torch.as_tensor(offsets).cuda()
+    output = torch.empty(len(offsets) - 1, device="cuda")
+    plan = device_plan(offsets)
+    try:
+        stream = torch.cuda.current_stream().cuda_stream
+        _native.plan_selftest_timeout(plan.handle, 1000, stream)
+        torch.cuda.synchronize()
+        with pytest.raises(RuntimeError, match="SWG_ERR_DEVICE_TIMEOUT"):
+            launch_gpu(values, device_offsets, output, "sum", plan=plan)
+        with pytest.raises(RuntimeError, match="SWG_ERR_DEVICE_TIMEOUT"):
+            plan.check()
+        plan.check()  # reported and cleared
+        plan.peek()
+        check_reduce(host_values, offsets, "sum", "split", plan=plan)
+        check_reduce(host_values, offsets, "max", "persistent", plan=plan)
+        plan.check()
+    finally:
+        plan.close()
+
+
 def test_two_streams_over_the_same_offsets_get_a_plan_each():
     """Launches that share a plan share its merge scratch; the drop-in call
     therefore caches plans per stream.  Two streams reducing over the same CSR
