@@ -114,14 +114,12 @@ struct HostPlan {
 // Schedule choice from the length statistics (measured on B200):
 //  - small inputs whose segments are all of moderate length: one warp per
 //    segment streams straight from global memory, no staging;
-//  - most values in long segments (nearly every tile a chunk) and a very
-//    large input: tile tasks, a CTA per pair (split) -- the hardware CTA
-//    scheduler then keeps the most copies in flight (4 % ahead of resident on
-//    2^30 values);
+//  - most values in long segments (nearly every tile a chunk): tile tasks, a
+//    CTA per pair (split) -- the hardware CTA scheduler then keeps the most
+//    copies in flight (8 % ahead of resident on 2^30 values, 3 % on 2^27);
 //  - otherwise, large inputs: the same tile tasks on resident CTAs, which
-//    hide the time a warp spends reducing a tile of many segments, and whose
-//    start and end cost least (on a 2^27-value share of the same input the
-//    two are level, resident the steadier);
+//    hide the time a warp spends reducing a tile of many segments (10 %
+//    ahead of split on the lognormal and uniform mixes);
 //  - small skewed inputs: split.
 // The persistent (ticketed ring) schedule runs the same tasks and is
 // selectable, but is never the fastest.
@@ -129,10 +127,8 @@ inline int choose_schedule(const int64_t *elements_in_bin, int64_t value_count,
                            int64_t max_length, double mean_length) {
   int64_t in_long = 0;  // values in segments of at least 4096
   for (int bin = 13; bin < kHistogramBins; ++bin) in_long += elements_in_bin[bin];
-  if (2 * in_long >= value_count && value_count >= (int64_t(1) << 29))
-    return SWG_SCHED_SPLIT;
-  if (value_count >= (int64_t(1) << 24)) return SWG_SCHED_RESIDENT;
   if (2 * in_long >= value_count && value_count > 0) return SWG_SCHED_SPLIT;
+  if (value_count >= (int64_t(1) << 24)) return SWG_SCHED_RESIDENT;
   return max_length <= 4096 && mean_length >= 256.0 ? SWG_SCHED_WARP
                                                     : SWG_SCHED_SPLIT;
 }
