@@ -710,12 +710,75 @@ def measure(problem, steps, warmup, barrier, peak):
     return result
 
 
+def measure_mapped(problem, check):
+    """The same reduction with an element map fused in front of it (sum of
+    squares, sum of exponentials), same plan, same bytes: the dominant
+    kernel's rate, and -- with ``check`` -- the sum of squares against the
+    fp64 sum of the oracle's mapped elements at full size."""
+    import torch
+
+    from swage_b200._segmented_qualification import ElementMap, launch_gpu
+
+    if (problem.operation != "reduce" or problem.kind == "sum+max"
+            or problem.plan is None):
+        return None
+    result = {}
+    for label, element_map in (("square", ElementMap("square")),
+                               ("exp", ElementMap("exp", 0.5, -1.0))):
+        def step():
+            launch_gpu(problem.values, problem.device_offsets, problem.out,
+                       problem.kind, problem.args.block, plan=problem.plan,
+                       schedule=problem.args.schedule, extensions=True,
+                       map=element_map,
+                       _validated=(problem.count, problem.segments))
+        for _ in range(3):
+            step()
+        kernel_ms = float(np.mean(dominant_kernel_ms(step, 10)))
+        result[label] = {
+            "map": f"{element_map.fn}({element_map.scale:g} * x + "
+                   f"{element_map.shift:g})",
+            "kernel_ms": kernel_ms,
+            "kernel_gbs": problem.bytes_per_step / (kernel_ms * 1e-3) / 1e9,
+        }
+        if check and label == "square":
+            import oracle
+
+            torch.cuda.synchronize()
+            got = problem.out.cpu().numpy()[:problem.segments]
+            mapped = oracle.map_f32(problem.values.cpu().numpy(), "square")
+            offsets = problem.local_offsets
+            threads = oracle.host_threads()
+            if problem.kind == "sum":
+                exact = oracle.segsum_f64(mapped, offsets, threads=threads)
+                bound = (oracle.sum_tolerance(mapped, offsets)
+                         + 1e-6 * np.abs(exact))
+                live = bound > 0
+                worst = float(np.max(np.abs(got - exact)[live] / bound[live],
+                                     initial=0.0))
+                same = bool(np.all(np.abs(got - exact) <= bound))
+                verdict = (f"sum of squares within {worst:.3f} x (1e-5 * "
+                           "sqrt(len) * max + 1e-6 * sum) of fp64")
+            else:
+                expected = oracle.segreduce_f32(mapped, offsets, problem.kind,
+                                                threads=threads)
+                same = bool(np.array_equal(got.view(np.uint32),
+                                           expected.view(np.uint32)))
+                verdict = f"{problem.kind} of squares bit-exact"
+            result[label]["parity"] = verdict if same else "MISMATCH"
+            del mapped
+    problem.plan.check()
+    return result
+
+
 def measure_cold(problem, barrier):
     """The drop-in call on offsets no cache has seen: validation, planning
-    and launch, inputs resident on the device.  Eight different offsets
+    and launch, inputs resident on the device.  Fourteen different offsets
     arrays (one boundary moved by one each), wall clock around call + stream
-    synchronisation; ``ms`` is the median, ``all_ms`` every call in order (the
-    first ones also grow the library's memory pool to its working size)."""
+    synchronisation.  The first six calls are this measurement's warm-up and
+    are reported apart (``first_calls_ms``): a process's first plans also grow
+    the library's memory pool until it holds the plan cache's working set, a
+    cost per process, not per call.  ``ms`` is the median of the other eight,
+    ``all_ms`` those eight in order."""
     import torch
 
     if problem.operation == "vadd" or problem.kind == "sum+max":
@@ -725,8 +788,11 @@ def measure_cold(problem, barrier):
     movable = np.nonzero(offsets[1:-1] > offsets[:-2])[0] + 1
     if movable.size < 3:
         return None
+    warm_up, timed = 6, 8
+    calls = warm_up + timed
     times = []
-    picks = [movable[(2 * i + 1) * movable.size // 16] for i in range(8)]
+    picks = [movable[(2 * i + 1) * movable.size // (2 * calls)]
+             for i in range(calls)]
     for pick in picks:
         changed = offsets.copy()
         changed[pick] -= 1
@@ -737,10 +803,12 @@ def measure_cold(problem, barrier):
         torch.cuda.current_stream().synchronize()
         times.append(1e3 * (time.perf_counter() - began))
     problem.device_offsets = keep
-    return {"ms": float(np.median(times)), "all_ms": times,
+    return {"ms": float(np.median(times[warm_up:])),
+            "all_ms": times[warm_up:], "first_calls_ms": times[:warm_up],
             "what": "validate + plan + launch through the drop-in call on "
                     "offsets not seen before, device-resident inputs, wall "
-                    "clock to stream completion"}
+                    "clock to stream completion; the first six calls (also "
+                    "growing the memory pool) reported apart"}
 
 
 def bind_to_gpu_cores(local_rank):
@@ -867,6 +935,9 @@ def run_ours(args):
     if problem.plan is not None:
         problem.plan.check()
     cold = measure_cold(problem, barrier)
+    mapped = None
+    if world == 1 and args.shrink == 1:
+        mapped = measure_mapped(problem, check=not args.no_parity)
     e2e_steps = args.e2e_steps or max(1, min(args.steps, 5))
     binding = bind_to_gpu_cores(local_rank) if world > 1 else "single rank"
     e2e_ms, h2d, d2h, host_sources = measure_e2e(problem, e2e_steps, barrier)
@@ -1011,6 +1082,7 @@ def run_ours(args):
                 "pct_of_8tbs": 100.0 * achieved / NOMINAL_HBM_GBS,
             },
             "cold": cold,
+            "mapped": mapped,
             "parity": parity,
             "cpu_baseline": cpu,
             "plan": summary["plan_info"] or None,

@@ -61,6 +61,25 @@ typedef enum swg_status {
 #define SWG_DTYPE_BF16 2
 #define SWG_DTYPE_I32 3
 
+/* Element maps in front of a reduction: the dialect's swage.map region feeding
+ * a swage.reduce (test/Dialect/Swage/roundtrip.mlir:43-52; the composition of
+ * test/Dialect/Swage/softmax.mlir:17-24), which the reference's lowering
+ * rejects -- it accepts the identity region only
+ * (SegmentedReduction.cpp:106-119).  A map is fn(scale * x + shift) with
+ * `scale` and `shift` captured at launch time; the product and the sum are
+ * rounded separately (arith.mulf then arith.addf, no contraction).  scale 1
+ * and shift -0.0 leave every value, signed zeros included, as it is (+0.0
+ * would turn a -0.0 into +0.0). */
+#define SWG_MAP_IDENTITY 0 /* y            */
+#define SWG_MAP_ABS 1      /* |y|          */
+#define SWG_MAP_SQUARE 2   /* y * y        */
+#define SWG_MAP_EXP 3      /* exp(y): one multiply and ex2.approx, relative error ~2^-22 */
+typedef struct swg_map {
+  int32_t fn; /* SWG_MAP_*; y = scale * x + shift */
+  float scale;
+  float shift;
+} swg_map;
+
 /* Operation a plan is built for. */
 #define SWG_OP_REDUCE 0
 #define SWG_OP_SOFTMAX 1
@@ -240,6 +259,21 @@ int swg_segreduce(int kind, int dtype, const void *values,
                   const int32_t *offsets, void *out, int32_t value_count,
                   int32_t segment_count, const swg_plan *plan, int schedule,
                   int32_t block_hint, void *stream);
+
+/* Map fused into the reduction: out[s] = reduce over the segment of
+ * map->fn(map->scale * x + map->shift), each value read once and never
+ * written back (a sum of squares, an L1 norm, a max of |x|, the sum of
+ * exponentials of a log-sum-exp, ...).  `dtype` is SWG_DTYPE_F32, F16 or BF16
+ * (the map acts on the value widened to fp32; results are fp32); integer
+ * segments are not mapped.  Same plans and schedules as swg_segreduce; WARP
+ * and CTA run the generic warp / CTA-per-segment kernel, PERSISTENT falls
+ * back to SPLIT.  An empty segment gives the identity of `kind`, not the map
+ * of it.  No reference counterpart (see SWG_MAP_* above). */
+int swg_segreduce_map(int kind, int dtype, const swg_map *map,
+                      const void *values, const int32_t *offsets, float *out,
+                      int32_t value_count, int32_t segment_count,
+                      const swg_plan *plan, int schedule, int32_t block_hint,
+                      void *stream);
 
 /* Sum AND max of every segment in one pass over the values:
  * out_sum[s] = swg_segreduce_f32(SWG_KIND_SUM)[s] to the documented tolerance,

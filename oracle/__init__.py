@@ -68,6 +68,8 @@ def _load():
         ctypes.c_int, f32p, i32p, f32p, i64, ctypes.c_int]
     lib.swg_oracle_segreduce_i32.argtypes = [ctypes.c_int, i32p, i32p, i32p,
                                              i64]
+    lib.swg_oracle_map_f32.argtypes = [ctypes.c_int, ctypes.c_float,
+                                       ctypes.c_float, f32p, f32p, i64]
     lib.swg_oracle_segsum_f64.argtypes = [f32p, i32p, f64p, i64, ctypes.c_int]
     lib.swg_oracle_segabsmax_f64.argtypes = [
         f32p, i32p, f64p, i64, ctypes.c_int]
@@ -79,7 +81,7 @@ def _load():
                                         ctypes.c_int]
     for name in (
         "swg_oracle_segreduce_f32", "swg_oracle_segreduce_i32",
-        "swg_oracle_segsum_f64",
+        "swg_oracle_segsum_f64", "swg_oracle_map_f32",
         "swg_oracle_segabsmax_f64", "swg_oracle_segsoftmax_f64",
         "swg_oracle_segsoftmax_f32", "swg_oracle_vadd_f32",
         "swg_oracle_max_threads",
@@ -154,6 +156,23 @@ def segreduce_i32(values, offsets, kind):
         out.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), out.size)
     if used < 0:
         raise ValueError("reduction kind must be 'sum', 'max' or 'min'")
+    return out
+
+
+_MAPS = {"identity": 0, "abs": 1, "square": 2, "exp": 3}
+
+
+def map_f32(values, fn="identity", scale=1.0, shift=0.0):
+    """``fn(scale * x + shift)`` element by element in fp32 (product and sum
+    rounded separately; ``exp`` evaluated in double, rounded once): what an
+    element map in front of a reduction feeds it."""
+    values, vp = _f32(values)
+    out = np.empty(values.size, dtype=np.float32)
+    used = _load().swg_oracle_map_f32(
+        _MAPS[fn], float(scale), float(shift), vp,
+        out.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), values.size)
+    if used < 0:
+        raise ValueError("unknown map function")
     return out
 
 

@@ -135,6 +135,28 @@ int swg_oracle_segreduce_i32(int kind, const int32_t *values,
   return 1;
 }
 
+/* Element map in front of a reduction: out[i] = fn(scale * x[i] + shift) in
+ * fp32, product and sum rounded separately (arith.mulf, arith.addf; this file
+ * is built with -ffp-contract=off), fn = 0 identity, 1 |y|, 2 y * y,
+ * 3 exp(y) evaluated in double and rounded once.  The form of a swage.map
+ * region (test/Dialect/Swage/roundtrip.mlir:43-52, softmax.mlir:17-24).
+ * Unpinned: the reference lowers no map in front of a reduce
+ * (SegmentedReduction.cpp:106-119), so it holds no result for one.  The
+ * mapped values are then reduced by the pinned functions of this file. */
+int swg_oracle_map_f32(int fn, float scale, float shift, const float *values,
+                       float *out, int64_t count) {
+  if (fn < 0 || fn > 3) return -1;
+  for (int64_t i = 0; i < count; ++i) {
+    const float product = values[i] * scale;
+    float y = product + shift;
+    if (fn == 1) y = fabsf(y);
+    if (fn == 2) y = y * y;
+    if (fn == 3) y = (float)exp((double)y);
+    out[i] = y;
+  }
+  return 1;
+}
+
 /* fp64 accumulation of the same sum: the quantity the fp32 tolerance
  * |err| <= 1e-5 * sqrt(len) * max|x| is stated against. */
 int swg_oracle_segsum_f64(const float *values, const int32_t *offsets,

@@ -36,11 +36,28 @@ class _Program(NamedTuple):
     ``kind`` is one of ``vector_add``, ``segmented_sum``, ``segmented_max``,
     ``segmented_min`` or ``segmented_softmax``; ``roles`` maps the role of each
     runtime parameter (``x``, ``y``, ``out``, ``n`` or ``values``, ``offsets``,
-    ``out``) to its name in the kernel signature.
+    ``out``) to its name in the kernel signature.  ``map`` is set for a
+    segmented reduction of mapped elements: ``(fn, scale, shift)`` with ``fn``
+    one of ``identity``, ``abs``, ``square``, ``exp`` and the two constants as
+    terms over literals and constexpr parameters (see ``constant_value``).
     """
 
     kind: str
     roles: dict
+    map: tuple = None
+
+
+def constant_value(term, constexprs):
+    """Evaluate a constant term of a recognised map with the launch's
+    constexpr values."""
+    tag = term[0]
+    if tag in ("int", "num"):
+        return float(term[1])
+    if tag == "static":
+        return float(constexprs[term[1]])
+    if tag == "neg":
+        return -constant_value(term[1], constexprs)
+    raise ValueError(f"not a constant term: {term!r}")
 
 
 def _is_constexpr_annotation(node):
@@ -338,13 +355,14 @@ class _Kernel:
 #   ("add", a, b) | ("mul", a, b) | ("sub", a, b) | ("div", a, b) | ("lt", a, b)
 #   ("load", address, mask) | ("sid",) | ("segment", values, offsets, index)
 #   ("elements", segment) | ("max", x) | ("min", x) | ("sum", x) | ("exp", x)
+#   ("abs", x) | ("neg", x) | ("num", v)
 # and a list of effects ("store", address, value, mask) or
 # ("store_segment", pointer, segment, value).  Matching is then plain tuple
 # comparison against the canonical forms below.
 
 _SEGMENT_CALLS = {
     "segment_id", "segment", "load_segment", "store_segment", "max", "min",
-    "sum", "exp",
+    "sum", "exp", "abs",
 }
 
 
@@ -417,6 +435,10 @@ class _Recognizer:
             self.fail(node, f"unknown name '{node.id}'")
         if isinstance(node, ast.Constant) and type(node.value) is int:
             return ("int", node.value)
+        if isinstance(node, ast.Constant) and type(node.value) is float:
+            return ("num", node.value)
+        if isinstance(node, ast.UnaryOp) and isinstance(node.op, ast.USub):
+            return ("neg", self.term(node.operand))
         if isinstance(node, ast.BinOp):
             operators = {ast.Add: "add", ast.Mult: "mul", ast.Sub: "sub",
                          ast.Div: "div"}
@@ -566,15 +588,26 @@ class _Recognizer:
         )
 
     def _segmented(self, effect):
-        if len(self.runtime) != 3 or self.static:
+        if len(self.runtime) != 3:
             return None
         values, offsets, out = (("param", name) for name in self.runtime)
         segment = ("segment", values, offsets, ("sid",))
         x = ("elements", segment)
         roles = dict(zip(("values", "offsets", "out"), self.runtime))
         for kind in ("sum", "max", "min"):
-            if effect == ("store", ("add", out, ("sid",)), (kind, x), None):
+            if effect[:2] != ("store", ("add", out, ("sid",))):
+                break
+            reduced = effect[2]
+            if effect[3] is not None or reduced[0] != kind or (
+                    len(reduced) != 2):
+                continue
+            if reduced[1] == x and not self.static:
                 return _Program(f"segmented_{kind}", roles)
+            element_map = _match_map(reduced[1], x)
+            if element_map is not None and element_map[0] is not None:
+                return _Program(f"segmented_{kind}", roles, element_map)
+        if self.static:
+            return None
         # softmax in the reference's semantic form
         # (test/Dialect/Swage/softmax.mlir:13-31): max, sum of exp(x - max),
         # exp(x - max) / sum, stored over the segment's own range.
@@ -586,6 +619,70 @@ class _Recognizer:
         if effect == wanted:
             return _Program("segmented_softmax", roles)
         return None
+
+
+def _is_constant(term):
+    """A literal, a constexpr parameter, or the negation of one."""
+    if not isinstance(term, tuple):
+        return False
+    if term[0] in ("int", "num", "static"):
+        return True
+    return term[0] == "neg" and _is_constant(term[1])
+
+
+def _match_affine(term, x):
+    """``(scale, shift)`` as constant terms when ``term`` is one of the exact
+    affine forms of ``x`` -- ``x``, ``-x``, ``x * c``, ``c * x``, each
+    optionally ``+ d``, ``d +`` or ``- d`` -- else ``None``.  Only forms whose
+    fp32 evaluation IS one multiply and one add are taken: nothing is
+    reassociated (``(x - c) * d`` is not ``x * d - c * d`` in fp32), so the
+    kernel's arithmetic is the expression's.  A missing shift is ``-0.0``,
+    which leaves every value, signed zeros included, as it is."""
+    one, no_shift = ("num", 1.0), ("num", -0.0)
+
+    def scaled(t):
+        if t == x:
+            return one
+        if t == ("neg", x):
+            return ("num", -1.0)
+        if t[0] == "mul" and t[1] == x and _is_constant(t[2]):
+            return t[2]
+        if t[0] == "mul" and t[2] == x and _is_constant(t[1]):
+            return t[1]
+        return None
+
+    if not isinstance(term, tuple):
+        return None
+    scale = scaled(term)
+    if scale is not None:
+        return scale, no_shift
+    if term[0] == "add":
+        for product, constant in ((term[1], term[2]), (term[2], term[1])):
+            scale = scaled(product) if isinstance(product, tuple) else None
+            if scale is not None and _is_constant(constant):
+                return scale, constant
+    if term[0] == "sub" and isinstance(term[1], tuple):
+        scale = scaled(term[1])
+        if scale is not None and _is_constant(term[2]):
+            return scale, ("neg", term[2])
+    return None
+
+
+def _match_map(term, x):
+    """``(fn, scale, shift)`` when ``term`` is ``A``, ``sl.abs(A)``,
+    ``sl.exp(A)`` or ``A * A`` with ``A`` an affine form of the segment's
+    elements ``x`` (see ``_match_affine``); ``None`` otherwise."""
+    if not isinstance(term, tuple):
+        return None
+    function, inner = "identity", term
+    if term[0] in ("abs", "exp") and len(term) == 2:
+        function, inner = term[0], term[1]
+    elif term[0] == "mul" and term[1] == term[2] and not _is_constant(term[1]):
+        function, inner = "square", term[1]
+    affine = _match_affine(inner, x)
+    if affine is None:
+        return None
+    return (function,) + affine
 
 
 def _call_name(node):

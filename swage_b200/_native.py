@@ -20,6 +20,17 @@ LIBRARY_PATH = pathlib.Path(__file__).resolve().parent / "libswage_b200.so"
 # mirrors of the header's constants
 KIND_SUM, KIND_MAX, KIND_MIN = 0, 1, 2
 DTYPE_F32, DTYPE_F16, DTYPE_BF16, DTYPE_I32 = range(4)
+MAP_IDENTITY, MAP_ABS, MAP_SQUARE, MAP_EXP = range(4)
+MAPS = {"identity": MAP_IDENTITY, "abs": MAP_ABS, "square": MAP_SQUARE,
+        "exp": MAP_EXP}
+
+
+class Map(ctypes.Structure):
+    """``swg_map``: ``fn(scale * x + shift)`` applied before the reduction."""
+
+    _fields_ = [("fn", ctypes.c_int32), ("scale", ctypes.c_float),
+                ("shift", ctypes.c_float)]
+
 OP_REDUCE, OP_SOFTMAX = 0, 1
 (SCHED_AUTO, SCHED_WARP, SCHED_CTA, SCHED_SPLIT, SCHED_PERSISTENT,
  SCHED_RESIDENT) = range(6)
@@ -46,6 +57,7 @@ EXPORTS = (
     "swg_validate_offsets_device", "swg_plan_create_device",
     "swg_segreduce_sum_max_f32", "swg_plan_create_validated",
     "swg_plan_peek_status", "swg_segreduce", "swg_plan_selftest_timeout",
+    "swg_segreduce_map",
 )
 
 _lock = threading.Lock()
@@ -86,6 +98,10 @@ def _declare(lib):
     lib.swg_segreduce.restype = c_int
     lib.swg_segreduce.argtypes = [
         c_int, c_int, ptr, ptr, ptr, c_i32, c_i32, ptr, c_int, c_i32, ptr]
+    lib.swg_segreduce_map.restype = c_int
+    lib.swg_segreduce_map.argtypes = [
+        c_int, c_int, ctypes.POINTER(Map), ptr, ptr, ptr, c_i32, c_i32, ptr,
+        c_int, c_i32, ptr]
     lib.swg_segsoftmax_f32.restype = c_int
     lib.swg_segsoftmax_f32.argtypes = [
         ptr, ptr, ptr, c_i32, c_i32, ptr, c_int, ptr]
@@ -168,6 +184,21 @@ def segreduce_typed(kind, dtype, values_ptr, offsets_ptr, out_ptr, value_count,
             kind, dtype, values_ptr, offsets_ptr, out_ptr, value_count,
             segment_count, plan_handle, schedule, block, stream),
         "swg_segreduce",
+    )
+
+
+def segreduce_map(kind, dtype, fn, scale, shift, values_ptr, offsets_ptr,
+                  out_ptr, value_count, segment_count, plan_handle, schedule,
+                  block, stream):
+    """Reduce ``fn(scale * x + shift)`` over every segment (``fn``: ``MAP_*``,
+    ``dtype`` a floating ``DTYPE_*``; fp32 results)."""
+    element_map = Map(fn, scale, shift)
+    check(
+        library().swg_segreduce_map(
+            kind, dtype, ctypes.byref(element_map), values_ptr, offsets_ptr,
+            out_ptr, value_count, segment_count, plan_handle, schedule, block,
+            stream),
+        "swg_segreduce_map",
     )
 
 

@@ -169,11 +169,17 @@ def _pointer_descriptor(declared):
 # ---------------------------------------------------------------------------
 
 def _looks_segmented(kernel):
-    """Three runtime parameters and no constexpr: the segment-kernel shape."""
+    """Three unannotated runtime parameters, then constexpr parameters only
+    (the constants a mapped reduction captures): the segment-kernel shape."""
     arguments = kernel.function.args.args
-    if len(arguments) != 3:
+    if len(arguments) < 3:
         return False
-    return all(argument.annotation is None for argument in arguments)
+    if any(argument.annotation is not None for argument in arguments[:3]):
+        return False
+    from ._frontend import _is_constexpr_annotation
+
+    return all(_is_constexpr_annotation(argument.annotation)
+               for argument in arguments[3:])
 
 
 def _launch_segmented(kernel, arguments, constexprs, grid, torch):
@@ -181,8 +187,16 @@ def _launch_segmented(kernel, arguments, constexprs, grid, torch):
         raise TypeError("arguments must be a mapping")
     if not isinstance(constexprs, Mapping):
         raise TypeError("constexprs must be a mapping")
-    if len(constexprs) != 0:
+    static_names = {a.arg for a in kernel.function.args.args[3:]}
+    if not static_names and len(constexprs) != 0:
         raise ValueError("segment kernels take no constexprs")
+    if set(constexprs) != static_names:
+        raise ValueError(
+            "constexprs must contain exactly the kernel's constexpr parameters"
+        )
+    for name, value in constexprs.items():
+        if type(value) not in (int, float):
+            raise TypeError(f"constexpr '{name}' must be an int or a float")
     grid_ok = (
         isinstance(grid, tuple) and len(grid) == 1 and type(grid[0]) is int
     )
@@ -212,7 +226,16 @@ def _launch_segmented(kernel, arguments, constexprs, grid, torch):
         return runner.launch_softmax_gpu(
             values, offsets, output, _validated=(value_count, segment_count)
         )
+    element_map = None
+    if program.map is not None:
+        from ._frontend import constant_value
+
+        function, scale, shift = program.map
+        element_map = runner.ElementMap(
+            function, constant_value(scale, constexprs),
+            constant_value(shift, constexprs))
     return runner.launch_gpu(
         values, offsets, output, program.kind[len("segmented_"):],
-        extensions=True, _validated=(value_count, segment_count),
+        extensions=True, map=element_map,
+        _validated=(value_count, segment_count),
     )

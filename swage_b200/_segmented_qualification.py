@@ -29,6 +29,7 @@ import json
 import os
 import sys
 import threading
+from typing import NamedTuple
 
 from . import _runtime
 
@@ -533,8 +534,22 @@ def _check_block(block_size, torch):
         )
 
 
+class ElementMap(NamedTuple):
+    """``fn(scale * x + shift)`` applied to every value before it is reduced:
+    the dialect's ``swage.map`` region in front of a ``swage.reduce``
+    (``test/Dialect/Swage/roundtrip.mlir:43-52``).  ``fn`` is ``"identity"``,
+    ``"abs"``, ``"square"`` or ``"exp"``; ``scale`` and ``shift`` are values
+    captured at launch.  The product and the sum are rounded separately; the
+    default shift is ``-0.0``, the one addend that leaves every value, signed
+    zeros included, as it is."""
+
+    fn: str = "identity"
+    scale: float = 1.0
+    shift: float = -0.0
+
+
 def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
-               schedule="auto", extensions=False, _validated=None):
+               schedule="auto", extensions=False, map=None, _validated=None):
     """Queue one segmented ``sum`` or ``max`` on the current PyTorch stream.
 
     ``output[s] = reduce(values[offsets[s]:offsets[s + 1]])`` for every
@@ -552,8 +567,12 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
     ``output`` fp32) or ``int32`` (wrap-around sum, signed max / min,
     ``output`` int32): element types the dialect admits
     (``SwageOps.td:101-105``) and the lowering rejects
-    (``SegmentedReduction.cpp:110-119``).  Without it the reference's errors
-    are kept.
+    (``SegmentedReduction.cpp:110-119``).  ``map`` (an ``ElementMap``,
+    extensions only, floating values only) is applied to every value before it
+    is reduced, in the same pass: a non-identity map region in front of the
+    reduce, which the reference's lowering rejects
+    (``SegmentedReduction.cpp:106-119``).  Without ``extensions`` the
+    reference's errors are kept.
     """
     torch = _runtime._import_torch()
     if _validated is None:
@@ -569,6 +588,16 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
     else:
         raise ValueError("reduction kind must be 'sum' or 'max'")
     code = _schedule_code(schedule)
+    if map is not None:
+        if not extensions:
+            raise ValueError("an element map needs extensions=True")
+        if not isinstance(map, ElementMap):
+            raise TypeError("map must be an ElementMap")
+        if map.fn not in ("identity", "abs", "square", "exp"):
+            raise ValueError(
+                "map function must be 'identity', 'abs', 'square' or 'exp'")
+        if values.dtype == torch.int32:
+            raise TypeError("integer segments are not mapped")
     if segment_count == 0:
         return None
 
@@ -587,7 +616,18 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
     if plan is not None:
         _peek(plan)
     stream = torch.cuda.current_stream()
-    if values.dtype == torch.float32:
+    if map is not None:
+        dtype = {torch.float32: _native.DTYPE_F32,
+                 torch.float16: _native.DTYPE_F16,
+                 torch.bfloat16: _native.DTYPE_BF16}[values.dtype]
+        _native.segreduce_map(
+            kind_code, dtype, _native.MAPS[map.fn], float(map.scale),
+            float(map.shift), values.data_ptr(), offsets.data_ptr(),
+            output.data_ptr(), value_count, segment_count,
+            plan.handle if plan is not None else None,
+            code, block_size, stream.cuda_stream,
+        )
+    elif values.dtype == torch.float32:
         _native.segreduce(
             kind_code, values.data_ptr(), offsets.data_ptr(),
             output.data_ptr(), value_count, segment_count,

@@ -603,8 +603,19 @@ int swg_plan_status(swg_plan *plan) {
 static int segreduce(const char *who, int kind, int dtype, const void *values,
                      const int32_t *offsets, void *out, int32_t value_count,
                      int32_t segment_count, const swg_plan *plan, int schedule,
-                     int32_t block_hint, void *stream) {
+                     int32_t block_hint, void *stream,
+                     const swg_map *map = nullptr) {
   swg::clear_error();
+  if (map) {
+    if (map->fn < SWG_MAP_IDENTITY || map->fn > SWG_MAP_EXP) {
+      swg::set_error("%s: map function must be one of SWG_MAP_*", who);
+      return SWG_ERR_INVALID_ARGUMENT;
+    }
+    if (dtype == SWG_DTYPE_I32) {
+      swg::set_error("%s: integer segments are not mapped", who);
+      return SWG_ERR_UNSUPPORTED;
+    }
+  }
   if (kind != SWG_KIND_SUM && kind != SWG_KIND_MAX && kind != SWG_KIND_MIN) {
     swg::set_error(
         "reduction kind must be SWG_KIND_SUM, SWG_KIND_MAX or SWG_KIND_MIN");
@@ -644,6 +655,7 @@ static int segreduce(const char *who, int kind, int dtype, const void *values,
     if (dtype != SWG_DTYPE_F32 &&
         (schedule == SWG_SCHED_WARP || schedule == SWG_SCHED_PERSISTENT))
       schedule = SWG_SCHED_SPLIT;
+    if (map && schedule == SWG_SCHED_PERSISTENT) schedule = SWG_SCHED_SPLIT;
   } else {
     if (schedule == SWG_SCHED_SPLIT || schedule == SWG_SCHED_PERSISTENT ||
         schedule == SWG_SCHED_RESIDENT) {
@@ -664,11 +676,11 @@ static int segreduce(const char *who, int kind, int dtype, const void *values,
   switch (schedule) {
     case SWG_SCHED_WARP:
     case SWG_SCHED_CTA:
-      if (!f32)
+      if (!f32 || map)
         e = swg::launch_segreduce_typed(kind, dtype, values, offsets, out,
                                         value_count, segment_count,
                                         schedule == SWG_SCHED_CTA, sm_count, s,
-                                        probe);
+                                        probe, map);
       else if (schedule == SWG_SCHED_WARP)
         e = swg::launch_segreduce_warp(kind, (const float *)values, offsets,
                                        (float *)out, segment_count, sm_count,
@@ -680,11 +692,11 @@ static int segreduce(const char *who, int kind, int dtype, const void *values,
       break;
     case SWG_SCHED_SPLIT:
       e = swg::launch_segreduce_split(kind, dtype, values, out, value_count,
-                                      plan->dev, s, probe);
+                                      plan->dev, s, probe, map);
       break;
     case SWG_SCHED_RESIDENT:
       e = swg::launch_segreduce_resident(kind, dtype, values, out, value_count,
-                                         plan->dev, s, probe);
+                                         plan->dev, s, probe, map);
       break;
     default:
       e = swg::launch_segreduce_persistent(kind, (const float *)values,
@@ -712,6 +724,21 @@ int swg_segreduce(int kind, int dtype, const void *values,
   return segreduce("swg_segreduce", kind, dtype, values, offsets, out,
                    value_count, segment_count, plan, schedule, block_hint,
                    stream);
+}
+
+int swg_segreduce_map(int kind, int dtype, const swg_map *map,
+                      const void *values, const int32_t *offsets, float *out,
+                      int32_t value_count, int32_t segment_count,
+                      const swg_plan *plan, int schedule, int32_t block_hint,
+                      void *stream) {
+  if (!map) {
+    swg::clear_error();
+    swg::set_error("swg_segreduce_map: null map");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  return segreduce("swg_segreduce_map", kind, dtype, values, offsets, out,
+                   value_count, segment_count, plan, schedule, block_hint,
+                   stream, map);
 }
 
 int swg_segreduce_sum_max_f32(const float *values, const int32_t *offsets,

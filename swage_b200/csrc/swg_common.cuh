@@ -111,6 +111,76 @@ struct Elem<__nv_bfloat16> {
   }
 };
 
+// ---------------------------------------------------------------------------
+// Element maps: what is applied to a value (already widened to its
+// accumulator type) before it enters the reduction -- the dialect's swage.map
+// region in front of a swage.reduce (test/Dialect/Swage/roundtrip.mlir:43-52,
+// softmax.mlir:17-24), which the reference's lowering rejects
+// (SegmentedReduction.cpp:106-119).  NoMap is the identity region every
+// reference kernel has and costs nothing.  ScalarMap is fn(scale * x + shift)
+// with scale and shift captured at launch; the product and the sum are
+// rounded separately (arith.mulf, arith.addf), the exponential is one
+// multiply and one ex2.approx like the softmax kernels'.
+// ---------------------------------------------------------------------------
+struct NoMap {
+  template <class A>
+  __device__ __forceinline__ A operator()(A v) const {
+    return v;
+  }
+};
+
+struct ScalarMap {
+  int32_t fn;  // SWG_MAP_*
+  float scale, shift;
+};
+
+// ScalarMap with the function fixed at compile time: what the kernels' inner
+// loops are instantiated for (see with_fixed_map), so that no loop carries a
+// test of `fn`.
+template <int kFn>
+struct FixedMap {
+  float scale, shift;
+  __device__ __forceinline__ float operator()(float x) const {
+    float y = __fadd_rn(__fmul_rn(x, scale), shift);
+    if constexpr (kFn == SWG_MAP_ABS) {
+      y = fabsf(y);
+    } else if constexpr (kFn == SWG_MAP_SQUARE) {
+      y = __fmul_rn(y, y);
+    } else if constexpr (kFn == SWG_MAP_EXP) {
+      float r;
+      asm("ex2.approx.ftz.f32 %0, %1;"
+          : "=f"(r)
+          : "f"(__fmul_rn(y, 1.4426950408889634f)));
+      y = r;
+    }
+    return y;
+  }
+};
+
+// Calls f with the map to apply: NoMap as it is, a ScalarMap as the FixedMap
+// of its function (one warp-uniform switch per call).
+template <class F>
+__device__ __forceinline__ void with_fixed_map(const NoMap &map, F &&f) {
+  f(map);
+}
+template <class F>
+__device__ __forceinline__ void with_fixed_map(const ScalarMap &map, F &&f) {
+  switch (map.fn) {
+    case SWG_MAP_ABS:
+      f(FixedMap<SWG_MAP_ABS>{map.scale, map.shift});
+      break;
+    case SWG_MAP_SQUARE:
+      f(FixedMap<SWG_MAP_SQUARE>{map.scale, map.shift});
+      break;
+    case SWG_MAP_EXP:
+      f(FixedMap<SWG_MAP_EXP>{map.scale, map.shift});
+      break;
+    default:
+      f(FixedMap<SWG_MAP_IDENTITY>{map.scale, map.shift});
+      break;
+  }
+}
+
 template <class Op>
 __device__ __forceinline__ float fold4(float acc, float4 q) {
   return Op::apply(Op::apply(acc, Op::apply(q.x, q.y)), Op::apply(q.z, q.w));
@@ -118,22 +188,23 @@ __device__ __forceinline__ float fold4(float acc, float4 q) {
 
 // One 16-byte line of elements of type T folded into acc: four 32-bit
 // elements as fold4 does, or eight 16-bit ones as two such groups.
-template <class Op, class T>
+template <class Op, class T, class M = NoMap>
 __device__ __forceinline__ typename Op::Acc fold_line(typename Op::Acc acc,
-                                                      uint4 raw) {
+                                                      uint4 raw,
+                                                      const M &map = M{}) {
   using A = typename Op::Acc;
   if constexpr (sizeof(T) == 4) {
     T v[4];
     memcpy(v, &raw, 16);
-    const A x = Elem<T>::get(v[0]), y = Elem<T>::get(v[1]),
-            z = Elem<T>::get(v[2]), w = Elem<T>::get(v[3]);
+    const A x = map(Elem<T>::get(v[0])), y = map(Elem<T>::get(v[1])),
+            z = map(Elem<T>::get(v[2])), w = map(Elem<T>::get(v[3]));
     return Op::apply(Op::apply(acc, Op::apply(x, y)), Op::apply(z, w));
   } else {
     T v[8];
     memcpy(v, &raw, 16);
     A e[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) e[i] = Elem<T>::get(v[i]);
+    for (int i = 0; i < 8; ++i) e[i] = map(Elem<T>::get(v[i]));
     const A lo = Op::apply(Op::apply(e[0], e[1]), Op::apply(e[2], e[3]));
     const A hi = Op::apply(Op::apply(e[4], e[5]), Op::apply(e[6], e[7]));
     return Op::apply(Op::apply(acc, lo), hi);

@@ -78,7 +78,8 @@ cudaError_t launch_segreduce_sum_max(const float *values,
 cudaError_t launch_segreduce_split(int kind, int dtype, const void *values,
                                    void *out, int32_t value_count,
                                    const DevicePlan &plan, cudaStream_t stream,
-                                   const Probe *probe);
+                                   const Probe *probe,
+                                   const swg_map *map = nullptr);
 // Persistent CTAs, bulk-copy ring, ticket counter + merge pass.
 cudaError_t launch_segreduce_persistent(int kind, const float *values,
                                         float *out, int32_t value_count,
@@ -90,13 +91,17 @@ cudaError_t launch_segreduce_persistent(int kind, const float *values,
 cudaError_t launch_segreduce_resident(int kind, int dtype, const void *values,
                                       void *out, int32_t value_count,
                                       const DevicePlan &plan,
-                                      cudaStream_t stream, const Probe *probe);
-// A warp or a CTA per segment for f16 / bf16 / i32 values (no plan).
+                                      cudaStream_t stream, const Probe *probe,
+                                      const swg_map *map = nullptr);
+// A warp or a CTA per segment for f16 / bf16 / i32 values, and for mapped
+// reductions of every floating type (no plan).  `map` (may be null) is
+// applied to every value before it is reduced; integer segments ignore it.
 cudaError_t launch_segreduce_typed(int kind, int dtype, const void *values,
                                    const int32_t *offsets, void *out,
                                    int32_t value_count, int32_t segment_count,
                                    bool cta, int sm_count, cudaStream_t stream,
-                                   const Probe *probe);
+                                   const Probe *probe,
+                                   const swg_map *map = nullptr);
 // Runs a wait that cannot succeed for `limit_ns`, so that the plan's error
 // words report a timeout (see swg_plan_selftest_timeout).
 cudaError_t launch_wait_selftest(const DevicePlan &plan, uint64_t limit_ns,

@@ -112,12 +112,12 @@ segreduce_sum_max_kernel(const float *__restrict__ values,
 // warp or CTA per segment for f16 / bf16 / i32 values: the plan-free mapping
 // of small inputs.  Coalesced element loads, four accumulators per thread.
 // ---------------------------------------------------------------------------
-template <class Op, class T, bool kCta>
+template <class Op, class T, bool kCta, class M = NoMap>
 __global__ void __launch_bounds__(kWarpKernelThreads)
 segreduce_typed_kernel(const T *__restrict__ values,
                        const int32_t *__restrict__ offsets,
                        typename Op::Acc *__restrict__ out,
-                       int32_t segment_count) {
+                       int32_t segment_count, M map) {
   using A = typename Op::Acc;
   __shared__ float scratch[32];
   const int lane = threadIdx.x & 31;
@@ -129,25 +129,28 @@ segreduce_typed_kernel(const T *__restrict__ values,
   const int64_t stride =
       kCta ? (int64_t)gridDim.x
            : ((int64_t)gridDim.x * kWarpKernelThreads) >> 5;
-  for (int64_t seg = first; seg < segment_count; seg += stride) {
-    const int64_t begin = __ldg(offsets + seg);
-    const int64_t end = __ldg(offsets + seg + 1);
-    A a0 = Op::identity(), a1 = Op::identity(), a2 = Op::identity(),
-      a3 = Op::identity();
-    int64_t i = begin + rank;
-    for (; i + 3 * width < end; i += 4 * width) {
-      const T q0 = values[i], q1 = values[i + width],
-              q2 = values[i + 2 * width], q3 = values[i + 3 * width];
-      a0 = Op::apply(a0, Elem<T>::get(q0));
-      a1 = Op::apply(a1, Elem<T>::get(q1));
-      a2 = Op::apply(a2, Elem<T>::get(q2));
-      a3 = Op::apply(a3, Elem<T>::get(q3));
+  with_fixed_map(map, [&](auto apply) {
+    for (int64_t seg = first; seg < segment_count; seg += stride) {
+      const int64_t begin = __ldg(offsets + seg);
+      const int64_t end = __ldg(offsets + seg + 1);
+      A a0 = Op::identity(), a1 = Op::identity(), a2 = Op::identity(),
+        a3 = Op::identity();
+      int64_t i = begin + rank;
+      for (; i + 3 * width < end; i += 4 * width) {
+        const T q0 = values[i], q1 = values[i + width],
+                q2 = values[i + 2 * width], q3 = values[i + 3 * width];
+        a0 = Op::apply(a0, apply(Elem<T>::get(q0)));
+        a1 = Op::apply(a1, apply(Elem<T>::get(q1)));
+        a2 = Op::apply(a2, apply(Elem<T>::get(q2)));
+        a3 = Op::apply(a3, apply(Elem<T>::get(q3)));
+      }
+      for (; i < end; i += width)
+        a0 = Op::apply(a0, apply(Elem<T>::get(values[i])));
+      A r = Op::apply(Op::apply(a0, a1), Op::apply(a2, a3));
+      r = kCta ? cta_reduce<Op>(r, scratch) : warp_reduce<Op>(r);
+      if (rank == 0) out[seg] = r;
     }
-    for (; i < end; i += width) a0 = Op::apply(a0, Elem<T>::get(values[i]));
-    A r = Op::apply(Op::apply(a0, a1), Op::apply(a2, a3));
-    r = kCta ? cta_reduce<Op>(r, scratch) : warp_reduce<Op>(r);
-    if (rank == 0) out[seg] = r;
-  }
+  });
 }
 
 // ---------------------------------------------------------------------------
@@ -400,9 +403,10 @@ __device__ __forceinline__ uint4 lds_line(const void *p) {
 // Warp-collective: reduces tile[lo, hi) (element indices) -- scalar ends,
 // 128-bit body, four independent accumulators per lane -- and returns the
 // result to every lane.
-template <class Op, class T>
+template <class Op, class T, class M>
 __device__ __forceinline__ typename Op::Acc warp_range(const T *tile, int lo,
-                                                       int hi, int lane) {
+                                                       int hi, int lane,
+                                                       const M &map) {
   using A = typename Op::Acc;
   constexpr int P = kPerLine<T>;
   int blo = (lo + P - 1) & ~(P - 1), bhi = hi & ~(P - 1);
@@ -410,31 +414,34 @@ __device__ __forceinline__ typename Op::Acc warp_range(const T *tile, int lo,
   const int head_end = blo < hi ? blo : hi;
   A a0 = Op::identity(), a1 = Op::identity(), a2 = Op::identity(),
     a3 = Op::identity();
-  if (lo + lane < head_end) a0 = Op::apply(a0, Elem<T>::get(tile[lo + lane]));
+  if (lo + lane < head_end)
+    a0 = Op::apply(a0, map(Elem<T>::get(tile[lo + lane])));
   const uint4 *body = reinterpret_cast<const uint4 *>(tile);
   const int vlo = blo / P, vhi = bhi / P;
   int v = vlo + lane;
   for (; v + 96 < vhi; v += 128) {
     const uint4 q0 = lds_line(body + v), q1 = lds_line(body + v + 32),
                 q2 = lds_line(body + v + 64), q3 = lds_line(body + v + 96);
-    a0 = fold_line<Op, T>(a0, q0);
-    a1 = fold_line<Op, T>(a1, q1);
-    a2 = fold_line<Op, T>(a2, q2);
-    a3 = fold_line<Op, T>(a3, q3);
+    a0 = fold_line<Op, T, M>(a0, q0, map);
+    a1 = fold_line<Op, T, M>(a1, q1, map);
+    a2 = fold_line<Op, T, M>(a2, q2, map);
+    a3 = fold_line<Op, T, M>(a3, q3, map);
   }
-  for (; v < vhi; v += 32) a0 = fold_line<Op, T>(a0, lds_line(body + v));
+  for (; v < vhi; v += 32)
+    a0 = fold_line<Op, T, M>(a0, lds_line(body + v), map);
   const int tail = bhi > head_end ? bhi : head_end;
-  if (tail + lane < hi) a1 = Op::apply(a1, Elem<T>::get(tile[tail + lane]));
+  if (tail + lane < hi)
+    a1 = Op::apply(a1, map(Elem<T>::get(tile[tail + lane])));
   return warp_reduce<Op>(Op::apply(Op::apply(a0, a1), Op::apply(a2, a3)));
 }
 
 // Warp-collective: reduce one staged task.
-template <class Op, class T>
+template <class Op, class T, class M>
 __device__ __forceinline__ void process_task(
     const Task &task, const Stage &stage, int mis,
     typename Op::Acc *__restrict__ out,
     typename Op::Acc *__restrict__ partials, WarpScratch *scratch,
-    const Limits &limits, uint32_t *control, int lane) {
+    const Limits &limits, uint32_t *control, int lane, const M &map) {
   using A = typename Op::Acc;
   constexpr int P = kPerLine<T>;
   if (!task_ok(task, limits)) {
@@ -449,7 +456,7 @@ __device__ __forceinline__ void process_task(
 
   if (kind == kTaskChunk) {
     // One piece of a long segment occupies tile[shift, shift + vcount).
-    const A r = warp_range<Op, T>(tile, shift, shift + vcount, lane);
+    const A r = warp_range<Op, T, M>(tile, shift, shift + vcount, lane, map);
     if (lane == 0) {
       if (task.count < 0) out[task.seg] = r;
       else partials[task.count] = r;
@@ -502,7 +509,7 @@ __device__ __forceinline__ void process_task(
       A x[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i)
-        x[i] = a + i < b ? Elem<T>::get(tile[a + i]) : Op::identity();
+        x[i] = a + i < b ? map(Elem<T>::get(tile[a + i])) : Op::identity();
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc = Op::apply(acc, x[i]);
     }
@@ -511,7 +518,7 @@ __device__ __forceinline__ void process_task(
         A x[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          x[i] = a + 8 + i < b ? Elem<T>::get(tile[a + 8 + i])
+          x[i] = a + 8 + i < b ? map(Elem<T>::get(tile[a + 8 + i]))
                                : Op::identity();
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc = Op::apply(acc, x[i]);
@@ -542,12 +549,12 @@ __device__ __forceinline__ void process_task(
         p3 = Op::identity();
       int i = ea + sub;
       for (; i + 24 < eb; i += 32) {
-        p0 = Op::apply(p0, Elem<T>::get(tile[i]));
-        p1 = Op::apply(p1, Elem<T>::get(tile[i + 8]));
-        p2 = Op::apply(p2, Elem<T>::get(tile[i + 16]));
-        p3 = Op::apply(p3, Elem<T>::get(tile[i + 24]));
+        p0 = Op::apply(p0, map(Elem<T>::get(tile[i])));
+        p1 = Op::apply(p1, map(Elem<T>::get(tile[i + 8])));
+        p2 = Op::apply(p2, map(Elem<T>::get(tile[i + 16])));
+        p3 = Op::apply(p3, map(Elem<T>::get(tile[i + 24])));
       }
-      for (; i < eb; i += 8) p0 = Op::apply(p0, Elem<T>::get(tile[i]));
+      for (; i < eb; i += 8) p0 = Op::apply(p0, map(Elem<T>::get(tile[i])));
       A r = Op::apply(Op::apply(p0, p1), Op::apply(p2, p3));
       r = Op::apply(r, __shfl_xor_sync(group_mask, r, 4));
       r = Op::apply(r, __shfl_xor_sync(group_mask, r, 2));
@@ -559,20 +566,20 @@ __device__ __forceinline__ void process_task(
       // (the 128-bit range reduce of the chunk path was tried here: same
       // speed on the lognormal workload, eight more registers everywhere)
 #if SWG_WIDE_VECTOR
-      const A r =
-          warp_range<Op, T>(tile, scratch->begin[e], scratch->end[e], lane);
+      const A r = warp_range<Op, T, M>(tile, scratch->begin[e],
+                                       scratch->end[e], lane, map);
 #else
       const int ea = scratch->begin[e], eb = scratch->end[e];
       A p0 = Op::identity(), p1 = Op::identity(), p2 = Op::identity(),
         p3 = Op::identity();
       int i = ea + lane;
       for (; i + 96 < eb; i += 128) {
-        p0 = Op::apply(p0, Elem<T>::get(tile[i]));
-        p1 = Op::apply(p1, Elem<T>::get(tile[i + 32]));
-        p2 = Op::apply(p2, Elem<T>::get(tile[i + 64]));
-        p3 = Op::apply(p3, Elem<T>::get(tile[i + 96]));
+        p0 = Op::apply(p0, map(Elem<T>::get(tile[i])));
+        p1 = Op::apply(p1, map(Elem<T>::get(tile[i + 32])));
+        p2 = Op::apply(p2, map(Elem<T>::get(tile[i + 64])));
+        p3 = Op::apply(p3, map(Elem<T>::get(tile[i + 96])));
       }
-      for (; i < eb; i += 32) p0 = Op::apply(p0, Elem<T>::get(tile[i]));
+      for (; i < eb; i += 32) p0 = Op::apply(p0, map(Elem<T>::get(tile[i])));
       const A r =
           warp_reduce<Op>(Op::apply(Op::apply(p0, p1), Op::apply(p2, p3)));
 #endif
@@ -595,7 +602,7 @@ __device__ __forceinline__ void process_task(
 // find their lines on the way instead of starting a cold DRAM round trip
 // after the wait.  The caller's arrays are read into the SM and written only
 // after the kernel before has finished.
-template <class Op, class T>
+template <class Op, class T, class M = NoMap>
 __global__ void __launch_bounds__(kSplitWarps * 32)
 segreduce_split_kernel(const T *__restrict__ values,
                        typename Op::Acc *__restrict__ out, int32_t value_count,
@@ -603,7 +610,7 @@ segreduce_split_kernel(const T *__restrict__ values,
                        const int32_t *__restrict__ d_off,
                        typename Op::Acc *__restrict__ partials,
                        uint32_t *__restrict__ control, Limits limits,
-                       uint32_t prefetch_ctas) {
+                       uint32_t prefetch_ctas, M map) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full[kSplitWarps];
   __shared__ WarpScratch scratch[kSplitWarps];
@@ -649,8 +656,11 @@ segreduce_split_kernel(const T *__restrict__ values,
     if (lane == 0) report(control, kErrTimeout, (uint32_t)index);
     return;
   }
-  process_task<Op, T>(task, stage, mis, out, partials, &scratch[warp], limits,
-                      control, lane);
+  with_fixed_map(map, [&](auto apply) {
+    process_task<Op, T, decltype(apply)>(task, stage, mis, out, partials,
+                                         &scratch[warp], limits, control,
+                                         lane, apply);
+  });
 }
 
 // persistent schedule: one resident CTA per SM, every warp an independent
@@ -738,8 +748,9 @@ segreduce_persistent_kernel(const float *__restrict__ values,
         running = false;
         break;
       }
-      process_task<Op, float>(t, stage_at(ring, s), mis, out, partials,
-                              &scratch[warp], limits, control, lane);
+      process_task<Op, float, NoMap>(t, stage_at(ring, s), mis, out, partials,
+                                     &scratch[warp], limits, control, lane,
+                                     NoMap{});
       __syncwarp();  // every lane is done with the stage before it is refilled
       const Task n = shuffle_task(nxt, s);
       if (!is_stop(n)) stage_in(n, s);
@@ -778,7 +789,7 @@ segreduce_persistent_kernel(const float *__restrict__ values,
 // hold many segments (their reduction keeps a stage busy longest), 7 % slower
 // where nearly every tile is a chunk of a long segment -- the planner picks by
 // the share of values in long segments.
-template <class Op, class T, int kWarps>
+template <class Op, class T, int kWarps, class M = NoMap>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 segreduce_resident_kernel(const T *__restrict__ values,
                           typename Op::Acc *__restrict__ out,
@@ -786,7 +797,8 @@ segreduce_resident_kernel(const T *__restrict__ values,
                           const Task *__restrict__ tasks, int32_t task_count,
                           const int32_t *__restrict__ d_off,
                           typename Op::Acc *__restrict__ partials,
-                          uint32_t *__restrict__ control, Limits limits) {
+                          uint32_t *__restrict__ control, Limits limits,
+                          M map) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full[kWarps];
   __shared__ WarpScratch scratch[kWarps];
@@ -839,8 +851,11 @@ segreduce_resident_kernel(const T *__restrict__ values,
       return;
     }
     parity ^= 1u;
-    process_task<Op, T>(task, stage, mis, out, partials, &scratch[warp],
-                        limits, control, lane);
+    with_fixed_map(map, [&](auto apply) {
+      process_task<Op, T, decltype(apply)>(task, stage, mis, out, partials,
+                                           &scratch[warp], limits, control,
+                                           lane, apply);
+    });
     if (!more) return;
     __syncwarp();  // every lane is done with the stage before it is refilled
     task = next;
@@ -1045,6 +1060,25 @@ static cudaError_t with_types(int kind, int dtype, F &&f) {
   }
 }
 
+// Calls f with the operator, element and map types of (kind, dtype, map).
+// Maps exist for the floating element types only.
+template <class F>
+static cudaError_t with_map(int kind, int dtype, const swg_map *map, F &&f) {
+  if (!map || dtype == SWG_DTYPE_I32)
+    return with_types(kind, dtype, [&](auto op, auto element) {
+      return f(op, element, NoMap{});
+    });
+  const ScalarMap m{map->fn, map->scale, map->shift};
+  switch (dtype) {
+    case SWG_DTYPE_F16:
+      return with_op(kind, [&](auto op) { return f(op, __half{}, m); });
+    case SWG_DTYPE_BF16:
+      return with_op(kind, [&](auto op) { return f(op, __nv_bfloat16{}, m); });
+    default:
+      return with_op(kind, [&](auto op) { return f(op, float{}, m); });
+  }
+}
+
 cudaError_t configure_segreduce_kernels() {
   DevicePlan none;
   for (int kind : {SWG_KIND_SUM, SWG_KIND_MAX, SWG_KIND_MIN}) {
@@ -1053,21 +1087,26 @@ cudaError_t configure_segreduce_kernels() {
                                                nullptr, true);
     });
     if (e != cudaSuccess) return e;
+    const swg_map some_map{SWG_MAP_IDENTITY, 1.0f, 0.0f};
     for (int dtype : {SWG_DTYPE_F32, SWG_DTYPE_F16, SWG_DTYPE_BF16,
                       SWG_DTYPE_I32}) {
-      e = with_types(kind, dtype, [&](auto op, auto element) {
-        using Op = decltype(op);
-        using T = decltype(element);
-        const cudaError_t inner = cudaFuncSetAttribute(
-            segreduce_resident_kernel<Op, T, kResidentWarps>,
-            cudaFuncAttributeMaxDynamicSharedMemorySize,
-            kResidentWarps * kStageBytes);
-        if (inner != cudaSuccess) return inner;
-        return cudaFuncSetAttribute(segreduce_split_kernel<Op, T>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    kSplitBytes);
-      });
-      if (e != cudaSuccess) return e;
+      for (const swg_map *map : {(const swg_map *)nullptr, &some_map}) {
+        if (map && dtype == SWG_DTYPE_I32) continue;
+        e = with_map(kind, dtype, map, [&](auto op, auto element, auto m) {
+          using Op = decltype(op);
+          using T = decltype(element);
+          using M = decltype(m);
+          const cudaError_t inner = cudaFuncSetAttribute(
+              segreduce_resident_kernel<Op, T, kResidentWarps, M>,
+              cudaFuncAttributeMaxDynamicSharedMemorySize,
+              kResidentWarps * kStageBytes);
+          if (inner != cudaSuccess) return inner;
+          return cudaFuncSetAttribute(
+              segreduce_split_kernel<Op, T, M>,
+              cudaFuncAttributeMaxDynamicSharedMemorySize, kSplitBytes);
+        });
+        if (e != cudaSuccess) return e;
+      }
     }
   }
   return cudaSuccess;
@@ -1078,28 +1117,30 @@ cudaError_t launch_segreduce_typed(int kind, int dtype, const void *values,
                                    const int32_t *offsets, void *out,
                                    int32_t value_count, int32_t segment_count,
                                    bool cta, int sm_count, cudaStream_t stream,
-                                   const Probe *probe) {
+                                   const Probe *probe, const swg_map *map) {
   const int per_cta = cta ? 1 : kWarpKernelThreads / 32;
   int64_t grid = ((int64_t)segment_count + per_cta - 1) / per_cta;
   const int64_t cap = (int64_t)sm_count * 8 * 4;
   if (grid > cap) grid = cap;
   probe_begin(probe, stream);
-  const cudaError_t e = with_types(kind, dtype, [&](auto op, auto element) {
-    using Op = decltype(op);
-    using T = decltype(element);
-    using A = typename Op::Acc;
-    if (cta)
-      segreduce_typed_kernel<Op, T, true>
-          <<<(unsigned)grid, kWarpKernelThreads, 0, stream>>>(
-              static_cast<const T *>(values), offsets, static_cast<A *>(out),
-              segment_count);
-    else
-      segreduce_typed_kernel<Op, T, false>
-          <<<(unsigned)grid, kWarpKernelThreads, 0, stream>>>(
-              static_cast<const T *>(values), offsets, static_cast<A *>(out),
-              segment_count);
-    return cudaGetLastError();
-  });
+  const cudaError_t e =
+      with_map(kind, dtype, map, [&](auto op, auto element, auto m) {
+        using Op = decltype(op);
+        using T = decltype(element);
+        using M = decltype(m);
+        using A = typename Op::Acc;
+        if (cta)
+          segreduce_typed_kernel<Op, T, true, M>
+              <<<(unsigned)grid, kWarpKernelThreads, 0, stream>>>(
+                  static_cast<const T *>(values), offsets,
+                  static_cast<A *>(out), segment_count, m);
+        else
+          segreduce_typed_kernel<Op, T, false, M>
+              <<<(unsigned)grid, kWarpKernelThreads, 0, stream>>>(
+                  static_cast<const T *>(values), offsets,
+                  static_cast<A *>(out), segment_count, m);
+        return cudaGetLastError();
+      });
   probe_end(probe, stream);
   (void)value_count;
   return e;
@@ -1218,24 +1259,27 @@ static cudaError_t launch_merge(int kind, int dtype, const DevicePlan &plan,
 cudaError_t launch_segreduce_split(int kind, int dtype, const void *values,
                                    void *out, int32_t value_count,
                                    const DevicePlan &plan, cudaStream_t stream,
-                                   const Probe *probe) {
+                                   const Probe *probe, const swg_map *map) {
   if (plan.task_count == 0) return cudaSuccess;
   const unsigned grid =
       (unsigned)((plan.task_count + kSplitWarps - 1) / kSplitWarps);
   const uint32_t first_wave =
       (uint32_t)plan.sm_count * SWG_SPLIT_CTAS_PER_SM;
   probe_begin(probe, stream);
-  const cudaError_t e = with_types(kind, dtype, [&](auto op, auto element) {
-    using Op = decltype(op);
-    using T = decltype(element);
-    using A = typename Op::Acc;
-    return launch_serialised(
-        segreduce_split_kernel<Op, T>, grid, kSplitWarps * 32, kSplitBytes,
-        stream, static_cast<const T *>(values), static_cast<A *>(out),
-        value_count, (const Task *)plan.tasks, plan.task_count,
-        (const int32_t *)plan.offsets, reinterpret_cast<A *>(plan.partials),
-        plan.control, limits_of(plan, value_count), first_wave);
-  });
+  const cudaError_t e =
+      with_map(kind, dtype, map, [&](auto op, auto element, auto m) {
+        using Op = decltype(op);
+        using T = decltype(element);
+        using M = decltype(m);
+        using A = typename Op::Acc;
+        return launch_serialised(
+            segreduce_split_kernel<Op, T, M>, grid, kSplitWarps * 32,
+            kSplitBytes, stream, static_cast<const T *>(values),
+            static_cast<A *>(out), value_count, (const Task *)plan.tasks,
+            plan.task_count, (const int32_t *)plan.offsets,
+            reinterpret_cast<A *>(plan.partials), plan.control,
+            limits_of(plan, value_count), first_wave, m);
+      });
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;
   return launch_merge(kind, dtype, plan, out, value_count, stream);
@@ -1260,25 +1304,29 @@ cudaError_t launch_segreduce_persistent(int kind, const float *values,
 cudaError_t launch_segreduce_resident(int kind, int dtype, const void *values,
                                       void *out, int32_t value_count,
                                       const DevicePlan &plan,
-                                      cudaStream_t stream,
-                                      const Probe *probe) {
+                                      cudaStream_t stream, const Probe *probe,
+                                      const swg_map *map) {
   if (plan.task_count == 0) return cudaSuccess;
   int grid = plan.sm_count;
   const int needed = (plan.task_count + kResidentWarps - 1) / kResidentWarps;
   if (grid > needed) grid = needed;
   probe_begin(probe, stream);
-  const cudaError_t e = with_types(kind, dtype, [&](auto op, auto element) {
-    using Op = decltype(op);
-    using T = decltype(element);
-    using A = typename Op::Acc;
-    return launch_serialised(
-        segreduce_resident_kernel<Op, T, kResidentWarps>, (unsigned)grid,
-        kResidentWarps * 32, (size_t)kResidentWarps * kStageBytes, stream,
-        static_cast<const T *>(values), static_cast<A *>(out), value_count,
-        (const Task *)plan.tasks, plan.task_count,
-        (const int32_t *)plan.offsets, reinterpret_cast<A *>(plan.partials),
-        plan.control, limits_of(plan, value_count));
-  });
+  const cudaError_t e =
+      with_map(kind, dtype, map, [&](auto op, auto element, auto m) {
+        using Op = decltype(op);
+        using T = decltype(element);
+        using M = decltype(m);
+        using A = typename Op::Acc;
+        return launch_serialised(
+            segreduce_resident_kernel<Op, T, kResidentWarps, M>,
+            (unsigned)grid, kResidentWarps * 32,
+            (size_t)kResidentWarps * kStageBytes, stream,
+            static_cast<const T *>(values), static_cast<A *>(out),
+            value_count, (const Task *)plan.tasks, plan.task_count,
+            (const int32_t *)plan.offsets,
+            reinterpret_cast<A *>(plan.partials), plan.control,
+            limits_of(plan, value_count), m);
+      });
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;
   return launch_merge(kind, dtype, plan, out, value_count, stream);

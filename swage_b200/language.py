@@ -135,7 +135,15 @@ def exp(value):
     _outside_kernel("exp")
 
 
+def abs(value):  # noqa: A001 - name fixed by the kernel language
+    """Elementwise absolute value (symbolic).  An extension: usable in front
+    of a segment reduction (a ``swage.map`` region feeding ``swage.reduce``),
+    which the reference's lowering does not accept."""
+    _outside_kernel("abs")
+
+
 __all__ = [
+    "abs",
     "arange",
     "constexpr",
     "exp",

@@ -109,6 +109,78 @@ def test_recognises_the_four_programs():
                              "out": "output_ptr"}
 
 
+@sw.jit
+def sum_of_squares(values_ptr, offsets_ptr, output_ptr,  # noqa: D103
+                   SCALE: sl.constexpr):
+    sid = sl.segment_id(0)
+    x = sl.load_segment(sl.segment(values_ptr, offsets_ptr, sid))
+    y = x * SCALE - 1.5
+    sl.store(output_ptr + sid, sl.sum(y * y))
+
+
+@sw.jit
+def max_magnitude(values_ptr, offsets_ptr, output_ptr):  # noqa: D103
+    sid = sl.segment_id(0)
+    x = sl.load_segment(sl.segment(values_ptr, offsets_ptr, sid))
+    sl.store(output_ptr + sid, sl.max(sl.abs(-x)))
+
+
+@sw.jit
+def sum_of_exponentials(values_ptr, offsets_ptr, output_ptr,  # noqa: D103
+                        SHIFT: sl.constexpr):
+    sid = sl.segment_id(0)
+    x = sl.load_segment(sl.segment(values_ptr, offsets_ptr, sid))
+    sl.store(output_ptr + sid, sl.min(sl.exp(SHIFT + 2 * x)))
+
+
+@sw.jit
+def reassociated(values_ptr, offsets_ptr, output_ptr):  # noqa: D103
+    sid = sl.segment_id(0)
+    x = sl.load_segment(sl.segment(values_ptr, offsets_ptr, sid))
+    sl.store(output_ptr + sid, sl.sum((x - 1.0) * 2.0))
+
+
+@sw.jit
+def map_after_the_function(values_ptr, offsets_ptr, output_ptr):  # noqa: D103
+    sid = sl.segment_id(0)
+    x = sl.load_segment(sl.segment(values_ptr, offsets_ptr, sid))
+    sl.store(output_ptr + sid, sl.sum(sl.exp(x) * 2.0))
+
+
+def test_recognises_maps_in_front_of_a_reduction():
+    """``fn(scale * x + shift)`` with fn in identity / abs / square / exp and
+    the constants literals or constexpr parameters; only forms that ARE one
+    multiply and one add in fp32 are taken (nothing is reassociated)."""
+    from swage_b200._frontend import constant_value
+
+    program = sum_of_squares.recognize()
+    assert program.kind == "segmented_sum"
+    function, scale, shift = program.map
+    assert function == "square"
+    assert constant_value(scale, {"SCALE": 3}) == 3.0
+    assert constant_value(shift, {"SCALE": 3}) == -1.5
+
+    program = max_magnitude.recognize()
+    assert program.kind == "segmented_max"
+    function, scale, shift = program.map
+    assert function == "abs"
+    assert constant_value(scale, {}) == -1.0
+    value = constant_value(shift, {})
+    assert value == 0.0 and str(value) == "-0.0"  # the neutral addend
+
+    program = sum_of_exponentials.recognize()
+    assert program.kind == "segmented_min"
+    function, scale, shift = program.map
+    assert (function, constant_value(scale, {}),
+            constant_value(shift, {"SHIFT": 0.25})) == ("exp", 2.0, 0.25)
+
+    assert segmented_sum.recognize().map is None
+    for kernel in (reassociated, map_after_the_function):
+        with pytest.raises(sw.CompilationError,
+                           match="not one of the supported"):
+            kernel.recognize()
+
+
 def test_non_canonical_bodies_are_compilation_errors():
     @sw.jit
     def swapped(x_ptr, y_ptr, output_ptr, n, BLOCK: sl.constexpr):

@@ -118,6 +118,29 @@ def test_fp64_references_and_tolerance():
     assert np.all(np.abs(sequential - exact) <= bound + 1e-30)
 
 
+def test_element_map_rounds_the_product_and_the_sum_separately():
+    """``fn(scale * x + shift)`` in fp32, no contraction: 0.1 * 10 rounds to
+    1 before -1 is added (a fused multiply-add would leave 2^-26 behind);
+    -0.0 is the neutral shift; |NaN| stays NaN."""
+    x = np.array([10.0, -0.0, 3.0, np.nan, -np.inf], np.float32)
+    got = oracle.map_f32(x, "identity", np.float32(0.1), -1.0)
+    assert got[0] == 0.0
+    assert np.float32(0.1).astype(np.float64) * 10.0 - 1.0 != 0.0
+    unchanged = oracle.map_f32(x, "identity", 1.0, -0.0)
+    assert np.array_equal(unchanged.view(np.uint32), x.view(np.uint32))
+    assert oracle.map_f32(x, "identity", 1.0, 0.0)[1].view(np.uint32) == 0
+    assert np.array_equal(oracle.map_f32(x, "abs")[[1, 2, 4]],
+                          np.array([0.0, 3.0, np.inf], np.float32))
+    assert np.isnan(oracle.map_f32(x, "abs")[3])
+    assert np.array_equal(oracle.map_f32(x, "square", 2.0, 1.0)[[0, 2]],
+                          np.array([441.0, 49.0], np.float32))
+    expected = np.exp(np.float64(0.5) * 3.0 - 1.0)
+    assert oracle.map_f32(x, "exp", 0.5, -1.0)[2] == np.float32(expected)
+    assert oracle.map_f32(x, "exp")[4] == 0.0
+    with pytest.raises(KeyError):
+        oracle.map_f32(x, "sqrt")
+
+
 def test_softmax_oracles():
     rng = np.random.default_rng(6)
     lengths = np.array([0, 1, 5, 0, 300, 33])
