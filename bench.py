@@ -1015,6 +1015,8 @@ def run_ours(args):
                 "frac_of_measured_copy": got["frac"],
                 "pct_of_8tbs": 100.0 * got["achieved_gbs"] / NOMINAL_HBM_GBS,
                 "step_us": 1e3 * got["ms_per_step"],
+                "step_gbs": other.bytes_per_step
+                / (got["ms_per_step"] * 1e-3) / 1e9,
                 "step_gelems": other.total_elements
                 / (got["ms_per_step"] * 1e-3) / 1e9,
                 "l2": got["l2"],

@@ -275,6 +275,35 @@ int swg_segreduce_map(int kind, int dtype, const swg_map *map,
                       const swg_plan *plan, int schedule, int32_t block_hint,
                       void *stream);
 
+/* A device buffer that other processes of the node can map and store into:
+ * what swg_scatter_results_f32 writes to.  create: cudaMalloc on the current
+ * device plus its 64-byte CUDA IPC handle, to be sent to the other processes
+ * by any means (torch.distributed.all_gather_object does); open: maps a
+ * peer's buffer into the CURRENT device's address space (peer access over
+ * NVLink is enabled on first use) -- the owner does not open its own; close /
+ * destroy undo open / create (close every mapping before the owner destroys).
+ * Plumbing, no kernels.  No reference counterpart. */
+#define SWG_PEER_HANDLE_BYTES 64
+int swg_peer_buffer_create(int64_t bytes, void **buffer, unsigned char *handle);
+int swg_peer_buffer_open(const unsigned char *handle, void **buffer);
+int swg_peer_buffer_close(void *buffer);
+int swg_peer_buffer_destroy(void *buffer);
+
+/* Result exchange of a sharded reduction without a collective:
+ * dst_bases[p][dst_offset + i] = src[i] for 0 <= p < dst_count (at most 16),
+ * 0 <= i < count.  `src` is this GPU's result shard; the destinations are
+ * device pointers to every GPU's copy of the full result array -- this GPU's
+ * own and its peers', mapped into this process through CUDA IPC or peer
+ * access -- each 16-byte aligned at its base.  One kernel on `stream`, queued
+ * behind the reduction; over NVLink it issues plain 128-bit stores only: no
+ * multicast, no load from peer memory, no wait on another GPU.  A destination
+ * is complete when this call's stream has passed the call; telling the peers
+ * so (a barrier, an event) is the caller's.  No reference counterpart: the
+ * reference is single-GPU (python/swage/_runtime.py:146-151). */
+int swg_scatter_results_f32(const float *src, int64_t count,
+                            void *const *dst_bases, int32_t dst_count,
+                            int64_t dst_offset, void *stream);
+
 /* Sum AND max of every segment in one pass over the values:
  * out_sum[s] = swg_segreduce_f32(SWG_KIND_SUM)[s] to the documented tolerance,
  * out_max[s] = swg_segreduce_f32(SWG_KIND_MAX)[s] bit for bit, for

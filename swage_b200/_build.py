@@ -21,6 +21,7 @@ SOURCES = (
     "swg_segreduce.cu",
     "swg_softmax.cu",
     "swg_device_plan.cu",
+    "swg_exchange.cu",
     "swg_planner.cpp",
 )
 

@@ -57,7 +57,8 @@ EXPORTS = (
     "swg_validate_offsets_device", "swg_plan_create_device",
     "swg_segreduce_sum_max_f32", "swg_plan_create_validated",
     "swg_plan_peek_status", "swg_segreduce", "swg_plan_selftest_timeout",
-    "swg_segreduce_map",
+    "swg_segreduce_map", "swg_scatter_results_f32", "swg_peer_buffer_create",
+    "swg_peer_buffer_open", "swg_peer_buffer_close", "swg_peer_buffer_destroy",
 )
 
 _lock = threading.Lock()
@@ -102,6 +103,18 @@ def _declare(lib):
     lib.swg_segreduce_map.argtypes = [
         c_int, c_int, ctypes.POINTER(Map), ptr, ptr, ptr, c_i32, c_i32, ptr,
         c_int, c_i32, ptr]
+    lib.swg_peer_buffer_create.restype = c_int
+    lib.swg_peer_buffer_create.argtypes = [
+        c_i64, ctypes.POINTER(ptr), ctypes.c_char_p]
+    lib.swg_peer_buffer_open.restype = c_int
+    lib.swg_peer_buffer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ptr)]
+    lib.swg_peer_buffer_close.restype = c_int
+    lib.swg_peer_buffer_close.argtypes = [ptr]
+    lib.swg_peer_buffer_destroy.restype = c_int
+    lib.swg_peer_buffer_destroy.argtypes = [ptr]
+    lib.swg_scatter_results_f32.restype = c_int
+    lib.swg_scatter_results_f32.argtypes = [
+        ptr, c_i64, ctypes.POINTER(ptr), c_i32, c_i64, ptr]
     lib.swg_segsoftmax_f32.restype = c_int
     lib.swg_segsoftmax_f32.argtypes = [
         ptr, ptr, ptr, c_i32, c_i32, ptr, c_int, ptr]
@@ -199,6 +212,49 @@ def segreduce_map(kind, dtype, fn, scale, shift, values_ptr, offsets_ptr,
             out_ptr, value_count, segment_count, plan_handle, schedule, block,
             stream),
         "swg_segreduce_map",
+    )
+
+
+PEER_HANDLE_BYTES = 64
+
+
+def peer_buffer_create(byte_count):
+    """A device buffer other processes can map: ``(pointer, handle bytes)``."""
+    pointer = ctypes.c_void_p()
+    handle = ctypes.create_string_buffer(PEER_HANDLE_BYTES)
+    check(library().swg_peer_buffer_create(byte_count, ctypes.byref(pointer),
+                                           handle),
+          "swg_peer_buffer_create")
+    return pointer.value, handle.raw
+
+
+def peer_buffer_open(handle):
+    """Map a peer's buffer into the current device's address space."""
+    if len(handle) != PEER_HANDLE_BYTES:
+        raise ValueError("a peer buffer handle has 64 bytes")
+    pointer = ctypes.c_void_p()
+    check(library().swg_peer_buffer_open(handle, ctypes.byref(pointer)),
+          "swg_peer_buffer_open")
+    return pointer.value
+
+
+def peer_buffer_close(pointer):
+    check(library().swg_peer_buffer_close(pointer), "swg_peer_buffer_close")
+
+
+def peer_buffer_destroy(pointer):
+    check(library().swg_peer_buffer_destroy(pointer),
+          "swg_peer_buffer_destroy")
+
+
+def scatter_results(src_ptr, count, destination_ptrs, offset, stream):
+    """``destination[p][offset + i] = src[i]`` for every destination pointer
+    (device memory of this GPU or peer-mapped memory of another)."""
+    bases = (ctypes.c_void_p * len(destination_ptrs))(*destination_ptrs)
+    check(
+        library().swg_scatter_results_f32(
+            src_ptr, count, bases, len(destination_ptrs), offset, stream),
+        "swg_scatter_results_f32",
     )
 
 

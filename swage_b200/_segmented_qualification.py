@@ -240,7 +240,7 @@ def _validate_device_offsets(offsets, value_count, output_count, torch):
         raise ValueError("offsets must contain at least the initial zero")
     segment_count = count - 1
     _validate_counts(value_count, segment_count)
-    stream = torch.cuda.current_stream()
+    stream = _runtime._current_stream(torch)
     reason, _, digest, last = _native.validate_offsets_device(
         offsets.data_ptr(), segment_count, value_count, output_count,
         stream.cuda_stream,
@@ -322,7 +322,7 @@ class SegmentPlan:
         code = _native.OP_SOFTMAX if op == "softmax" else _native.OP_REDUCE
         self._handle = None
         _validate_counts(self.value_count, self.segment_count)
-        stream = torch.cuda.current_stream()
+        stream = _runtime._current_stream(torch)
         if digest is not None:
             # validated a moment ago on this stream: its summary is reused
             self._handle = _native.plan_create_validated(
@@ -462,7 +462,7 @@ def _cached_device_plan(offsets, value_count, op, device, stream, digest):
 def _plan_for_launch(offsets, value_count, segment_count, op, torch):
     """The cached plan for a launch that was just validated on this thread."""
     device = torch.cuda.current_device()
-    stream = torch.cuda.current_stream().cuda_stream
+    stream = _runtime._current_stream(torch).cuda_stream
     digest = getattr(_last_digest, "value", None)
     _last_digest.value = None
     if digest is not None and digest[:2] == (offsets.data_ptr(),
@@ -615,7 +615,7 @@ def launch_gpu(values, offsets, output, kind, block_size=128, *, plan=None,
     _last_digest.value = None
     if plan is not None:
         _peek(plan)
-    stream = torch.cuda.current_stream()
+    stream = _runtime._current_stream(torch)
     if map is not None:
         dtype = {torch.float32: _native.DTYPE_F32,
                  torch.float16: _native.DTYPE_F16,
@@ -689,7 +689,7 @@ def launch_sum_max_gpu(values, offsets, sum_output, max_output, *,
 
     from . import _native
 
-    stream = torch.cuda.current_stream()
+    stream = _runtime._current_stream(torch)
     _native.segreduce_sum_max(
         values.data_ptr(), offsets.data_ptr(), sum_output.data_ptr(),
         max_output.data_ptr(), value_count, segment_count, stream.cuda_stream)
@@ -735,7 +735,7 @@ def launch_softmax_gpu(values, offsets, output, *, plan=None, schedule="auto",
     _last_digest.value = None
     if plan is not None:
         _peek(plan)
-    stream = torch.cuda.current_stream()
+    stream = _runtime._current_stream(torch)
     _native.segsoftmax(
         values.data_ptr(), offsets.data_ptr(), output.data_ptr(), value_count,
         segment_count, plan.handle if plan is not None else None, code,

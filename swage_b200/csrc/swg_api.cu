@@ -741,6 +741,103 @@ int swg_segreduce_map(int kind, int dtype, const swg_map *map,
                    stream, map);
 }
 
+// ---------------------------------------------------------------------------
+// Buffers other processes of the node can store into (CUDA IPC)
+// ---------------------------------------------------------------------------
+static_assert(sizeof(cudaIpcMemHandle_t) == SWG_PEER_HANDLE_BYTES,
+              "swg_peer_buffer handles carry one cudaIpcMemHandle_t");
+
+int swg_peer_buffer_create(int64_t bytes, void **buffer,
+                           unsigned char *handle) {
+  swg::clear_error();
+  if (bytes <= 0 || !buffer || !handle) {
+    swg::set_error("swg_peer_buffer_create: bad size or null pointer");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  void *p = nullptr;
+  cudaError_t e = cudaMalloc(&p, (size_t)bytes);
+  if (e != cudaSuccess) return cuda_failure("cudaMalloc (peer buffer)", e);
+  cudaIpcMemHandle_t ipc;
+  e = cudaIpcGetMemHandle(&ipc, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return cuda_failure("cudaIpcGetMemHandle", e);
+  }
+  memcpy(handle, &ipc, sizeof(ipc));
+  *buffer = p;
+  return SWG_OK;
+}
+
+int swg_peer_buffer_open(const unsigned char *handle, void **buffer) {
+  swg::clear_error();
+  if (!handle || !buffer) {
+    swg::set_error("swg_peer_buffer_open: null pointer");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  cudaIpcMemHandle_t ipc;
+  memcpy(&ipc, handle, sizeof(ipc));
+  void *p = nullptr;
+  // mapped into the CURRENT device's address space; access to the owning
+  // GPU over NVLink / PCIe is enabled on first use
+  const cudaError_t e =
+      cudaIpcOpenMemHandle(&p, ipc, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return cuda_failure("cudaIpcOpenMemHandle", e);
+  *buffer = p;
+  return SWG_OK;
+}
+
+int swg_peer_buffer_close(void *buffer) {
+  swg::clear_error();
+  if (!buffer) return SWG_OK;
+  const cudaError_t e = cudaIpcCloseMemHandle(buffer);
+  if (e != cudaSuccess) return cuda_failure("cudaIpcCloseMemHandle", e);
+  return SWG_OK;
+}
+
+int swg_peer_buffer_destroy(void *buffer) {
+  swg::clear_error();
+  if (!buffer) return SWG_OK;
+  const cudaError_t e = cudaFree(buffer);
+  if (e != cudaSuccess) return cuda_failure("cudaFree (peer buffer)", e);
+  return SWG_OK;
+}
+
+int swg_scatter_results_f32(const float *src, int64_t count,
+                            void *const *dst_bases, int32_t dst_count,
+                            int64_t dst_offset, void *stream) {
+  swg::clear_error();
+  if (count < 0 || dst_offset < 0 || dst_count < 0 ||
+      dst_count > swg::kMaxPeers) {
+    swg::set_error(
+        "swg_scatter_results_f32: negative count or offset, or more than %d "
+        "destinations", swg::kMaxPeers);
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  if (count == 0 || dst_count == 0) return SWG_OK;
+  if (!src || !dst_bases) {
+    swg::set_error("swg_scatter_results_f32: null pointer");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  float *bases[swg::kMaxPeers];
+  for (int p = 0; p < dst_count; ++p) {
+    if (!dst_bases[p] || ((uintptr_t)dst_bases[p] & 15u) != 0) {
+      swg::set_error(
+          "swg_scatter_results_f32: destination %d is null or not 16-byte "
+          "aligned", p);
+      return SWG_ERR_INVALID_ARGUMENT;
+    }
+    bases[p] = static_cast<float *>(dst_bases[p]);
+  }
+  int device = 0, sm_count = 0;
+  const int status = current_device(&device, &sm_count);
+  if (status != SWG_OK) return status;
+  const cudaError_t e = swg::launch_scatter_results(
+      src, count, bases, dst_count, dst_offset, sm_count,
+      (cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_failure("result scatter launch", e);
+  return SWG_OK;
+}
+
 int swg_segreduce_sum_max_f32(const float *values, const int32_t *offsets,
                               float *out_sum, float *out_max,
                               int32_t value_count, int32_t segment_count,

@@ -58,6 +58,14 @@ inline void probe_end(const Probe *probe, cudaStream_t stream) {
 cudaError_t launch_vadd(const float *x, const float *y, float *out, int32_t n,
                         cudaStream_t stream, const Probe *probe);
 
+// dst_bases[p][dst_offset + i] = src[i] for every destination (device
+// pointers, possibly peer-mapped memory of other GPUs); plain stores.
+constexpr int kMaxPeers = 16;
+cudaError_t launch_scatter_results(const float *src, int64_t count,
+                                   float *const *dst_bases, int peer_count,
+                                   int64_t dst_offset, int sm_count,
+                                   cudaStream_t stream);
+
 cudaError_t launch_segreduce_warp(int kind, const float *values,
                                   const int32_t *offsets, float *out,
                                   int32_t segment_count, int sm_count,

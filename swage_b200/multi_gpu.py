@@ -7,8 +7,12 @@ its rebased offsets resident on its own GPU and calls the single-GPU entry
 points.  The reference is single-GPU (``python/swage/_runtime.py:146-151``
 insists on the current device), so nothing here mirrors a reference function.
 
-``gather_results`` is the optional exchange step: an all-gather of the
-per-segment results (NCCL over NVLink on GPUs; gloo works for CPU tensors).
+``gather_results`` is the optional exchange step as a collective: an
+all-gather of the per-segment results (NCCL over NVLink on GPUs; gloo works
+for CPU tensors).  ``PeerResults`` is the same exchange without a collective:
+every rank stores its results straight into every rank's copy of the full
+result array (plain stores into peer-mapped memory), one small kernel queued
+behind the reduction.
 """
 
 from . import _runtime
@@ -72,4 +76,118 @@ def gather_results(local_output, cuts, group=None):
     return torch.cat([rows[g, :counts[g]] for g in range(world)])
 
 
-__all__ = ["gather_results", "local_shard", "shard_cuts"]
+class PeerResults:
+    """Every rank's copy of the full per-segment result array, filled by the
+    ranks themselves.
+
+    Each rank owns one fp32 buffer of ``cuts[-1]`` results on its GPU and maps
+    every other rank's buffer into its own address space (CUDA IPC over the
+    handles exchanged with ``all_gather_object``).  ``publish(local_output)``
+    queues ONE kernel on the current stream that stores this rank's
+    ``cuts[rank + 1] - cuts[rank]`` results at their place in every copy --
+    plain 128-bit stores over NVLink, no multicast, no load from peer memory,
+    nothing waits on another GPU.  ``wait()`` (synchronise the stream, then a
+    host barrier) is when ``results`` is complete on every rank.
+
+    One process per GPU, all on one node.  Collective: every rank of ``group``
+    constructs, and later closes, its ``PeerResults`` together.
+    """
+
+    def __init__(self, cuts, group=None):
+        from . import _native
+
+        torch = _runtime._import_torch()
+        import torch.distributed as dist
+
+        self._dist = dist
+        self._group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        cuts = [int(c) for c in cuts]
+        if len(cuts) != self.world + 1 or cuts[0] != 0 or any(
+                b < a for a, b in zip(cuts, cuts[1:])):
+            raise ValueError(
+                "cuts must be world_size + 1 nondecreasing segment indices "
+                "starting at zero")
+        self.cuts = cuts
+        self.total = cuts[-1]
+        self.device = torch.cuda.current_device()
+        self._own, handle = _native.peer_buffer_create(4 * max(self.total, 4))
+        self._mapped = {}
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle, group=group)
+        self._bases = []
+        for peer, peer_handle in enumerate(handles):
+            if peer == self.rank:
+                self._bases.append(self._own)
+            else:
+                self._mapped[peer] = _native.peer_buffer_open(peer_handle)
+                self._bases.append(self._mapped[peer])
+        self.results = _device_view(torch, self._own, self.total, self.device)
+        dist.barrier(group)  # every mapping exists before anyone publishes
+
+    def publish(self, local_output):
+        """Queue the stores of this rank's results into every copy."""
+        from . import _native
+
+        torch = _runtime._import_torch()
+        count = self.cuts[self.rank + 1] - self.cuts[self.rank]
+        if (not isinstance(local_output, torch.Tensor)
+                or local_output.dtype != torch.float32
+                or not local_output.is_contiguous()
+                or local_output.device.type != "cuda"
+                or local_output.device.index != self.device):
+            raise TypeError(
+                "local output must be a contiguous fp32 tensor on this "
+                "rank's GPU")
+        if local_output.numel() < count:
+            raise ValueError("local output is shorter than this rank's shard")
+        if self._own is None:
+            raise RuntimeError("the peer buffers are closed")
+        stream = _runtime._current_stream(torch)
+        _native.scatter_results(local_output.data_ptr(), count, self._bases,
+                                self.cuts[self.rank], stream.cuda_stream)
+        local_output.record_stream(stream)
+
+    def wait(self):
+        """On return ``results`` holds every rank's published results."""
+        torch = _runtime._import_torch()
+        _runtime._current_stream(torch).synchronize()
+        self._dist.barrier(self._group)
+
+    def close(self):
+        """Unmap the peers' buffers, then (after a barrier) free this rank's."""
+        from . import _native
+
+        if self._own is None:
+            return
+        torch = _runtime._import_torch()
+        torch.cuda.synchronize()
+        self.results = None
+        for pointer in self._mapped.values():
+            _native.peer_buffer_close(pointer)
+        self._mapped = {}
+        self._dist.barrier(self._group)  # nobody maps this buffer any more
+        _native.peer_buffer_destroy(self._own)
+        self._own = None
+        self._bases = []
+
+
+class _DeviceArray:
+    """Describes library-owned device memory to ``torch.as_tensor``."""
+
+    def __init__(self, pointer, count):
+        self.__cuda_array_interface__ = {
+            "shape": (count,), "typestr": "<f4", "data": (pointer, False),
+            "version": 2, "strides": None,
+        }
+
+
+def _device_view(torch, pointer, count, device):
+    if count == 0:
+        return torch.empty(0, dtype=torch.float32, device=f"cuda:{device}")
+    return torch.as_tensor(_DeviceArray(pointer, count),
+                           device=f"cuda:{device}")
+
+
+__all__ = ["PeerResults", "gather_results", "local_shard", "shard_cuts"]
