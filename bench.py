@@ -56,8 +56,11 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch of the dominant kernel divided by its algorithmic
 # bytes, from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum) of
 # shrunk cases; traffic grows in proportion to the units processed.
+# Softmax: the reads were measured (1.0077 x the input on a case shrunk 8x);
+# the writes are counted as algorithmic, because at that size much of the
+# output is still dirty in L2 when a kernel ends and the counter misses it.
 # Workloads without a capture report null.
-TRAFFIC_RATIO = {"c5": 1.0074, "c4": 0.966}
+TRAFFIC_RATIO = {"c5": 1.0091, "c4": 1.004}
 ALL_WORKLOADS = ("c1", "c1x256", "c2", "c3", "c4", "c5")
 VADD_COUNT = (1 << 28) - 37
 
