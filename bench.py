@@ -1,7 +1,8 @@
 """Benchmark of the segmented-reduction hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME]
-                    [--impl ours|reference] [--schedule NAME] [--allgather]
+                    [--impl ours|reference] [--schedule NAME]
+                    [--allgather | --peer-results]
 
 One "step" is one pass of the hot path over one batch of synthetic input.
 Default workload ``c5``: extreme-skew segmented sum, 2**30 fp32 values in 2**22
@@ -9,7 +10,10 @@ segments (64 of them 2**23 long), the configuration the multi-GPU metric is
 quoted on.  With N > 1 (launched by torchrun, one rank per GPU) the SAME 2**30
 values are cut into N element-balanced contiguous segment ranges -- strong
 scaling, no data-path collective (``--allgather`` adds the optional NCCL
-all-gather of the per-segment results to every step).
+all-gather of the per-segment results to every step; ``--peer-results`` the
+same exchange without a collective: every rank stores its results into every
+rank's copy through peer-mapped memory, one small kernel behind the
+reduction).
 
 Rank 0 prints ONE JSON line.
 
@@ -75,6 +79,9 @@ def parse_arguments():
     parser.add_argument("--schedule", default="auto")
     parser.add_argument("--block", type=int, default=128)
     parser.add_argument("--allgather", action="store_true")
+    parser.add_argument("--peer-results", action="store_true",
+                        help="every step also stores this rank's results "
+                             "into every rank's copy (peer-mapped memory)")
     parser.add_argument("--planner", default="device",
                         choices=["device", "host"],
                         help="where the plan of the timed region is built "
@@ -931,6 +938,16 @@ def run_ours(args):
             plain_step()
             multi_gpu.gather_results(problem.out, problem.cuts)
         problem.step = step_with_gather
+    exchange = None
+    if (args.peer_results and world > 1 and problem.operation == "reduce"
+            and problem.kind != "sum+max"):
+        exchange = multi_gpu.PeerResults(problem.cuts)
+        kernel_step = problem.step
+
+        def step_with_peer_stores():
+            kernel_step()
+            exchange.publish(problem.out)
+        problem.step = step_with_peer_stores
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     numbers = measure(problem, args.steps, args.warmup, barrier, peak)
@@ -987,7 +1004,8 @@ def run_ours(args):
             "single_thread_value": sample_count / single / 1e9,
         }
     del host_sources
-    launches = problem.launches_per_step()
+    launches = problem.launches_per_step() + (1 if exchange is not None
+                                              else 0)
     summary = {
         "operation": problem.operation, "kind": problem.kind,
         "count": problem.count, "segments": problem.segments,
@@ -997,6 +1015,10 @@ def run_ours(args):
         "config": workload_config(args, problem.text, problem.operation,
                                   problem.kind, problem.full_offsets),
     }
+    if exchange is not None:
+        exchange.close()
+    peer_stores = exchange is not None
+    exchange = None
     problem.close()
     del problem
     torch.cuda.empty_cache()
@@ -1058,7 +1080,10 @@ def run_ours(args):
                 "sharding": f"{world} element-balanced contiguous segment "
                             "ranges, no collective"
                             + (" + NCCL all-gather of results"
-                               if gather else ""),
+                               if gather else "")
+                            + (" + results stored into every rank's copy "
+                               "(peer-mapped memory, one kernel per step)"
+                               if peer_stores else ""),
                 "l2": numbers["l2"]},
             "hbm_gbs_per_gpu": step_gbs,
             "pct_of_8tbs_per_gpu": 100.0 * step_gbs / NOMINAL_HBM_GBS,
