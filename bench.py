@@ -886,6 +886,36 @@ def measure_e2e(problem, steps, barrier):
     return ms, h2d, d2h, sources
 
 
+def measure_h2d_alone(problem, sources, world, rank, barrier):
+    """This rank's host-to-device rate with the host to itself: the ranks
+    take turns copying their pinned inputs (three rounds each) while the
+    others wait at a barrier.  Beside the rates seen when all ranks copy at
+    once (the end-to-end steps) it says whether the links are independent or
+    the ranks share a host-side limit."""
+    import torch
+
+    if problem.operation == "vadd":
+        targets = [problem.x, problem.y]
+    else:
+        targets = [problem.values, problem.device_offsets]
+    rate = 0.0
+    for turn in range(world):
+        barrier()
+        if turn == rank:
+            start = torch.cuda.Event(enable_timing=True)
+            stop = torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(3):
+                for target, source in zip(targets, sources):
+                    target.copy_(source, non_blocking=True)
+            stop.record()
+            torch.cuda.current_stream().synchronize()
+            copied = 3 * sum(4 * source.numel() for source in sources)
+            rate = copied / (start.elapsed_time(stop) * 1e-3) / 1e9
+    barrier()
+    return rate
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -967,6 +997,27 @@ def run_ours(args):
         rates[rank] = h2d_rank_gbs
         dist.all_reduce(rates)
         h2d_rank_gbs = [round(float(r), 2) for r in rates.tolist()]
+        rates.zero_()
+        rates[rank] = measure_h2d_alone(problem, host_sources, world, rank,
+                                        barrier)
+        dist.all_reduce(rates)
+        h2d_alone_gbs = [round(float(r), 2) for r in rates.tolist()]
+        together, alone = sum(h2d_rank_gbs), sum(h2d_alone_gbs)
+        host_limit = (
+            f"all ranks copying at once move {together:.0f} GB/s in total "
+            f"against {alone:.0f} GB/s if every link ran at the rate it "
+            "reaches alone: "
+            + ("the ranks share a host-side limit (memory bandwidth of the "
+               "socket that holds the pinned buffers, or shared PCIe root "
+               "ports), not their own links"
+               if together < 0.8 * alone else
+               "the links run independently; a rank is bound by its own link")
+        )
+    else:
+        h2d_alone_gbs = None
+        host_limit = ("one rank: bound by its own PCIe link "
+                      f"({h2d_rank_gbs:.1f} GB/s over the whole step, copies "
+                      "and kernel in sequence)")
     e2e_ms = max_over_ranks(e2e_ms)
     clocks = sampler.stop() if sampler is not None else None
     parity = None
@@ -1093,6 +1144,8 @@ def run_ours(args):
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "ms_per_step": e2e_ms / e2e_steps,
                     "h2d_gbs_per_rank": h2d_rank_gbs,
+                    "h2d_gbs_per_rank_alone": h2d_alone_gbs,
+                    "host_limit": host_limit,
                     "host_cores_rank0": binding},
             "gpu_launches": args.steps * launches,
             "roofline": {
