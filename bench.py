@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME]
                     [--impl ours|reference] [--schedule NAME]
-                    [--allgather | --peer-results]
+                    [--allgather | --peer-results [fused|scatter]]
 
 One "step" is one pass of the hot path over one batch of synthetic input.
 Default workload ``c5``: extreme-skew segmented sum, 2**30 fp32 values in 2**22
@@ -12,7 +12,8 @@ values are cut into N element-balanced contiguous segment ranges -- strong
 scaling, no data-path collective (``--allgather`` adds the optional NCCL
 all-gather of the per-segment results to every step; ``--peer-results`` the
 same exchange without a collective: every rank stores its results into every
-rank's copy through peer-mapped memory, one small kernel behind the
+rank's copy through peer-mapped memory -- ``fused``, the default: by the
+reducing warps themselves; ``scatter``: by one small kernel behind the
 reduction).
 
 Rank 0 prints ONE JSON line.
@@ -79,7 +80,8 @@ def parse_arguments():
     parser.add_argument("--schedule", default="auto")
     parser.add_argument("--block", type=int, default=128)
     parser.add_argument("--allgather", action="store_true")
-    parser.add_argument("--peer-results", action="store_true",
+    parser.add_argument("--peer-results", nargs="?", const="fused",
+                        default=None, choices=["fused", "scatter"],
                         help="every step also stores this rank's results "
                              "into every rank's copy (peer-mapped memory)")
     parser.add_argument("--planner", default="device",
@@ -974,10 +976,16 @@ def run_ours(args):
         exchange = multi_gpu.PeerResults(problem.cuts)
         kernel_step = problem.step
 
-        def step_with_peer_stores():
+        def step_with_scatter():
             kernel_step()
             exchange.publish(problem.out)
-        problem.step = step_with_peer_stores
+
+        def step_fused():
+            exchange.reduce(problem.values, problem.device_offsets,
+                            problem.kind, problem.plan,
+                            schedule=args.schedule)
+        problem.step = (step_fused if args.peer_results == "fused"
+                        else step_with_scatter)
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     numbers = measure(problem, args.steps, args.warmup, barrier, peak)
@@ -1055,8 +1063,8 @@ def run_ours(args):
             "single_thread_value": sample_count / single / 1e9,
         }
     del host_sources
-    launches = problem.launches_per_step() + (1 if exchange is not None
-                                              else 0)
+    launches = problem.launches_per_step() + (
+        1 if exchange is not None and args.peer_results == "scatter" else 0)
     summary = {
         "operation": problem.operation, "kind": problem.kind,
         "count": problem.count, "segments": problem.segments,
@@ -1133,8 +1141,11 @@ def run_ours(args):
                             + (" + NCCL all-gather of results"
                                if gather else "")
                             + (" + results stored into every rank's copy "
-                               "(peer-mapped memory, one kernel per step)"
-                               if peer_stores else ""),
+                               "through peer-mapped memory ("
+                               + ("by the reducing warps themselves"
+                                  if args.peer_results == "fused"
+                                  else "one kernel behind the reduction")
+                               + ")" if peer_stores else ""),
                 "l2": numbers["l2"]},
             "hbm_gbs_per_gpu": step_gbs,
             "pct_of_8tbs_per_gpu": 100.0 * step_gbs / NOMINAL_HBM_GBS,

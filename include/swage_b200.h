@@ -284,6 +284,7 @@ int swg_segreduce_map(int kind, int dtype, const swg_map *map,
  * destroy undo open / create (close every mapping before the owner destroys).
  * Plumbing, no kernels.  No reference counterpart. */
 #define SWG_PEER_HANDLE_BYTES 64
+#define SWG_MAX_PEERS 16 /* destinations of one scatter / fused launch */
 int swg_peer_buffer_create(int64_t bytes, void **buffer, unsigned char *handle);
 int swg_peer_buffer_open(const unsigned char *handle, void **buffer);
 int swg_peer_buffer_close(void *buffer);
@@ -303,6 +304,24 @@ int swg_peer_buffer_destroy(void *buffer);
 int swg_scatter_results_f32(const float *src, int64_t count,
                             void *const *dst_bases, int32_t dst_count,
                             int64_t dst_offset, void *stream);
+
+/* Reduction and result exchange in one launch: swg_segreduce_f32 with a plan,
+ * except that the result of segment s is stored by the reducing warp (or by
+ * the merge pass, for a segment cut across tiles) at
+ * dst_bases[p][dst_offset + s] for EVERY destination p -- this GPU's copy of
+ * the full result array of a sharded reduction and its peers' copies
+ * (swg_peer_buffer_open) -- instead of a local out[s].  The stores over
+ * NVLink ride along with the reduction: no collective, no copy kernel, plain
+ * st.global only (no multicast, no load from peer memory, no wait on another
+ * GPU).  Tile schedules only (SPLIT or RESIDENT; anything else runs SPLIT), so
+ * a plan is required.  Same bits as swg_segreduce_f32 with that plan and
+ * schedule.  Completion on the peers as for swg_scatter_results_f32.  No
+ * reference counterpart. */
+int swg_segreduce_peers_f32(int kind, const float *values,
+                            const int32_t *offsets, void *const *dst_bases,
+                            int32_t dst_count, int64_t dst_offset,
+                            int32_t value_count, int32_t segment_count,
+                            const swg_plan *plan, int schedule, void *stream);
 
 /* Sum AND max of every segment in one pass over the values:
  * out_sum[s] = swg_segreduce_f32(SWG_KIND_SUM)[s] to the documented tolerance,

@@ -54,17 +54,22 @@ def build_library(force=False, verbose=False):
     """Compile every source for sm_100a and link the shared library."""
     if not force and not _stale():
         return LIBRARY
+    # linked under a temporary name and renamed, so that a reader never sees
+    # a half-written library
+    fresh = LIBRARY.with_suffix(".so.new")
     command = [_nvcc(), *NVCC_FLAGS, "-shared",
                "-I", str(ROOT / "include"), "-I", str(CSRC),
-               "-o", str(LIBRARY)]
+               "-o", str(fresh)]
     if verbose:
         command += ["-Xptxas", "-v"]
     command += [str(CSRC / name) for name in SOURCES]
     result = subprocess.run(command, capture_output=True, text=True)
     if result.returncode != 0:
+        fresh.unlink(missing_ok=True)
         raise RuntimeError(
             "nvcc failed:\n" + result.stdout + "\n" + result.stderr
         )
+    fresh.replace(LIBRARY)
     if verbose:
         sys.stderr.write(result.stderr)
     return LIBRARY

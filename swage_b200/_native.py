@@ -59,6 +59,7 @@ EXPORTS = (
     "swg_plan_peek_status", "swg_segreduce", "swg_plan_selftest_timeout",
     "swg_segreduce_map", "swg_scatter_results_f32", "swg_peer_buffer_create",
     "swg_peer_buffer_open", "swg_peer_buffer_close", "swg_peer_buffer_destroy",
+    "swg_segreduce_peers_f32",
 )
 
 _lock = threading.Lock()
@@ -112,6 +113,10 @@ def _declare(lib):
     lib.swg_peer_buffer_close.argtypes = [ptr]
     lib.swg_peer_buffer_destroy.restype = c_int
     lib.swg_peer_buffer_destroy.argtypes = [ptr]
+    lib.swg_segreduce_peers_f32.restype = c_int
+    lib.swg_segreduce_peers_f32.argtypes = [
+        c_int, ptr, ptr, ctypes.POINTER(ptr), c_i32, c_i64, c_i32, c_i32, ptr,
+        c_int, ptr]
     lib.swg_scatter_results_f32.restype = c_int
     lib.swg_scatter_results_f32.argtypes = [
         ptr, c_i64, ctypes.POINTER(ptr), c_i32, c_i64, ptr]
@@ -245,6 +250,20 @@ def peer_buffer_close(pointer):
 def peer_buffer_destroy(pointer):
     check(library().swg_peer_buffer_destroy(pointer),
           "swg_peer_buffer_destroy")
+
+
+def segreduce_peers(kind, values_ptr, offsets_ptr, destination_ptrs, offset,
+                    value_count, segment_count, plan_handle, schedule, stream):
+    """``segreduce`` with a plan whose results go to ``destination[p][offset +
+    s]`` for every destination pointer instead of a local output."""
+    bases = (ctypes.c_void_p * len(destination_ptrs))(*destination_ptrs)
+    check(
+        library().swg_segreduce_peers_f32(
+            kind, values_ptr, offsets_ptr, bases, len(destination_ptrs),
+            offset, value_count, segment_count, plan_handle, schedule,
+            stream),
+        "swg_segreduce_peers_f32",
+    )
 
 
 def scatter_results(src_ptr, count, destination_ptrs, offset, stream):

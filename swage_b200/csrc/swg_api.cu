@@ -6,6 +6,7 @@
 #include <new>
 #include <vector>
 
+#include "swg_common.cuh"
 #include "swg_launch.h"
 
 struct swg_plan {
@@ -741,6 +742,70 @@ int swg_segreduce_map(int kind, int dtype, const swg_map *map,
                    stream, map);
 }
 
+int swg_segreduce_peers_f32(int kind, const float *values,
+                            const int32_t *offsets, void *const *dst_bases,
+                            int32_t dst_count, int64_t dst_offset,
+                            int32_t value_count, int32_t segment_count,
+                            const swg_plan *plan, int schedule, void *stream) {
+  swg::clear_error();
+  const char *who = "swg_segreduce_peers_f32";
+  if (kind != SWG_KIND_SUM && kind != SWG_KIND_MAX && kind != SWG_KIND_MIN) {
+    swg::set_error(
+        "reduction kind must be SWG_KIND_SUM, SWG_KIND_MAX or SWG_KIND_MIN");
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  if (value_count < 0 || segment_count < 0 || dst_offset < 0 ||
+      dst_count < 1 || dst_count > SWG_MAX_PEERS) {
+    swg::set_error("%s: bad count or offset, or not 1..%d destinations", who,
+                   SWG_MAX_PEERS);
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  if (segment_count == 0) return SWG_OK;
+  if (!offsets || !dst_bases || (!values && value_count > 0)) {
+    swg::set_error("%s: null pointer", who);
+    return SWG_ERR_INVALID_ARGUMENT;
+  }
+  if (!plan) {
+    swg::set_error("%s needs a plan (it runs the tile schedules)", who);
+    return SWG_ERR_UNSUPPORTED;
+  }
+  int device = 0, sm_count = 0;
+  const int status = current_device(&device, &sm_count);
+  if (status != SWG_OK) return status;
+  if (plan->host.op != SWG_OP_REDUCE ||
+      plan->host.segment_count != segment_count ||
+      plan->host.value_count > value_count || plan->dev.device != device) {
+    swg::set_error("%s: the plan does not belong to this launch", who);
+    return SWG_ERR_PLAN_MISMATCH;
+  }
+  if (schedule == SWG_SCHED_AUTO) schedule = plan->host.schedule;
+  if (schedule != SWG_SCHED_RESIDENT) schedule = SWG_SCHED_SPLIT;
+  swg::PeerOut peers = {};
+  for (int p = 0; p < dst_count; ++p) {
+    if (!dst_bases[p] || ((uintptr_t)dst_bases[p] & 3u) != 0) {
+      swg::set_error("%s: destination %d is null or misaligned", who, p);
+      return SWG_ERR_INVALID_ARGUMENT;
+    }
+    peers.base[p] = static_cast<float *>(dst_bases[p]);
+  }
+  peers.count = dst_count;
+  peers.offset = dst_offset;
+  cudaStream_t s = (cudaStream_t)stream;
+  const swg::Probe *probe = next_probe();
+  note_launch(plan, s);
+  // `out` is unused by a peer launch: every result goes to the destinations
+  const cudaError_t e =
+      schedule == SWG_SCHED_RESIDENT
+          ? swg::launch_segreduce_resident(kind, SWG_DTYPE_F32, values,
+                                           nullptr, value_count, plan->dev, s,
+                                           probe, nullptr, &peers)
+          : swg::launch_segreduce_split(kind, SWG_DTYPE_F32, values, nullptr,
+                                        value_count, plan->dev, s, probe,
+                                        nullptr, &peers);
+  if (e != cudaSuccess) return cuda_failure("segmented reduce launch", e);
+  return SWG_OK;
+}
+
 // ---------------------------------------------------------------------------
 // Buffers other processes of the node can store into (CUDA IPC)
 // ---------------------------------------------------------------------------
@@ -807,10 +872,10 @@ int swg_scatter_results_f32(const float *src, int64_t count,
                             int64_t dst_offset, void *stream) {
   swg::clear_error();
   if (count < 0 || dst_offset < 0 || dst_count < 0 ||
-      dst_count > swg::kMaxPeers) {
+      dst_count > SWG_MAX_PEERS) {
     swg::set_error(
         "swg_scatter_results_f32: negative count or offset, or more than %d "
-        "destinations", swg::kMaxPeers);
+        "destinations", SWG_MAX_PEERS);
     return SWG_ERR_INVALID_ARGUMENT;
   }
   if (count == 0 || dst_count == 0) return SWG_OK;
@@ -818,7 +883,7 @@ int swg_scatter_results_f32(const float *src, int64_t count,
     swg::set_error("swg_scatter_results_f32: null pointer");
     return SWG_ERR_INVALID_ARGUMENT;
   }
-  float *bases[swg::kMaxPeers];
+  float *bases[SWG_MAX_PEERS];
   for (int p = 0; p < dst_count; ++p) {
     if (!dst_bases[p] || ((uintptr_t)dst_bases[p] & 15u) != 0) {
       swg::set_error(

@@ -181,6 +181,33 @@ __device__ __forceinline__ void with_fixed_map(const ScalarMap &map, F &&f) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// Where a segment's result goes.  NoPeers: out[seg], the caller's array.
+// PeerOut: element offset + seg of EVERY GPU's copy of the full result array
+// of a sharded reduction -- this GPU's own copy and its peers', mapped into
+// this process -- written by the reducing warp itself with plain stores, so
+// that the exchange of the results rides along with the reduction instead of
+// following it as a collective or a copy kernel.  No multicast, no load from
+// peer memory, nothing waits on another GPU.
+// ---------------------------------------------------------------------------
+constexpr int kMaxPeers = SWG_MAX_PEERS;
+
+struct NoPeers {
+  template <class A>
+  __device__ __forceinline__ void store(A *out, int seg, A v) const {
+    out[seg] = v;
+  }
+};
+
+struct PeerOut {
+  float *base[kMaxPeers];
+  int32_t count;
+  int64_t offset;
+  __device__ __forceinline__ void store(float *, int seg, float v) const {
+    for (int p = 0; p < count; ++p) base[p][offset + seg] = v;
+  }
+};
+
 template <class Op>
 __device__ __forceinline__ float fold4(float acc, float4 q) {
   return Op::apply(Op::apply(acc, Op::apply(q.x, q.y)), Op::apply(q.z, q.w));

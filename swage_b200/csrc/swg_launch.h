@@ -8,6 +8,11 @@
 
 namespace swg {
 
+// Destinations of a launch that stores its results into every GPU's copy of
+// a full result array (`peers`, may be null: results go to `out`); f32,
+// unmapped launches only.  Defined beside the kernels.
+struct PeerOut;
+
 constexpr int kTicketBase = 4;
 constexpr int kStatusWord = kTicketBase + kSoftmaxBuckets;  // 12
 constexpr int kControlWords = kStatusWord + 4;              // 16
@@ -60,7 +65,6 @@ cudaError_t launch_vadd(const float *x, const float *y, float *out, int32_t n,
 
 // dst_bases[p][dst_offset + i] = src[i] for every destination (device
 // pointers, possibly peer-mapped memory of other GPUs); plain stores.
-constexpr int kMaxPeers = 16;
 cudaError_t launch_scatter_results(const float *src, int64_t count,
                                    float *const *dst_bases, int peer_count,
                                    int64_t dst_offset, int sm_count,
@@ -87,7 +91,8 @@ cudaError_t launch_segreduce_split(int kind, int dtype, const void *values,
                                    void *out, int32_t value_count,
                                    const DevicePlan &plan, cudaStream_t stream,
                                    const Probe *probe,
-                                   const swg_map *map = nullptr);
+                                   const swg_map *map = nullptr,
+                                   const PeerOut *peers = nullptr);
 // Persistent CTAs, bulk-copy ring, ticket counter + merge pass.
 cudaError_t launch_segreduce_persistent(int kind, const float *values,
                                         float *out, int32_t value_count,
@@ -100,7 +105,8 @@ cudaError_t launch_segreduce_resident(int kind, int dtype, const void *values,
                                       void *out, int32_t value_count,
                                       const DevicePlan &plan,
                                       cudaStream_t stream, const Probe *probe,
-                                      const swg_map *map = nullptr);
+                                      const swg_map *map = nullptr,
+                                      const PeerOut *peers = nullptr);
 // A warp or a CTA per segment for f16 / bf16 / i32 values, and for mapped
 // reductions of every floating type (no plan).  `map` (may be null) is
 // applied to every value before it is reduced; integer segments ignore it.

@@ -436,12 +436,13 @@ __device__ __forceinline__ typename Op::Acc warp_range(const T *tile, int lo,
 }
 
 // Warp-collective: reduce one staged task.
-template <class Op, class T, class M>
+template <class Op, class T, class M, class R = NoPeers>
 __device__ __forceinline__ void process_task(
     const Task &task, const Stage &stage, int mis,
     typename Op::Acc *__restrict__ out,
     typename Op::Acc *__restrict__ partials, WarpScratch *scratch,
-    const Limits &limits, uint32_t *control, int lane, const M &map) {
+    const Limits &limits, uint32_t *control, int lane, const M &map,
+    const R &peers = R{}) {
   using A = typename Op::Acc;
   constexpr int P = kPerLine<T>;
   if (!task_ok(task, limits)) {
@@ -458,7 +459,7 @@ __device__ __forceinline__ void process_task(
     // One piece of a long segment occupies tile[shift, shift + vcount).
     const A r = warp_range<Op, T, M>(tile, shift, shift + vcount, lane, map);
     if (lane == 0) {
-      if (task.count < 0) out[task.seg] = r;
+      if (task.count < 0) peers.store(out, task.seg, r);
       else partials[task.count] = r;
     }
     return;
@@ -526,11 +527,15 @@ __device__ __forceinline__ void process_task(
     }
     const unsigned medium_mask = __ballot_sync(kFullMask, medium);
     const unsigned wide_mask = __ballot_sync(kFullMask, wide);
-    A *target = out + task.seg + k;
-    if (head_piece) target = partials + task.head_slot;
-    if (tail_piece) target = partials + task.tail_slot;
+    // a piece of a cut segment leaves a partial; a whole segment its result
+    A *piece = nullptr;
+    if (head_piece) piece = partials + task.head_slot;
+    if (tail_piece) piece = partials + task.tail_slot;
     if ((medium_mask | wide_mask) == 0) {
-      if (valid) *target = acc;
+      if (valid) {
+        if (piece) *piece = acc;
+        else peers.store(out, task.seg + k, acc);
+      }
       continue;
     }
     const int medium_count = __popc(medium_mask);
@@ -587,7 +592,10 @@ __device__ __forceinline__ void process_task(
     }
     __syncwarp();
     if (slot >= 0) acc = results[slot];
-    if (valid) *target = acc;
+    if (valid) {
+      if (piece) *piece = acc;
+      else peers.store(out, task.seg + k, acc);
+    }
     __syncwarp();  // the lists are rewritten by the next 32 segments
   }
 }
@@ -602,7 +610,7 @@ __device__ __forceinline__ void process_task(
 // find their lines on the way instead of starting a cold DRAM round trip
 // after the wait.  The caller's arrays are read into the SM and written only
 // after the kernel before has finished.
-template <class Op, class T, class M = NoMap>
+template <class Op, class T, class M = NoMap, class R = NoPeers>
 __global__ void __launch_bounds__(kSplitWarps * 32)
 segreduce_split_kernel(const T *__restrict__ values,
                        typename Op::Acc *__restrict__ out, int32_t value_count,
@@ -610,7 +618,7 @@ segreduce_split_kernel(const T *__restrict__ values,
                        const int32_t *__restrict__ d_off,
                        typename Op::Acc *__restrict__ partials,
                        uint32_t *__restrict__ control, Limits limits,
-                       uint32_t prefetch_ctas, M map) {
+                       uint32_t prefetch_ctas, M map, R peers) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full[kSplitWarps];
   __shared__ WarpScratch scratch[kSplitWarps];
@@ -657,9 +665,9 @@ segreduce_split_kernel(const T *__restrict__ values,
     return;
   }
   with_fixed_map(map, [&](auto apply) {
-    process_task<Op, T, decltype(apply)>(task, stage, mis, out, partials,
-                                         &scratch[warp], limits, control,
-                                         lane, apply);
+    process_task<Op, T, decltype(apply), R>(task, stage, mis, out, partials,
+                                            &scratch[warp], limits, control,
+                                            lane, apply, peers);
   });
 }
 
@@ -789,7 +797,7 @@ segreduce_persistent_kernel(const float *__restrict__ values,
 // hold many segments (their reduction keeps a stage busy longest), 7 % slower
 // where nearly every tile is a chunk of a long segment -- the planner picks by
 // the share of values in long segments.
-template <class Op, class T, int kWarps, class M = NoMap>
+template <class Op, class T, int kWarps, class M = NoMap, class R = NoPeers>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 segreduce_resident_kernel(const T *__restrict__ values,
                           typename Op::Acc *__restrict__ out,
@@ -798,7 +806,7 @@ segreduce_resident_kernel(const T *__restrict__ values,
                           const int32_t *__restrict__ d_off,
                           typename Op::Acc *__restrict__ partials,
                           uint32_t *__restrict__ control, Limits limits,
-                          M map) {
+                          M map, R peers) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint64_t full[kWarps];
   __shared__ WarpScratch scratch[kWarps];
@@ -852,9 +860,9 @@ segreduce_resident_kernel(const T *__restrict__ values,
     }
     parity ^= 1u;
     with_fixed_map(map, [&](auto apply) {
-      process_task<Op, T, decltype(apply)>(task, stage, mis, out, partials,
-                                           &scratch[warp], limits, control,
-                                           lane, apply);
+      process_task<Op, T, decltype(apply), R>(task, stage, mis, out, partials,
+                                              &scratch[warp], limits, control,
+                                              lane, apply, peers);
     });
     if (!more) return;
     __syncwarp();  // every lane is done with the stage before it is refilled
@@ -882,14 +890,15 @@ segreduce_resident_kernel(const T *__restrict__ values,
 // to be visible before they read one.
 constexpr int kMergeThreads = 512;
 
-template <class Op>
+template <class Op, class R = NoPeers>
 __global__ void __launch_bounds__(kMergeThreads)
 segreduce_merge_kernel(const MergeRecord *__restrict__ records, int32_t count,
                        uint32_t record_ctas,
                        const MergeRecord *__restrict__ bigs,
                        const int32_t *__restrict__ big_count,
                        const typename Op::Acc *__restrict__ partials,
-                       typename Op::Acc *__restrict__ out, Limits limits) {
+                       typename Op::Acc *__restrict__ out, Limits limits,
+                       R peers) {
   using A = typename Op::Acc;
   __shared__ float scratch[32];
   // the next launch in the stream, if it is one of the tile kernels, may
@@ -921,7 +930,7 @@ segreduce_merge_kernel(const MergeRecord *__restrict__ records, int32_t count,
 #pragma unroll
       for (int k = 0; k < kLaneMerge; ++k)
         if (k < r.pieces) acc = Op::apply(acc, q[k]);
-      out[r.seg] = acc;
+      peers.store(out, r.seg, acc);
     }
     unsigned waiting = __ballot_sync(kFullMask, medium);
     while (waiting) {
@@ -940,7 +949,7 @@ segreduce_merge_kernel(const MergeRecord *__restrict__ records, int32_t count,
       for (int u = 0; u < kWarpMerge / 32; ++u)
         if (lane + 32 * u < pieces) acc = Op::apply(acc, q[u]);
       acc = warp_reduce<Op>(acc);
-      if (lane == 0) out[seg] = acc;
+      if (lane == 0) peers.store(out, seg, acc);
     }
   } else {
     const int total = bigs != nullptr ? *big_count : 0;
@@ -971,7 +980,7 @@ segreduce_merge_kernel(const MergeRecord *__restrict__ records, int32_t count,
       const A mine =
           Op::apply(Op::apply(a[0], a[1]), Op::apply(a[2], a[3]));
       const A v = cta_reduce<Op>(mine, scratch);
-      if (tid == 0 && valid) out[r.seg] = v;
+      if (tid == 0 && valid) peers.store(out, r.seg, v);
       i += stride;
       if (i < total) r = bigs[i];
     }
@@ -1108,6 +1117,18 @@ cudaError_t configure_segreduce_kernels() {
         if (e != cudaSuccess) return e;
       }
     }
+    e = with_op(kind, [&](auto op) {
+      using Op = decltype(op);
+      const cudaError_t inner = cudaFuncSetAttribute(
+          segreduce_resident_kernel<Op, float, kResidentWarps, NoMap, PeerOut>,
+          cudaFuncAttributeMaxDynamicSharedMemorySize,
+          kResidentWarps * kStageBytes);
+      if (inner != cudaSuccess) return inner;
+      return cudaFuncSetAttribute(
+          segreduce_split_kernel<Op, float, NoMap, PeerOut>,
+          cudaFuncAttributeMaxDynamicSharedMemorySize, kSplitBytes);
+    });
+    if (e != cudaSuccess) return e;
   }
   return cudaSuccess;
 }
@@ -1232,7 +1253,8 @@ static cudaError_t launch_serialised(Kernel kernel, unsigned grid,
 
 static cudaError_t launch_merge(int kind, int dtype, const DevicePlan &plan,
                                 void *out, int32_t value_count,
-                                cudaStream_t stream) {
+                                cudaStream_t stream,
+                                const PeerOut *peers = nullptr) {
   if (plan.merge_count == 0 && plan.big_capacity == 0) return cudaSuccess;
   const unsigned record_ctas =
       (unsigned)(((int64_t)plan.merge_count + kMergeThreads - 1) /
@@ -1243,6 +1265,16 @@ static cudaError_t launch_merge(int kind, int dtype, const DevicePlan &plan,
   if (big_ctas > 2 * plan.sm_count) big_ctas = 2 * plan.sm_count;
   // (the accumulator type decides: f16 / bf16 values merge as fp32)
   const int acc_dtype = dtype == SWG_DTYPE_I32 ? SWG_DTYPE_I32 : SWG_DTYPE_F32;
+  if (peers)  // fp32 results stored into every GPU's copy
+    return with_op(kind, [&](auto op) {
+      using Op = decltype(op);
+      return launch_serialised(
+          segreduce_merge_kernel<Op, PeerOut>, record_ctas + (unsigned)big_ctas,
+          kMergeThreads, 0, stream, (const MergeRecord *)plan.merges,
+          plan.merge_count, record_ctas, (const MergeRecord *)plan.bigs,
+          (const int32_t *)plan.big_count, (const float *)plan.partials,
+          static_cast<float *>(out), limits_of(plan, value_count), *peers);
+    });
   return with_types(kind, acc_dtype, [&](auto op, auto) {
     using Op = decltype(op);
     using A = typename Op::Acc;
@@ -1252,37 +1284,50 @@ static cudaError_t launch_merge(int kind, int dtype, const DevicePlan &plan,
         plan.merge_count, record_ctas, (const MergeRecord *)plan.bigs,
         (const int32_t *)plan.big_count,
         reinterpret_cast<const A *>(plan.partials), static_cast<A *>(out),
-        limits_of(plan, value_count));
+        limits_of(plan, value_count), NoPeers{});
   });
 }
 
 cudaError_t launch_segreduce_split(int kind, int dtype, const void *values,
                                    void *out, int32_t value_count,
                                    const DevicePlan &plan, cudaStream_t stream,
-                                   const Probe *probe, const swg_map *map) {
+                                   const Probe *probe, const swg_map *map,
+                                   const PeerOut *peers) {
   if (plan.task_count == 0) return cudaSuccess;
   const unsigned grid =
       (unsigned)((plan.task_count + kSplitWarps - 1) / kSplitWarps);
   const uint32_t first_wave =
       (uint32_t)plan.sm_count * SWG_SPLIT_CTAS_PER_SM;
   probe_begin(probe, stream);
-  const cudaError_t e =
-      with_map(kind, dtype, map, [&](auto op, auto element, auto m) {
-        using Op = decltype(op);
-        using T = decltype(element);
-        using M = decltype(m);
-        using A = typename Op::Acc;
-        return launch_serialised(
-            segreduce_split_kernel<Op, T, M>, grid, kSplitWarps * 32,
-            kSplitBytes, stream, static_cast<const T *>(values),
-            static_cast<A *>(out), value_count, (const Task *)plan.tasks,
-            plan.task_count, (const int32_t *)plan.offsets,
-            reinterpret_cast<A *>(plan.partials), plan.control,
-            limits_of(plan, value_count), first_wave, m);
-      });
+  cudaError_t e;
+  if (peers)  // f32, unmapped (checked by the caller)
+    e = with_op(kind, [&](auto op) {
+      using Op = decltype(op);
+      return launch_serialised(
+          segreduce_split_kernel<Op, float, NoMap, PeerOut>, grid,
+          kSplitWarps * 32, kSplitBytes, stream,
+          static_cast<const float *>(values), static_cast<float *>(out),
+          value_count, (const Task *)plan.tasks, plan.task_count,
+          (const int32_t *)plan.offsets, plan.partials, plan.control,
+          limits_of(plan, value_count), first_wave, NoMap{}, *peers);
+    });
+  else
+    e = with_map(kind, dtype, map, [&](auto op, auto element, auto m) {
+      using Op = decltype(op);
+      using T = decltype(element);
+      using M = decltype(m);
+      using A = typename Op::Acc;
+      return launch_serialised(
+          segreduce_split_kernel<Op, T, M>, grid, kSplitWarps * 32,
+          kSplitBytes, stream, static_cast<const T *>(values),
+          static_cast<A *>(out), value_count, (const Task *)plan.tasks,
+          plan.task_count, (const int32_t *)plan.offsets,
+          reinterpret_cast<A *>(plan.partials), plan.control,
+          limits_of(plan, value_count), first_wave, m, NoPeers{});
+    });
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;
-  return launch_merge(kind, dtype, plan, out, value_count, stream);
+  return launch_merge(kind, dtype, plan, out, value_count, stream, peers);
 }
 
 cudaError_t launch_segreduce_persistent(int kind, const float *values,
@@ -1305,31 +1350,44 @@ cudaError_t launch_segreduce_resident(int kind, int dtype, const void *values,
                                       void *out, int32_t value_count,
                                       const DevicePlan &plan,
                                       cudaStream_t stream, const Probe *probe,
-                                      const swg_map *map) {
+                                      const swg_map *map,
+                                      const PeerOut *peers) {
   if (plan.task_count == 0) return cudaSuccess;
   int grid = plan.sm_count;
   const int needed = (plan.task_count + kResidentWarps - 1) / kResidentWarps;
   if (grid > needed) grid = needed;
   probe_begin(probe, stream);
-  const cudaError_t e =
-      with_map(kind, dtype, map, [&](auto op, auto element, auto m) {
-        using Op = decltype(op);
-        using T = decltype(element);
-        using M = decltype(m);
-        using A = typename Op::Acc;
-        return launch_serialised(
-            segreduce_resident_kernel<Op, T, kResidentWarps, M>,
-            (unsigned)grid, kResidentWarps * 32,
-            (size_t)kResidentWarps * kStageBytes, stream,
-            static_cast<const T *>(values), static_cast<A *>(out),
-            value_count, (const Task *)plan.tasks, plan.task_count,
-            (const int32_t *)plan.offsets,
-            reinterpret_cast<A *>(plan.partials), plan.control,
-            limits_of(plan, value_count), m);
-      });
+  cudaError_t e;
+  if (peers)  // f32, unmapped (checked by the caller)
+    e = with_op(kind, [&](auto op) {
+      using Op = decltype(op);
+      return launch_serialised(
+          segreduce_resident_kernel<Op, float, kResidentWarps, NoMap, PeerOut>,
+          (unsigned)grid, kResidentWarps * 32,
+          (size_t)kResidentWarps * kStageBytes, stream,
+          static_cast<const float *>(values), static_cast<float *>(out),
+          value_count, (const Task *)plan.tasks, plan.task_count,
+          (const int32_t *)plan.offsets, plan.partials, plan.control,
+          limits_of(plan, value_count), NoMap{}, *peers);
+    });
+  else
+    e = with_map(kind, dtype, map, [&](auto op, auto element, auto m) {
+      using Op = decltype(op);
+      using T = decltype(element);
+      using M = decltype(m);
+      using A = typename Op::Acc;
+      return launch_serialised(
+          segreduce_resident_kernel<Op, T, kResidentWarps, M>, (unsigned)grid,
+          kResidentWarps * 32, (size_t)kResidentWarps * kStageBytes, stream,
+          static_cast<const T *>(values), static_cast<A *>(out), value_count,
+          (const Task *)plan.tasks, plan.task_count,
+          (const int32_t *)plan.offsets,
+          reinterpret_cast<A *>(plan.partials), plan.control,
+          limits_of(plan, value_count), m, NoPeers{});
+    });
   probe_end(probe, stream);
   if (e != cudaSuccess) return e;
-  return launch_merge(kind, dtype, plan, out, value_count, stream);
+  return launch_merge(kind, dtype, plan, out, value_count, stream, peers);
 }
 
 // ---------------------------------------------------------------------------

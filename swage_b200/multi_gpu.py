@@ -86,8 +86,10 @@ class PeerResults:
     queues ONE kernel on the current stream that stores this rank's
     ``cuts[rank + 1] - cuts[rank]`` results at their place in every copy --
     plain 128-bit stores over NVLink, no multicast, no load from peer memory,
-    nothing waits on another GPU.  ``wait()`` (synchronise the stream, then a
-    host barrier) is when ``results`` is complete on every rank.
+    nothing waits on another GPU.  ``reduce(values, offsets, kind, plan)``
+    goes one step further: the reduction's own warps store each result into
+    every copy as they produce it.  ``wait()`` (synchronise the stream, then
+    a host barrier) is when ``results`` is complete on every rank.
 
     One process per GPU, all on one node.  Collective: every rank of ``group``
     constructs, and later closes, its ``PeerResults`` together.
@@ -148,6 +150,56 @@ class PeerResults:
         _native.scatter_results(local_output.data_ptr(), count, self._bases,
                                 self.cuts[self.rank], stream.cuda_stream)
         local_output.record_stream(stream)
+
+    def reduce(self, values, offsets, kind, plan, schedule="auto"):
+        """Reduce this rank's shard and store every result straight into every
+        rank's copy, in ONE launch sequence (tile kernel + merge pass): the
+        reducing warps themselves issue the stores over NVLink, so the
+        exchange rides along with the reduction -- no collective and no copy
+        kernel behind it.  ``values`` / ``offsets`` are this rank's shard
+        (offsets rebased to zero, on its GPU), ``plan`` a ``SegmentPlan`` for
+        them (``plan_segments``); the caller has validated the offsets (the
+        plan was built from them).  Same bits as ``launch_gpu`` with that
+        plan.  ``wait()`` as after ``publish``.
+        """
+        from . import _native
+        from . import _segmented_qualification as runner
+
+        torch = _runtime._import_torch()
+        count = self.cuts[self.rank + 1] - self.cuts[self.rank]
+        for name, tensor, dtype in (("values", values, torch.float32),
+                                    ("offsets", offsets, torch.int32)):
+            if (not isinstance(tensor, torch.Tensor) or tensor.dtype != dtype
+                    or tensor.dim() != 1 or not tensor.is_contiguous()
+                    or tensor.device.type != "cuda"
+                    or tensor.device.index != self.device):
+                raise TypeError(
+                    f"{name} must be a contiguous rank-one {dtype} tensor on "
+                    "this rank's GPU")
+        if offsets.numel() != count + 1:
+            raise ValueError(
+                f"offsets describe {offsets.numel() - 1} segments, this "
+                f"rank's shard has {count}")
+        if kind in runner._KINDS:
+            kind_code = runner._KINDS[kind]
+        elif kind in runner._EXTENDED_KINDS:
+            kind_code = runner._EXTENDED_KINDS[kind]
+        else:
+            raise ValueError("reduction kind must be 'sum', 'max' or 'min'")
+        if not isinstance(plan, runner.SegmentPlan):
+            raise TypeError("plan must be a SegmentPlan for these offsets")
+        if self._own is None:
+            raise RuntimeError("the peer buffers are closed")
+        if count == 0:
+            return
+        runner._peek(plan)
+        stream = _runtime._current_stream(torch)
+        _native.segreduce_peers(
+            kind_code, values.data_ptr(), offsets.data_ptr(), self._bases,
+            self.cuts[self.rank], values.numel(), count, plan.handle,
+            runner._schedule_code(schedule), stream.cuda_stream)
+        for tensor in (values, offsets):
+            tensor.record_stream(stream)
 
     def wait(self):
         """On return ``results`` holds every rank's published results."""

@@ -1,8 +1,9 @@
 """One rank of tests/test_gpu_peer_results.py (run as a child process).
 
 Reduces its shard of a small extreme-skew problem, publishes the results into
-every rank's copy through ``PeerResults`` and checks the full array against
-the CPU oracle.  RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT come from the
+every rank's copy through ``PeerResults`` -- once with the scatter kernel
+behind the reduction, once with the reduction's own warps storing into every
+copy -- and checks the full array against the CPU oracle.  RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT come from the
 environment; the ranks talk over gloo, and share GPU 0 when the box has fewer
 GPUs than ranks (CUDA IPC works between processes on one device too).
 """
@@ -21,7 +22,10 @@ import torch.distributed as dist  # noqa: E402
 import oracle  # noqa: E402
 import workloads  # noqa: E402
 from swage_b200 import multi_gpu  # noqa: E402
-from swage_b200._segmented_qualification import launch_gpu  # noqa: E402
+from swage_b200._segmented_qualification import (  # noqa: E402
+    launch_gpu,
+    plan_segments,
+)
 
 
 def main():
@@ -55,6 +59,31 @@ def main():
                 bound = oracle.sum_tolerance(host_values, offsets)
                 assert np.all(np.abs(got - exact) <= bound), "sum out of bound"
             dist.barrier()  # everyone has read before the next kind overwrites
+        # the fused form: the reduction's own warps store into every copy
+        plan = plan_segments(device_offsets, int(values.numel()))
+        try:
+            for kind, schedule in (("max", "split"), ("max", "resident"),
+                                   ("sum", "auto")):
+                exchange.results.fill_(float("nan"))
+                torch.cuda.synchronize()
+                dist.barrier()
+                exchange.reduce(values, device_offsets, kind, plan,
+                                schedule=schedule)
+                exchange.wait()
+                got = exchange.results.cpu().numpy()
+                if kind == "max":
+                    expected = oracle.segreduce_f32(host_values, offsets,
+                                                    "max")
+                    assert np.array_equal(got.view(np.uint32),
+                                          expected.view(np.uint32)), schedule
+                else:
+                    exact = oracle.segsum_f64(host_values, offsets)
+                    bound = oracle.sum_tolerance(host_values, offsets)
+                    assert np.all(np.abs(got - exact) <= bound), schedule
+                dist.barrier()
+            plan.check()
+        finally:
+            plan.close()
     finally:
         exchange.close()
     dist.destroy_process_group()

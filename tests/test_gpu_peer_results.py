@@ -63,6 +63,59 @@ def test_scatter_rejects_bad_arguments():
                                 stream)
 
 
+@pytest.mark.parametrize("schedule", ["split", "resident"])
+@pytest.mark.parametrize("kind", ["sum", "max", "min"])
+def test_fused_launch_stores_every_result_in_every_destination(kind, schedule):
+    """Same-process form of the fused reduce + exchange: three destination
+    arrays on this GPU, results at an odd offset.  Bit for bit what the plain
+    launch with the same plan and schedule writes (so parity with the oracle
+    carries over), guard elements untouched."""
+    import workloads
+    from swage_b200._segmented_qualification import launch_gpu, plan_segments
+
+    offsets = workloads.c5_offsets(segments=(1 << 13) + 5, total=1 << 21,
+                                   giants=3, giant_length=1 << 18)
+    segments = len(offsets) - 1
+    count = int(offsets[-1])
+    values = workloads.normal_values(count, "cuda", 17)
+    device_offsets = torch.as_tensor(offsets).cuda()
+    plan = plan_segments(device_offsets, count)
+    try:
+        plain = torch.empty(segments, device="cuda")
+        launch_gpu(values, device_offsets, plain, kind, plan=plan,
+                   schedule=schedule, extensions=True)
+        shift = 37
+        destinations = [
+            torch.full((shift + segments + 9,), float("nan"), device="cuda")
+            for _ in range(3)]
+        _native.segreduce_peers(
+            {"sum": 0, "max": 1, "min": 2}[kind], values.data_ptr(),
+            device_offsets.data_ptr(), [d.data_ptr() for d in destinations],
+            shift, count, segments, plan.handle, _native.SCHEDULES[schedule],
+            torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        plan.check()
+        expected = plain.cpu().numpy().view(np.uint32)
+        for destination in destinations:
+            host = destination.cpu().numpy()
+            assert np.array_equal(
+                host[shift:shift + segments].view(np.uint32), expected)
+            assert np.isnan(host[:shift]).all()
+            assert np.isnan(host[shift + segments:]).all()
+    finally:
+        plan.close()
+
+
+def test_fused_launch_needs_a_plan():
+    values = torch.ones(8, device="cuda")
+    offsets = torch.tensor([0, 4, 8], dtype=torch.int32, device="cuda")
+    out = torch.zeros(2, device="cuda")
+    with pytest.raises(RuntimeError, match="needs a plan"):
+        _native.segreduce_peers(0, values.data_ptr(), offsets.data_ptr(),
+                                [out.data_ptr()], 0, 8, 2, None, 0,
+                                torch.cuda.current_stream().cuda_stream)
+
+
 def free_port():
     with socket.socket() as probe:
         probe.bind(("127.0.0.1", 0))
