@@ -782,6 +782,41 @@ def measure_mapped(problem, check):
     return result
 
 
+def measure_vadd_misaligned(device, block):
+    """The vector add on views whose three pointers disagree on their phase
+    inside a 16-byte line (element offsets 1, 2 and 3): the element-wise
+    kernel the library falls back to, against the 256-bit kernel of aligned
+    inputs.  CUDA events around twenty launches, inputs larger than L2."""
+    import torch
+
+    from swage_b200 import _native
+
+    n = VADD_COUNT
+    base = [torch.empty(n + 4, device=device).normal_() for _ in range(2)]
+    base.append(torch.empty(n + 4, device=device))
+    x, y, out = (tensor[shift:shift + n]
+                 for shift, tensor in zip((1, 2, 3), base))
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        _native.vadd(x.data_ptr(), y.data_ptr(), out.data_ptr(), n, block,
+                     stream)
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(20):
+        _native.vadd(x.data_ptr(), y.data_ptr(), out.data_ptr(), n, block,
+                     stream)
+    stop.record()
+    torch.cuda.synchronize()
+    same = bool(torch.equal(out, x + y))
+    kernel_ms = start.elapsed_time(stop) / 20
+    return {"what": "views at element offsets 1, 2, 3 (scalar kernel)",
+            "kernel_us": 1e3 * kernel_ms,
+            "kernel_gbs": 12.0 * n / (kernel_ms * 1e-3) / 1e9,
+            "parity": "bit-exact vs x + y" if same else "MISMATCH"}
+
+
 def measure_cold(problem, barrier):
     """The drop-in call on offsets no cache has seen: validation, planning
     and launch, inputs resident on the device.  Fourteen different offsets
@@ -1115,6 +1150,10 @@ def run_ours(args):
             other.close()
             del other
             torch.cuda.empty_cache()
+            if name == "c2":
+                entry["misaligned_views"] = measure_vadd_misaligned(
+                    device, args.block)
+                torch.cuda.empty_cache()
 
     if rank == 0:
         ms_per_step = elapsed_ms / args.steps
