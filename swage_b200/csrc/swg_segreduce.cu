@@ -48,10 +48,15 @@ __global__ void __launch_bounds__(kWarpKernelThreads, SWG_WARP_MINBLOCKS)
 segreduce_warp_kernel(const float *__restrict__ values,
                       const int32_t *__restrict__ offsets,
                       float *__restrict__ out, int32_t segment_count) {
+  // Launched with programmatic stream serialisation: when the kernel before
+  // this one in the stream is one of this library's, the CTAs are placed
+  // while it drains; nothing of the caller's is touched before the wait.
+  asm volatile("griddepcontrol.launch_dependents;");
   const int lane = threadIdx.x & 31;
   const int64_t warp =
       ((int64_t)blockIdx.x * kWarpKernelThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kWarpKernelThreads) >> 5;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   for (int64_t seg = warp; seg < segment_count; seg += nwarps) {
     const int64_t begin = __ldg(offsets + seg);
     const int64_t end = __ldg(offsets + seg + 1);
@@ -75,7 +80,10 @@ segreduce_sum_max_kernel(const float *__restrict__ values,
                          float *__restrict__ out_sum,
                          float *__restrict__ out_max, int32_t segment_count) {
   __shared__ float scratch[32];
+  // (programmatic stream serialisation: see segreduce_warp_kernel)
+  asm volatile("griddepcontrol.launch_dependents;");
   const int lane = threadIdx.x & 31;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (kCta) {
     for (int64_t seg = blockIdx.x; seg < segment_count; seg += gridDim.x) {
       const int64_t begin = __ldg(offsets + seg);
@@ -1133,6 +1141,25 @@ cudaError_t configure_segreduce_kernels() {
   return cudaSuccess;
 }
 
+// A tile kernel launched with programmatic stream serialisation: it may be
+// placed while the kernel before it in the stream drains (see the kernels).
+template <class Kernel, class... Args>
+static cudaError_t launch_serialised(Kernel kernel, unsigned grid,
+                                     unsigned block, size_t shared,
+                                     cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(block);
+  config.dynamicSmemBytes = shared;
+  config.stream = stream;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, args...);
+}
+
 // Plan-free launch for the element types other than f32.
 cudaError_t launch_segreduce_typed(int kind, int dtype, const void *values,
                                    const int32_t *offsets, void *out,
@@ -1177,10 +1204,9 @@ cudaError_t launch_segreduce_warp(int kind, const float *values,
   if (grid > cap) grid = cap;
   probe_begin(probe, stream);
   const cudaError_t e = with_op(kind, [&](auto op) {
-    segreduce_warp_kernel<decltype(op)>
-        <<<(unsigned)grid, kWarpKernelThreads, 0, stream>>>(
-            values, offsets, out, segment_count);
-    return cudaGetLastError();
+    return launch_serialised(segreduce_warp_kernel<decltype(op)>,
+                             (unsigned)grid, kWarpKernelThreads, 0, stream,
+                             values, offsets, out, segment_count);
   });
   probe_end(probe, stream);
   return e;
@@ -1198,15 +1224,13 @@ cudaError_t launch_segreduce_sum_max(const float *values,
   const int64_t cap = (int64_t)sm_count * 8 * 4;
   if (grid > cap) grid = cap;
   probe_begin(probe, stream);
-  if (cta)
-    segreduce_sum_max_kernel<true>
-        <<<(unsigned)grid, kWarpKernelThreads, 0, stream>>>(
-            values, offsets, out_sum, out_max, segment_count);
-  else
-    segreduce_sum_max_kernel<false>
-        <<<(unsigned)grid, kWarpKernelThreads, 0, stream>>>(
-            values, offsets, out_sum, out_max, segment_count);
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e =
+      cta ? launch_serialised(segreduce_sum_max_kernel<true>, (unsigned)grid,
+                              kWarpKernelThreads, 0, stream, values, offsets,
+                              out_sum, out_max, segment_count)
+          : launch_serialised(segreduce_sum_max_kernel<false>, (unsigned)grid,
+                              kWarpKernelThreads, 0, stream, values, offsets,
+                              out_sum, out_max, segment_count);
   probe_end(probe, stream);
   return e;
 }
@@ -1230,25 +1254,6 @@ cudaError_t launch_segreduce_cta(int kind, const float *values,
   });
   probe_end(probe, stream);
   return e;
-}
-
-// A tile kernel launched with programmatic stream serialisation: it may be
-// placed while the kernel before it in the stream drains (see the kernels).
-template <class Kernel, class... Args>
-static cudaError_t launch_serialised(Kernel kernel, unsigned grid,
-                                     unsigned block, size_t shared,
-                                     cudaStream_t stream, Args... args) {
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(grid);
-  config.blockDim = dim3(block);
-  config.dynamicSmemBytes = shared;
-  config.stream = stream;
-  cudaLaunchAttribute attribute;
-  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute.val.programmaticStreamSerializationAllowed = 1;
-  config.attrs = &attribute;
-  config.numAttrs = 1;
-  return cudaLaunchKernelEx(&config, kernel, args...);
 }
 
 static cudaError_t launch_merge(int kind, int dtype, const DevicePlan &plan,
