@@ -92,7 +92,8 @@ class PeerResults:
     a host barrier) is when ``results`` is complete on every rank.
 
     One process per GPU, all on one node.  Collective: every rank of ``group``
-    constructs, and later closes, its ``PeerResults`` together.
+    constructs, and later closes, its ``PeerResults`` together.  ``results``
+    is a view of library-owned memory: it must not be used after ``close()``.
     """
 
     def __init__(self, cuts, group=None):
