@@ -746,7 +746,39 @@ def measure(problem, steps, warmup, barrier, peak):
     }
     if warm_ms is not None:
         result["kernel_warm_ms"] = float(np.mean(warm_ms))
+    if fits_l2 and problem.kind == "sum+max":
+        result["launch_interval_ms"] = launch_interval_ms(problem)
     return result
+
+
+def launch_interval_ms(problem, launches=200):
+    """Device time per launch when the fused sum+max kernel of a small input
+    is issued back to back straight through the C ABI (two CUDA events around
+    ``launches`` calls, L2-warm).  An event pair around ONE launch of a kernel
+    this short measures mostly the events; the interval between launches in a
+    saturated stream -- each launch placed while the one before drains -- is
+    what a caller issuing many small reductions gets."""
+    import torch
+
+    from swage_b200 import _native
+
+    pointers = (problem.values.data_ptr(), problem.device_offsets.data_ptr(),
+                problem.out.data_ptr(), problem.out2.data_ptr())
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def issue(count):
+        for _ in range(count):
+            _native.segreduce_sum_max(*pointers, problem.count,
+                                      problem.segments, stream)
+    issue(20)
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    issue(launches)
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / launches
 
 
 def measure_mapped(problem, check):
@@ -1171,6 +1203,8 @@ def run_ours(args):
             }
             if "kernel_warm_ms" in got:
                 entry["kernel_warm_us"] = 1e3 * got["kernel_warm_ms"]
+            if "launch_interval_ms" in got:
+                entry["launch_interval_us"] = 1e3 * got["launch_interval_ms"]
             if not args.no_parity:
                 entry["parity"] = other.parity()
             others[name] = entry
