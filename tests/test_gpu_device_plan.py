@@ -19,7 +19,6 @@ from gpu_util import (
 from swage_b200 import _native
 from swage_b200 import _segmented_qualification as runner
 from swage_b200._segmented_qualification import (
-    SegmentPlan,
     launch_gpu,
     launch_softmax_gpu,
     plan_segments,

@@ -1,6 +1,5 @@
 """Offsets validation, planner and sharding: host logic only (no GPU)."""
 
-import ctypes
 import json
 import pathlib
 
