@@ -181,7 +181,13 @@ segsoftmax_resident_kernel(const float *__restrict__ values,
   __shared__ float scratch[32];
   constexpr bool kGroup = kThreads <= 32;
   const int t = kGroup ? (int)(threadIdx.x % kThreads) : (int)threadIdx.x;
-  const int64_t which =
+  // Groups narrower than a CTA take one segment each; a CTA-wide group walks
+  // the list with the grid's stride (the launcher sizes the grid to what is
+  // resident at once), and fetches the bounds of its next segment while the
+  // values of the current one are in flight: neither a CTA launch nor the two
+  // dependent index loads sit between two segments of a CTA.
+  const int64_t stride = kGroup ? (int64_t)count : (int64_t)gridDim.x;
+  int64_t which =
       kGroup ? ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / kThreads
              : (int64_t)blockIdx.x;
   // a group past the end of the list keeps in step with the rest of its warp
@@ -192,30 +198,46 @@ segsoftmax_resident_kernel(const float *__restrict__ values,
     begin = __ldg(offsets + seg);
     length = (int)(__ldg(offsets + seg + 1) - begin);
   }
-  const float *p = values + begin + t;
-  float x[kRows];
+  while (true) {
+    const float *p = values + begin + t;
+    float x[kRows];
 #pragma unroll
-  for (int r = 0; r < kRows; ++r)
-    x[r] = (r * kThreads + t < length) ? __ldcs(p + r * kThreads)
-                                       : MaxOp::identity();
-  float m = x[0];
+    for (int r = 0; r < kRows; ++r)
+      x[r] = (r * kThreads + t < length) ? __ldcs(p + r * kThreads)
+                                         : MaxOp::identity();
+    const int64_t after = which + stride;
+    int64_t next_begin = 0;
+    int next_length = 0;
+    if (!kGroup && after < count) {
+      const int32_t seg = __ldg(segments + after);
+      next_begin = __ldg(offsets + seg);
+      next_length = (int)(__ldg(offsets + seg + 1) - next_begin);
+    }
+    float m = x[0];
 #pragma unroll
-  for (int r = 1; r < kRows; ++r) m = MaxOp::apply(m, x[r]);
-  m = kGroup ? group_reduce<MaxOp>(m, kThreads) : cta_reduce<MaxOp>(m, scratch);
-  float d = 0.0f;
+    for (int r = 1; r < kRows; ++r) m = MaxOp::apply(m, x[r]);
+    m = kGroup ? group_reduce<MaxOp>(m, kThreads)
+               : cta_reduce<MaxOp>(m, scratch);
+    float d = 0.0f;
 #pragma unroll
-  for (int r = 0; r < kRows; ++r) {
-    // padding slots are masked: exp(-inf - m) is 0 only for an ordered m
-    const float e = (r * kThreads + t < length) ? exp_neg(x[r] - m) : 0.0f;
-    x[r] = e;
-    d += e;
+    for (int r = 0; r < kRows; ++r) {
+      // padding slots are masked: exp(-inf - m) is 0 only for an ordered m
+      const float e = (r * kThreads + t < length) ? exp_neg(x[r] - m) : 0.0f;
+      x[r] = e;
+      d += e;
+    }
+    d = kGroup ? group_reduce<SumOp>(d, kThreads)
+               : cta_reduce<SumOp>(d, scratch);
+    const float inv = 1.0f / d;
+    float *o = out + begin + t;
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+      if (r * kThreads + t < length) __stcs(o + r * kThreads, x[r] * inv);
+    if (kGroup || after >= count) break;
+    which = after;
+    begin = next_begin;
+    length = next_length;
   }
-  d = kGroup ? group_reduce<SumOp>(d, kThreads) : cta_reduce<SumOp>(d, scratch);
-  const float inv = 1.0f / d;
-  float *o = out + begin + t;
-#pragma unroll
-  for (int r = 0; r < kRows; ++r)
-    if (r * kThreads + t < length) __stcs(o + r * kThreads, x[r] * inv);
 }
 
 // Pieces of the streamed (two-sweep) schedule.
@@ -761,8 +783,13 @@ static cudaError_t launch_buckets(const float *values, const int32_t *offsets,
                              plan, side);
       if (e != cudaSuccess) return e;
     } else if (b == 2) {
+      // persistent over the class's list: what is resident at once
+      // (registers allow twelve 128-thread CTAs per SM), never more CTAs
+      // than segments
+      const int resident = plan.sm_count * 12;
       segsoftmax_resident_kernel<128, 16>
-          <<<(unsigned)n, 128, 0, side>>>(values, offsets, out, bucket, n);
+          <<<(unsigned)(n < resident ? n : resident), 128, 0, side>>>(
+              values, offsets, out, bucket, n);
     } else if (b == 1) {
       segsoftmax_resident_kernel<32, 16>
           <<<(unsigned)((n + 7) / 8), 256, 0, side>>>(values, offsets, out,
