@@ -6,8 +6,9 @@
 ``torch``.  With this library aliased under that name (``install_as``) they
 run as they are: the validation and oracle cases everywhere, the launch cases
 wherever a CUDA device is present as well.  The files are read from a
-reference checkout (``SWAGE_REFERENCE``, default ``/root/reference``) and are
-never copied; without a checkout the test is skipped.
+reference checkout (``SWAGE_REFERENCE``; default: a directory ``reference``
+beside this repository) and are never copied; without a checkout the test is
+skipped.
 """
 
 import os
@@ -18,7 +19,8 @@ import sys
 import pytest
 
 ROOT = pathlib.Path(__file__).resolve().parent.parent
-REFERENCE = pathlib.Path(os.environ.get("SWAGE_REFERENCE", "/root/reference"))
+REFERENCE = pathlib.Path(
+    os.environ.get("SWAGE_REFERENCE", ROOT.parent / "reference"))
 FILES = ("python/tests/mlir/test_runtime.py",
          "python/tests/mlir/test_segmented_runtime.py")
 
